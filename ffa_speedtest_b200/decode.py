@@ -1,0 +1,201 @@
+"""Host side of the FFA decode call: the reference's validation, then one C-ABI call.
+
+Mirrors the wrappers ``attn_forward_decode_*`` of the reference
+(ffa-q2fp8/attn_kernel/attn_kernel_v1210_fused_bsz_q2fp8.py:191-309 and the fp8fp8 / fp4fp8 /
+nf4fp8 / nvfp4fp8 siblings): same positional and keyword arguments, same exceptions for the
+same mistakes, same return values.  Additions, all keyword-only and off by default:
+
+* ``block_table`` ``[B, pages] int32`` (+ ``seq_len``): K/V tensors are then paged pools
+  ``[n_pages, 64, HKV, D]``; ``None`` keeps the reference layout ``[B, T, HKV, D]``.
+* ``workspace``: a :class:`DecodeWorkspace` to reuse scratch and output across calls.
+* ``out``: preallocated output ``[B, HQ, V]``.
+* ``partial_out``: ``[B, HQ, 129]`` fp32 buffer receiving (normalised output, base-2 LSE) for
+  merging across sequence shards.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+PAGE = 64
+
+
+class DecodeWorkspace:
+    """Reusable scratch for one decode shape (the analogue of ``Q2FP8DecodeWorkspace`` in
+    ffa-q2fp8-h100/attn_kernel/attn_kernel_v1210_fused_bsz_q2fp8.py:232-277)."""
+
+    def __init__(self, B: int, T: int, HQ: int, HKV: int, V: int, *, BS: int, SBS: int, device, dtype,
+                 pages_per_chunk: int = 0):
+        self.key = (B, T, HQ, HKV, V, BS, SBS, torch.device(device), dtype, pages_per_chunk)
+        nbytes = _lib.lib().ffa_decode_workspace_bytes(B, T, HQ, HKV, pages_per_chunk)
+        ntbs = -(-T // BS) * (BS // SBS)
+        self.scratch = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        self.o = torch.empty((B, HQ, V), dtype=dtype, device=device)
+        self.mask = torch.empty((B, HKV, ntbs), dtype=torch.int8, device=device)
+        self.threshold = torch.empty((B, HQ), dtype=torch.float32, device=device)
+        self.pages_per_chunk = pages_per_chunk
+
+
+def allocate_decode_workspace(q, v, *, BS: int = 128, SBS: Optional[int] = None, seq_len: Optional[int] = None,
+                              pages_per_chunk: int = 0) -> DecodeWorkspace:
+    B, _, HQ, _ = q.shape
+    T = seq_len if seq_len is not None else v.shape[1]
+    return DecodeWorkspace(B, T, HQ, v.shape[2], v.shape[3], BS=BS, SBS=SBS or BS, device=q.device, dtype=q.dtype,
+                           pages_per_chunk=pages_per_chunk)
+
+
+def _fp8_format(*tensors) -> int:
+    """fp8 encoding shared by the fp8 tensors of a call (e5m2 if there is none)."""
+    fmt = None
+    for t in tensors:
+        if t is None:
+            continue
+        if t.dtype not in (torch.float8_e5m2, torch.float8_e4m3fn):
+            raise ValueError(
+                f"this build reads fp8 (float8_e5m2 / float8_e4m3fn) K base and residual tensors, got {t.dtype}")
+        code = _lib.fp8_code(t.dtype)
+        if fmt is not None and fmt != code:
+            raise ValueError("fp8 K base and residual must use the same fp8 encoding")
+        fmt = code
+    return _lib.E5M2 if fmt is None else fmt
+
+
+def decode_call(
+    variant: str,
+    q: torch.Tensor,
+    k_codes: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    k_scale: Optional[torch.Tensor] = None,
+    k_zero: Optional[torch.Tensor] = None,
+    k_residual: Optional[torch.Tensor] = None,
+    scale: Optional[float] = None,
+    BS: int = 128,
+    SBS: Optional[int] = None,
+    delta: float = 5.0,
+    return_skip_ratio: bool = False,
+    precomputed_threshold: Optional[torch.Tensor] = None,
+    use_fp8_residual: bool = True,
+    block_table: Optional[torch.Tensor] = None,
+    seq_len: Optional[int] = None,
+    workspace: Optional[DecodeWorkspace] = None,
+    out: Optional[torch.Tensor] = None,
+    partial_out: Optional[torch.Tensor] = None,
+    pages_per_chunk: int = 0,
+):
+    """Shape bookkeeping shared by the five entry points; tensors are already type-checked."""
+    B, Tq, HQ, K = q.shape
+    HKV, V = v.shape[2], v.shape[3]
+    if block_table is None:
+        T = v.shape[1]
+    else:
+        if block_table.dtype != torch.int32 or block_table.dim() != 2 or block_table.shape[0] != B:
+            raise ValueError("block_table must be an int32 tensor of shape [B, pages_per_sequence]")
+        if v.shape[1] != PAGE or k_codes.shape[1] != PAGE:
+            raise ValueError("with block_table, K/V tensors are paged pools [n_pages, 64, HKV, D]")
+        T = seq_len if seq_len is not None else block_table.shape[1] * PAGE
+        if block_table.shape[1] * PAGE < T:
+            raise ValueError("block_table has too few pages for seq_len")
+        assert block_table.is_cuda and block_table.is_contiguous()
+    if HQ % HKV != 0:
+        raise ValueError(f"HQ ({HQ}) must be divisible by HKV ({HKV}) for GQA")
+    G = HQ // HKV
+    if K != 128 or V != 128:
+        raise ValueError(f"this build supports head_dim 128 for K and V, got K={K}, V={V}")
+    if G > 8:
+        raise ValueError(f"this build supports GQA group sizes up to 8, got {G}")
+    if scale is None:
+        scale = 1.0 / math.sqrt(K)
+    if SBS is None:
+        SBS = BS
+    if SBS != PAGE or BS % PAGE != 0:
+        raise ValueError(f"this build prunes at page granularity: SBS must be 64 and BS a multiple of 64 "
+                         f"(got BS={BS}, SBS={SBS})")
+    NTB = -(-T // BS)
+    NTBS = NTB * (BS // SBS)
+
+    use_res = bool(use_fp8_residual and k_residual is not None)
+    fp8_fmt = _fp8_format(k_codes if variant == "fp8" else None, k_residual if use_res else None)
+
+    if precomputed_threshold is not None:
+        assert precomputed_threshold.is_cuda and precomputed_threshold.shape == (B, HQ)
+        th_in = precomputed_threshold.contiguous()
+        if th_in.dtype != torch.float32:
+            th_in = th_in.float()
+    else:
+        th_in = None
+
+    if workspace is None:
+        workspace = DecodeWorkspace(B, T, HQ, HKV, V, BS=BS, SBS=SBS, device=q.device, dtype=q.dtype,
+                                    pages_per_chunk=pages_per_chunk)
+    elif workspace.key != (B, T, HQ, HKV, V, BS, SBS, q.device, q.dtype, pages_per_chunk):
+        raise ValueError("workspace was allocated for a different decode shape")
+    o = workspace.o if out is None else out
+    if o.shape != (B, HQ, V) or o.dtype != q.dtype or not o.is_contiguous():
+        raise ValueError("out must be a contiguous [B, HQ, V] tensor of q's dtype")
+    if partial_out is not None:
+        if partial_out.shape != (B, HQ, V + 1) or partial_out.dtype != torch.float32 or not partial_out.is_contiguous():
+            raise ValueError("partial_out must be a contiguous fp32 [B, HQ, 129] tensor")
+
+    a = _lib.FfaDecodeArgs()
+    a.variant = _lib.VARIANT_CODE[variant]
+    a.B, a.T, a.HQ, a.HKV, a.head_dim = B, T, HQ, HKV, K
+    a.BS, a.SBS = BS, SBS
+    a.sm_scale, a.delta = float(scale), float(delta)
+    a.q_dtype = _lib.float_code(q.dtype)
+    a.v_dtype = _lib.float_code(v.dtype)
+    if a.v_dtype == _lib.F32:
+        raise ValueError("v must be float16 or bfloat16")
+    a.scale_dtype = _lib.float_code(k_scale.dtype) if k_scale is not None else _lib.F32
+    a.fp8_format = fp8_fmt
+    a.use_residual = int(use_res)
+    a.q, a.k_codes, a.v = q.data_ptr(), k_codes.data_ptr(), v.data_ptr()
+    a.k_scale, a.k_zero = _lib.ptr(k_scale), _lib.ptr(k_zero)
+    a.k_residual = k_residual.data_ptr() if use_res else None
+    a.block_table = _lib.ptr(block_table)
+    a.bt_stride = block_table.shape[1] if block_table is not None else 0
+    a.threshold_in = _lib.ptr(th_in)
+    a.out = o.data_ptr()
+    a.kept_mask = workspace.mask.data_ptr()
+    a.threshold_out = workspace.threshold.data_ptr()
+    a.partial_out = _lib.ptr(partial_out)
+    a.workspace = workspace.scratch.data_ptr()
+    a.workspace_bytes = workspace.scratch.numel()
+    a.pages_per_chunk = pages_per_chunk
+    _lib.check(_lib.lib().ffa_decode(a, _lib.current_stream(q.device)), "ffa_decode")
+
+    if return_skip_ratio:
+        kept = workspace.mask.to(torch.int32).sum()
+        total = workspace.mask.numel()
+        skip_ratio = float((1.0 - (kept.float() / float(total))).item())
+        return o, skip_ratio
+    return o
+
+
+def check_common(q, k_codes, v, k_residual, what: str):
+    """The checks every reference wrapper makes before launching (…q2fp8.py:211-262)."""
+    assert q.is_cuda and k_codes.is_cuda and v.is_cuda
+    if k_residual is not None and not k_residual.is_cuda:
+        raise ValueError("k_residual must be a CUDA tensor when provided")
+    if k_residual is not None and not k_residual.is_floating_point():
+        raise ValueError("k_residual must be a floating point tensor (e.g., fp8/fp16/bf16)")
+    if q.dim() != 4 or k_codes.dim() != 4 or v.dim() != 4:
+        raise ValueError(f"{what}: q, K and v must be 4-D tensors")
+    assert q.is_contiguous() and k_codes.is_contiguous() and v.is_contiguous()
+    if k_residual is not None:
+        assert k_residual.is_contiguous()
+
+
+def check_layout(q, k_codes, v, k_residual, k_last: int, paged: bool):
+    B, Tq, HQ, K = q.shape
+    Bk, T, HKV, Kk = k_codes.shape
+    Bv, Tv, HKVv, V = v.shape
+    ok = Tq == 1 and Tv == T and HKVv == HKV and Kk == k_last and (paged or B == Bk == Bv) and Bk == Bv
+    if k_residual is not None:
+        Br, Tr, HKVr, Kr = k_residual.shape
+        ok = ok and Br == Bk and Tr == T and HKVr == HKV and Kr == K
+    assert ok, "K/V layouts must be [B, T, HKV, D]"

@@ -1,0 +1,100 @@
+"""K-cache quantisers on the GPU, with the reference's function names and return values.
+
+Each function is one or two streaming CUDA passes (``ffa_quantize_*`` in libffa_b200.so) that
+reproduce the reference's torch implementation bit for bit on the same K:
+
+====================================  =====================================================
+this module                           reference
+====================================  =====================================================
+``quantize_k_2bit_fp8_residual``      ffa-q2fp8/fused_kproj_rope_q2fp8.py:40-68
+``quantize_k_fp8_fp8_residual``       ffa-fp8fp8/fused_kproj_rope_fp8fp8.py:58-64
+``encode_k_fp4_fp8_residual``         ffa-fp4fp8/fused_kproj_rope_fp4fp8.py:40-73
+``encode_k_nf4_fp8_residual``         ffa-nf4fp8/fused_kproj_rope_nf4fp8.py:72-96
+``encode_k_nvfp4_fp8_residual``       ffa-nvfp4fp8/fused_kproj_rope_nvfp4fp8.py:62-114
+====================================  =====================================================
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+
+from . import _lib
+
+
+def _prep(k: torch.Tensor, fp8_dtype: torch.dtype):
+    if not k.is_cuda:
+        raise ValueError("k must be a CUDA tensor (this build has no CPU path)")
+    if k.dim() != 4 or k.shape[-1] != 128:
+        raise ValueError(f"k must be [B, T, HKV, 128], got {tuple(k.shape)}")
+    if k.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError(f"k must be float16 or bfloat16, got {k.dtype}")
+    k = k.contiguous()
+    B, T, HKV, D = k.shape
+    return k, B, T, HKV, _lib.float_code(k.dtype), _lib.fp8_code(fp8_dtype), _lib.current_stream(k.device)
+
+
+def _scratch(B: int, HKV: int, device) -> torch.Tensor:
+    return torch.empty(_lib.lib().ffa_quantize_scratch_bytes(B, HKV), dtype=torch.uint8, device=device)
+
+
+def quantize_k_2bit_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype
+                                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """-> (codes [B,T,HKV,32] u8, scale [B,HKV,128], zero [B,HKV,128], residual [B,T,HKV,128] fp8)."""
+    k, B, T, HKV, dt, f8, st = _prep(k, fp8_dtype)
+    codes = torch.empty((B, T, HKV, 32), dtype=torch.uint8, device=k.device)
+    scale = torch.empty((B, HKV, 128), dtype=k.dtype, device=k.device)
+    zero = torch.empty_like(scale)
+    res = torch.empty((B, T, HKV, 128), dtype=fp8_dtype, device=k.device)
+    scratch = _scratch(B, HKV, k.device)
+    _lib.check(_lib.lib().ffa_quantize_q2(k.data_ptr(), dt, B, T, HKV, f8, codes.data_ptr(), scale.data_ptr(),
+                                          zero.data_ptr(), res.data_ptr(), scratch.data_ptr(), st), "ffa_quantize_q2")
+    return codes, scale, zero, res
+
+
+def quantize_k_fp8_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor]:
+    """-> (base [B,T,HKV,128] fp8, residual [B,T,HKV,128] fp8)."""
+    k, B, T, HKV, dt, f8, st = _prep(k, fp8_dtype)
+    base = torch.empty((B, T, HKV, 128), dtype=fp8_dtype, device=k.device)
+    res = torch.empty_like(base)
+    _lib.check(_lib.lib().ffa_quantize_fp8fp8(k.data_ptr(), dt, B, T, HKV, f8, base.data_ptr(), res.data_ptr(), st),
+               "ffa_quantize_fp8fp8")
+    return base, res
+
+
+def encode_k_fp4_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor]:
+    """-> (nibbles [B,T,HKV,64] u8, residual fp8)."""
+    k, B, T, HKV, dt, f8, st = _prep(k, fp8_dtype)
+    codes = torch.empty((B, T, HKV, 64), dtype=torch.uint8, device=k.device)
+    res = torch.empty((B, T, HKV, 128), dtype=fp8_dtype, device=k.device)
+    _lib.check(_lib.lib().ffa_quantize_fp4(k.data_ptr(), dt, B, T, HKV, f8, codes.data_ptr(), res.data_ptr(), st),
+               "ffa_quantize_fp4")
+    return codes, res
+
+
+def encode_k_nf4_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype
+                              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """-> (nibbles [B,T,HKV,64] u8, absmax [B,HKV,128] in k's dtype, residual fp8)."""
+    k, B, T, HKV, dt, f8, st = _prep(k, fp8_dtype)
+    codes = torch.empty((B, T, HKV, 64), dtype=torch.uint8, device=k.device)
+    scale = torch.empty((B, HKV, 128), dtype=k.dtype, device=k.device)
+    res = torch.empty((B, T, HKV, 128), dtype=fp8_dtype, device=k.device)
+    scratch = _scratch(B, HKV, k.device)
+    _lib.check(_lib.lib().ffa_quantize_nf4(k.data_ptr(), dt, B, T, HKV, f8, codes.data_ptr(), scale.data_ptr(),
+                                           res.data_ptr(), scratch.data_ptr(), st), "ffa_quantize_nf4")
+    return codes, scale, res
+
+
+def encode_k_nvfp4_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype, page_size: int
+                                ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """-> (nibbles [B,T,HKV,64] u8, scale [B, ceil(T/page), HKV] in k's dtype, residual fp8)."""
+    if page_size <= 0:
+        raise ValueError(f"page_size must be positive, got {page_size}")
+    k, B, T, HKV, dt, f8, st = _prep(k, fp8_dtype)
+    n_pages = -(-T // page_size)
+    codes = torch.empty((B, T, HKV, 64), dtype=torch.uint8, device=k.device)
+    scale = torch.empty((B, n_pages, HKV), dtype=k.dtype, device=k.device)
+    res = torch.empty((B, T, HKV, 128), dtype=fp8_dtype, device=k.device)
+    _lib.check(_lib.lib().ffa_quantize_nvfp4(k.data_ptr(), dt, B, T, HKV, f8, page_size, codes.data_ptr(),
+                                             scale.data_ptr(), res.data_ptr(), st), "ffa_quantize_nvfp4")
+    return codes, scale, res

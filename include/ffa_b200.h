@@ -1,0 +1,143 @@
+/*
+ * C ABI of libffa_b200.so: FFA quantised, pruned decode attention and its quantisers for
+ * NVIDIA B200 (sm_100a).
+ *
+ * The reference project (qluoluo/ffa-speedtest) has no FFI: its boundary for this path is a
+ * set of Python entry points that validate tensors and launch two Triton kernels.  Every
+ * function below is what a binding for one of those entry points calls after it has done
+ * the reference's own validation; each comment cites the reference interface it replaces
+ * (paths relative to the reference root).
+ *
+ * Conventions: all pointers are device pointers unless stated; all tensors are contiguous;
+ * nothing here allocates, synchronises or throws; every call only enqueues work on `stream`
+ * and is safe to record into a CUDA graph.  Return value 0 = enqueued, negative = FFA_E_*.
+ */
+#ifndef FFA_B200_H_
+#define FFA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* ffa_stream_t; /* a cudaStream_t */
+
+enum {
+  FFA_OK = 0,
+  FFA_E_NULL = -1,        /* a required pointer is NULL */
+  FFA_E_SHAPE = -2,       /* unsupported dimension (head_dim != 128, G > 8, page != 64, ...) */
+  FFA_E_DTYPE = -3,       /* unsupported element type code */
+  FFA_E_WORKSPACE = -4,   /* workspace too small */
+  FFA_E_LAUNCH = -5,      /* the CUDA runtime refused the launch (see ffa_last_cuda_error) */
+  FFA_E_VARIANT = -6,     /* unknown coarse-K format */
+  FFA_E_LIMIT = -7        /* size beyond a compiled-in maximum */
+};
+
+/* element types */
+enum { FFA_F16 = 0, FFA_BF16 = 1, FFA_F32 = 2 };
+/* fp8 encodings (torch.float8_e5m2 / torch.float8_e4m3fn) */
+enum { FFA_E5M2 = 0, FFA_E4M3 = 1 };
+/* coarse K formats, one per reference variant directory */
+enum {
+  FFA_K_FP8 = 0,   /* ffa-fp8fp8   : fp8 cast of K, 128 B per token per kv-head           */
+  FFA_K_Q2 = 1,    /* ffa-q2fp8    : 2-bit codes + (scale, zero) per (b, kv-head, channel) */
+  FFA_K_FP4 = 2,   /* ffa-fp4fp8   : unscaled e2m1 nibbles                                 */
+  FFA_K_NF4 = 3,   /* ffa-nf4fp8   : NF4 nibbles + absmax per (b, kv-head, channel)        */
+  FFA_K_NVFP4 = 4  /* ffa-nvfp4fp8 : e2m1 nibbles + one scale per (b, BS-block, kv-head)   */
+};
+
+/*
+ * Arguments of one decode step.  Token rows of the K/V tensors are addressed as
+ *     row(b, t) = block_table ? block_table[b*bt_stride + t/64]*64 + t%64 : b*T + t
+ * and a row holds HKV heads back to back, i.e. the reference layout [B, T, HKV, D] when
+ * block_table is NULL and a paged pool [n_pages, 64, HKV, D] otherwise.
+ */
+typedef struct FfaDecodeArgs {
+  int32_t variant;          /* FFA_K_*                                                          */
+  int32_t B, T, HQ, HKV;    /* batch, context length, query heads, kv heads (G = HQ/HKV <= 8)   */
+  int32_t head_dim;         /* K = V = 128                                                      */
+  int32_t BS, SBS;          /* reference block sizes; SBS (prune granularity) must be 64,
+                               BS a multiple of 64                                              */
+  float sm_scale;           /* softmax scale, reference default 1/sqrt(K)                       */
+  float delta;              /* threshold offset in log2 units                                   */
+  int32_t q_dtype;          /* FFA_F16 | FFA_BF16 | FFA_F32; the output has the same type       */
+  int32_t v_dtype;          /* FFA_F16 | FFA_BF16                                               */
+  int32_t scale_dtype;      /* type of k_scale / k_zero                                         */
+  int32_t fp8_format;       /* FFA_E5M2 | FFA_E4M3: residual (and fp8 base) encoding            */
+  int32_t use_residual;     /* 0: refine == coarse scores (reference use_fp8_residual=False)    */
+  const void* q;            /* [B, HQ, 128]                                                     */
+  const void* k_codes;      /* coarse K rows: 128 B (fp8), 32 B (q2) or 64 B (4-bit) per head   */
+  const void* k_scale;      /* q2, nf4: [B, HKV, 128]; nvfp4: [B, ceil(T/BS), HKV]; else NULL   */
+  const void* k_zero;       /* q2: [B, HKV, 128]; else NULL                                     */
+  const void* k_residual;   /* fp8 rows, 128 B per head; may be NULL when use_residual == 0     */
+  const void* v;            /* V rows, 256 B per head                                           */
+  const int32_t* block_table; /* [B, bt_stride] page ids, or NULL for the contiguous layout     */
+  int32_t bt_stride;
+  const float* threshold_in;  /* [B, HQ] precomputed thresholds, or NULL to derive them          */
+  void* out;                /* [B, HQ, 128] in q_dtype                                          */
+  int8_t* kept_mask;        /* optional [B, HKV, NTBS] (NTBS = ceil(T/BS)*(BS/SBS)), 1 = kept   */
+  float* threshold_out;     /* optional [B, HQ]: thresholds actually used                       */
+  float* partial_out;       /* optional [B, HQ, 129] fp32: normalised output followed by the
+                               base-2 log-sum-exp of the kept scores (-inf if none kept), the
+                               form ffa_merge_partials consumes                                 */
+  void* workspace;          /* >= ffa_decode_workspace_bytes(...) bytes, 256-byte aligned       */
+  size_t workspace_bytes;
+  int32_t pages_per_chunk;  /* 0 = choose automatically                                         */
+  int32_t reserved;
+} FfaDecodeArgs;
+
+/* Replaces attn_forward_decode_quantized / _fp8fp8 / _fp4 / _nf4 / _nvfp4fp8 after validation:
+ *   ffa-q2fp8/attn_kernel/attn_kernel_v1210_fused_bsz_q2fp8.py:264-304 (allocate, stage 1, stage 2)
+ *   ffa-fp8fp8/attn_kernel/attn_kernel_v1210_fused_bsz_fp8fp8.py:243-308
+ *   ffa-fp4fp8/attn_kernel/attn_kernel_v1210_fused_bsz_fp4fp8.py:182-294
+ *   ffa-nf4fp8/attn_kernel/attn_kernel_v1210_fused_bsz_nf4fp8.py:212-330
+ *   ffa-nvfp4fp8/attn_kernel/attn_kernel_v1210_fused_bsz_nvfp4fp8.py:225-367 */
+int ffa_decode(const FfaDecodeArgs* args, ffa_stream_t stream);
+
+/* Scratch needed by ffa_decode for these dimensions (the reference allocates m_buf, l_buf,
+ * o_buf and mask_buf per call: ...q2fp8.py:269-273). */
+size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, int32_t HKV, int32_t pages_per_chunk);
+
+/* Chunking ffa_decode will use: pages per CTA and CTAs per (b, kv-head). */
+int ffa_decode_plan(int32_t B, int32_t T, int32_t HKV, int32_t pages_per_chunk_in,
+                    int32_t* pages_per_chunk, int32_t* n_chunks);
+
+/* Merge R partial results (split-KV inside a GPU, or one per rank after an all-gather):
+ * parts is [R, rows, 129] fp32 holding a normalised partial output (128) followed by its
+ * base-2 LSE (-inf when the part kept nothing).  out is [rows, 128] in out_dtype.
+ * The reference has only the intra-GPU form: attn_forward_stage2_masked
+ * (ffa-q2fp8/attn_kernel/attn_kernel_v1210_fused_bsz_q2fp8.py:142-171). */
+int ffa_merge_partials(const float* parts, int32_t R, int32_t rows, void* out, int32_t out_dtype,
+                       ffa_stream_t stream);
+
+/* Standalone quantisers, bit-exact with the reference's torch functions on the same K.
+ * k is [B, T, HKV, 128] in k_dtype (FFA_F16 | FFA_BF16); outputs use the reference layouts.
+ * scratch must hold ffa_quantize_scratch_bytes(B, HKV) bytes (per-channel min/max). */
+size_t ffa_quantize_scratch_bytes(int32_t B, int32_t HKV);
+/* ffa-q2fp8/fused_kproj_rope_q2fp8.py:40-68  quantize_k_2bit_fp8_residual */
+int ffa_quantize_q2(const void* k, int32_t k_dtype, int32_t B, int32_t T, int32_t HKV, int32_t fp8_format,
+                    uint8_t* codes, void* scale, void* zero, uint8_t* residual, void* scratch, ffa_stream_t stream);
+/* ffa-fp8fp8/fused_kproj_rope_fp8fp8.py:58-64  quantize_k_fp8_fp8_residual */
+int ffa_quantize_fp8fp8(const void* k, int32_t k_dtype, int32_t B, int32_t T, int32_t HKV, int32_t fp8_format,
+                        uint8_t* base, uint8_t* residual, ffa_stream_t stream);
+/* ffa-fp4fp8/fused_kproj_rope_fp4fp8.py:40-73  encode_k_fp4_fp8_residual */
+int ffa_quantize_fp4(const void* k, int32_t k_dtype, int32_t B, int32_t T, int32_t HKV, int32_t fp8_format,
+                     uint8_t* codes, uint8_t* residual, ffa_stream_t stream);
+/* ffa-nf4fp8/fused_kproj_rope_nf4fp8.py:72-96  encode_k_nf4_fp8_residual */
+int ffa_quantize_nf4(const void* k, int32_t k_dtype, int32_t B, int32_t T, int32_t HKV, int32_t fp8_format,
+                     uint8_t* codes, void* scale, uint8_t* residual, void* scratch, ffa_stream_t stream);
+/* ffa-nvfp4fp8/fused_kproj_rope_nvfp4fp8.py:62-114  encode_k_nvfp4_fp8_residual */
+int ffa_quantize_nvfp4(const void* k, int32_t k_dtype, int32_t B, int32_t T, int32_t HKV, int32_t fp8_format,
+                       int32_t page_size, uint8_t* codes, void* scale, uint8_t* residual, ffa_stream_t stream);
+
+/* Text of the last CUDA runtime error seen by this library on the calling thread ("" if none). */
+const char* ffa_last_cuda_error(void);
+/* Library version, bumped when the ABI changes. */
+int ffa_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FFA_B200_H_ */
