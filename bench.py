@@ -1,0 +1,359 @@
+#!/usr/bin/env python
+"""Benchmark of the FFA pruned decode-attention step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A "step" is one decode-attention call over one batch of synthetic K/V cache (one pass of the hot
+path).  The default workload is BASELINE config 1: fp8 K + fp8 residual ("fp8fp8"), batch 8,
+32 query / 8 kv heads, head_dim 128, context 32768, page 64, delta 8, bf16 V as in the reference.
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank owns its own batch
+of the same size - the (batch x kv-head) units are sharded with no data-path collective - so the
+job is N times larger ("weak" scaling).
+
+One JSON line is printed by rank 0.  `value` is the whole-job achieved HBM rate over the
+ALGORITHMIC bytes of a step (coarse K of every page + residual and V of the kept pages + block
+table + q + o), with the K/V cache resident in HBM; `ms_per_step` carries the latency half of the
+metric.  `e2e` is the same rate measured through the public Python entry point with the step's
+host-resident input (q) copied in and the result (o) copied out inside the timed region.
+
+`--impl reference` times the CPU restatement of the reference algorithm (oracle/ffa_oracle.py,
+torch eager on all host threads) on a bounded sample of the same workload: the reference itself
+is Triton-only and has no CPU implementation that can travel to the benchmark machine.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: kind, B, T, delta, fp8
+    "fp8fp8_b8_t32k": dict(kind="fp8", B=8, T=32768, delta=8.0, fp8="e4m3"),
+    "q2fp8_b1_t4k": dict(kind="q2", B=1, T=4096, delta=8.0, fp8="e4m3"),
+    "q2fp8_b32_t128k": dict(kind="q2", B=32, T=131072, delta=8.0, fp8="e4m3"),
+    "fp4fp8_b16_t64k": dict(kind="fp4", B=16, T=65536, delta=8.0, fp8="e4m3"),
+    "nf4fp8_b16_t64k": dict(kind="nf4", B=16, T=65536, delta=8.0, fp8="e4m3"),
+    "nvfp4fp8_b16_t64k": dict(kind="nvfp4", B=16, T=65536, delta=8.0, fp8="e4m3"),
+}
+HQ, HKV, D, PAGE = 32, 8, 128, 64
+CODE_BYTES = {"fp8": 128, "q2": 32, "fp4": 64, "nf4": 64, "nvfp4": 64}
+METRIC = "decode_attn_achieved_hbm_TBps"   # BASELINE metric: decode-attn us/step and achieved HBM TB/s
+UNIT = "TB/s"
+
+
+def algorithmic_bytes(kind: str, B: int, T: int, kept_fraction: float, paged: bool) -> float:
+    """Bytes one decode step has to touch."""
+    n_pages = -(-T // PAGE)
+    coarse = B * HKV * T * CODE_BYTES[kind]
+    refine = kept_fraction * B * HKV * T * (128 + 256)           # fp8 residual + bf16 V
+    table = B * n_pages * 4 if paged else 0
+    scales = {"q2": 2 * D * 2, "nf4": D * 2}.get(kind, 0) * B * HKV
+    if kind == "nvfp4":
+        scales = B * n_pages * HKV * 2
+    qo = 2 * B * HQ * D * 2
+    return coarse + refine + table + scales + qo
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return json.loads(p.read_text()).get("hbm_gbs", 6650.0), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(index)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        rows = [r.split(", ") for r in Path(self.tmp.name).read_text().strip().splitlines() if r.strip()]
+        os.unlink(self.tmp.name)
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in rows:
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.strip().lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def oracle_step_fn(kind: str, B: int, T: int, delta: float, fp8: str, seed: int):
+    """CPU restatement on a (B, T) workload: returns (callable, kept_fraction)."""
+    from oracle import ffa_oracle as fo
+    from ffa_speedtest_b200.synth import make_decode_inputs
+    f8 = {"e5m2": torch.float8_e5m2, "e4m3": torch.float8_e4m3fn}[fp8]
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, D, seed=seed)
+    coarse, res = fo.make_coarse(kind, k, f8, PAGE)
+    del k
+
+    def step():
+        return fo.decode_attention_fast(q, coarse, v, res, BS=PAGE, SBS=PAGE, delta=delta)
+
+    _, keep = step()
+    return step, float(keep.float().mean())
+
+
+def run_reference(args, wl_name: str, wl: dict) -> dict:
+    """The reference arm: the CPU restatement of the reference algorithm on all host threads, on a
+    bounded sample (one sequence of the batch) of the workload."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    B_s = 1
+    T_s = min(wl["T"], 32768)
+    step, kept = oracle_step_fn(wl["kind"], B_s, T_s, wl["delta"], wl["fp8"], seed=1)
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    byt = algorithmic_bytes(wl["kind"], B_s, T_s, kept, paged=False)
+    value = byt / dt / 1e12
+    sample = f"B={B_s} of {wl['B']} sequences, T={T_s}, {steps} timed steps"
+    return {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
+        "config": {"workload": wl_name, "kept_fraction": kept, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="fp8fp8_b8_t32k", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--identity-table", action="store_true", help="identity block table instead of a permutation")
+    ap.add_argument("--pages-per-chunk", type=int, default=0)
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference(args, args.workload, wl)), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the product has no CPU path")
+    import torch.distributed as dist
+    from ffa_speedtest_b200 import quantize as Q
+    from ffa_speedtest_b200.decode import allocate_decode_workspace, decode_call
+    from ffa_speedtest_b200.synth import make_block_table, make_decode_inputs
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    kind, B, T, delta = wl["kind"], wl["B"], wl["T"], wl["delta"]
+    f8 = {"e5m2": torch.float8_e5m2, "e4m3": torch.float8_e4m3fn}[wl["fp8"]]
+    NP = T // PAGE
+    W = max(args.warmup, 3)
+
+    # ---- this rank's slice of the job: its own batch of B sequences, quantised on the GPU --------
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, D, seed=1 + rank, device=dev)
+    scale = zero = None
+    if kind == "fp8":
+        codes, res = Q.quantize_k_fp8_fp8_residual(k, f8)
+    elif kind == "q2":
+        codes, scale, zero, res = Q.quantize_k_2bit_fp8_residual(k, f8)
+    elif kind == "fp4":
+        codes, res = Q.encode_k_fp4_fp8_residual(k, f8)
+    elif kind == "nf4":
+        codes, scale, res = Q.encode_k_nf4_fp8_residual(k, f8)
+    else:
+        codes, scale, res = Q.encode_k_nvfp4_fp8_residual(k, f8, PAGE)
+    del k
+    # paged pool behind a seeded random permutation of pages
+    bt = make_block_table(B, NP, seed=7 + rank, identity=args.identity_table).to(dev)
+
+    def to_pool(x):
+        xp = x.reshape(B * NP, PAGE, *x.shape[2:])
+        pool = torch.empty_like(xp)
+        pool.view(torch.uint8 if x.dtype.itemsize == 1 else torch.int16)[bt.reshape(-1).long()] = \
+            xp.view(torch.uint8 if x.dtype.itemsize == 1 else torch.int16)
+        return pool
+
+    codes_p, res_p, v_p = to_pool(codes), to_pool(res), to_pool(v)
+    del codes, res, v
+    torch.cuda.empty_cache()
+
+    ws = allocate_decode_workspace(q, v_p, BS=PAGE, SBS=PAGE, seq_len=T, pages_per_chunk=args.pages_per_chunk)
+    q_dev = q.clone()
+
+    def step():
+        return decode_call(kind, q_dev, codes_p, v_p, k_scale=scale, k_zero=zero, k_residual=res_p, BS=PAGE, SBS=PAGE,
+                           delta=delta, block_table=bt, seq_len=T, workspace=ws,
+                           pages_per_chunk=args.pages_per_chunk)
+
+    step()
+    torch.cuda.synchronize()
+    kept = float(ws.mask.float().mean())
+    step_bytes = algorithmic_bytes(kind, B, T, kept, paged=True)
+
+    graph = None
+    if not args.no_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+    run = graph.replay if graph is not None else step
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed region: K steps, cache resident in HBM (inputs >> L2, no flush needed) ------
+    for _ in range(W):
+        run()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+
+    # ---- end-to-end: q from pinned host memory in, o back to host, through the public call -------
+    q_host = q.cpu().pin_memory()
+    o_host = torch.empty((B, HQ, D), dtype=q.dtype).pin_memory()
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        o = step() if graph is None else (graph.replay() or ws.o)
+        o_host.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # the caller needs o before the next token
+
+    for _ in range(W):
+        e2e_step()
+    barrier()
+    n_e2e = max(10, min(args.steps, 200))
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e, kept, step_bytes], dtype=torch.float64, device=dev)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms, ms_e2e = float(tmax[0]), float(tmax[1])
+        kept = float(tsum[2]) / world
+        job_bytes = float(tsum[3])
+    else:
+        job_bytes = step_bytes
+
+    if rank == 0:
+        per_step_s = ms / 1e3 / args.steps
+        value = job_bytes / per_step_s / 1e12
+        e2e_value = job_bytes / (ms_e2e / 1e3 / n_e2e) / 1e12
+        peak, peak_kind = peaks()
+        per_gpu_gbs = step_bytes / per_step_s / 1e9
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": W,
+            "ms_per_step": per_step_s * 1e3, "us_per_step": per_step_s * 1e6, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16xf16->f32 (fp8/bf16 storage)", "data": "synthetic",
+            "config": {
+                "workload": args.workload, "variant": kind + "fp8", "batch_per_gpu": B, "context": T, "q_heads": HQ,
+                "kv_heads": HKV, "head_dim": D, "page": PAGE, "delta": delta, "fp8": wl["fp8"], "v_dtype": "bf16",
+                "block_table": "identity" if args.identity_table else "seeded permutation",
+                "kept_fraction": kept, "algorithmic_bytes_per_step_per_gpu": step_bytes,
+                "cuda_graph": graph is not None, "l2": "inputs_larger_than_l2 (no flush)",
+                "sharding": "batch x kv-head units per rank, no collective",
+            },
+            "roofline": {
+                "bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
+                "peak_source": peak_kind, "traffic": None,
+                "note": "achieved = algorithmic bytes / whole step (stage-1 kernel + merge kernel)",
+            },
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": q_host.numel() * 2,
+                    "d2h_bytes_per_step": o_host.numel() * 2, "us_per_step": ms_e2e * 1e3 / n_e2e, "steps": n_e2e},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            cstep, ckept = oracle_step_fn(kind, 1, min(T, 32768), delta, wl["fp8"], seed=1)
+            cstep()
+            n_c = 3
+            t0 = time.perf_counter()
+            for _ in range(n_c):
+                cstep()
+            dt = (time.perf_counter() - t0) / n_c
+            cb = algorithmic_bytes(kind, 1, min(T, 32768), ckept, paged=False)
+            out["cpu_baseline"] = {"value": cb / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+                                   "sample": f"B=1 of {B} sequences, T={min(T, 32768)}, {n_c} timed steps",
+                                   "us_per_step": dt * 1e6}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

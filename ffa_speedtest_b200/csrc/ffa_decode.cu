@@ -81,14 +81,15 @@ struct Smem {
   static constexpr int kBaseSlot = kPage * Fmt<FMT>::kRow;
   static constexpr int kOffRv = kNB * kBaseSlot;
   static constexpr int kOffAux = kOffRv + kNR * kRvSlot;
-  // aux: xchg[2][2][4][8] f32 | pT[4][8][16] f16 | th[8] f32 | sS[128] | sZ[128] | book[16]
+  // aux: xchg[2][2][4][8] f32 | th[2][8] f32 | (q2, nf4 only) sS[128] | sZ[128] | book[16]
+  // kept small: the fp8 variant needs 2 x (112 KiB + aux + 1 KiB reserved) <= 228 KiB per SM
+  static constexpr bool kHasChannelScale = (FMT == FFA_K_Q2 || FMT == FFA_K_NF4);
   static constexpr int kOffXchg = kOffAux;
-  static constexpr int kOffPT = kOffXchg + 2 * 2 * 4 * 8 * 4;
-  static constexpr int kOffTh = kOffPT + 4 * 8 * 16 * 2;
+  static constexpr int kOffTh = kOffXchg + 2 * 2 * 4 * 8 * 4;
   static constexpr int kOffS = kOffTh + 2 * 8 * 4;
   static constexpr int kOffZ = kOffS + 128 * 4;
   static constexpr int kOffBook = kOffZ + 128 * 4;
-  static constexpr int kBytes = kOffBook + 16 * 4;
+  static constexpr int kBytes = kHasChannelScale ? kOffBook + 16 * 4 : kOffS;
   static_assert(kNR * kRvSlot >= kWarps * 8 * 128 * 4 + 256, "epilogue scratch must fit in the rv ring");
 };
 
@@ -234,7 +235,6 @@ __global__ void __launch_bounds__(kThreads) decode_stage1_kernel(const __grid_co
   const int h0 = 2 * t, h1 = 2 * t + 1;
 
   float* xchg = reinterpret_cast<float*>(smem + L::kOffXchg);       // [parity][kind][warp][head]
-  __half* pT = reinterpret_cast<__half*>(smem + L::kOffPT) + warp * 128;   // [head 8][token 16]
   float* sTh = reinterpret_cast<float*>(smem + L::kOffTh);          // [2][8]
   float* sS = reinterpret_cast<float*>(smem + L::kOffS);
   float* sZ = reinterpret_cast<float*>(smem + L::kOffZ);
@@ -416,14 +416,15 @@ __global__ void __launch_bounds__(kThreads) decode_stage1_kernel(const __grid_co
       const float p2 = s_ref[2] == -INFINITY ? 0.f : exp2f(s_ref[2] - rm0);
       const float p3 = s_ref[3] == -INFINITY ? 0.f : exp2f(s_ref[3] - rm1);
       const float l0 = p0 + p2, l1 = p1 + p3;
-      __syncwarp();
-      pT[h0 * 16 + g] = __float2half_rn(p0);
-      pT[h1 * 16 + g] = __float2half_rn(p1);
-      pT[h0 * 16 + g + 8] = __float2half_rn(p2);
-      pT[h1 * 16 + g + 8] = __float2half_rn(p3);
-      __syncwarp();
-      const uint32_t pb0 = *reinterpret_cast<const uint32_t*>(pT + g * 16 + 2 * t);
-      const uint32_t pb1 = *reinterpret_cast<const uint32_t*>(pT + g * 16 + 2 * t + 8);
+      // P^T fragment (B operand of O^T = V^T P^T): this lane needs tokens 2t, 2t+1, 2t+8, 2t+9 of
+      // head g; they live in lanes 8t + g/2 and 8t + 4 + g/2, in the half selected by g & 1.
+      const uint32_t pa = pack_h2(p0, p1), pb = pack_h2(p2, p3);
+      const int src = 8 * t + (g >> 1);
+      const uint32_t x0 = __shfl_sync(0xffffffffu, pa, src), x1 = __shfl_sync(0xffffffffu, pa, src + 4);
+      const uint32_t y0 = __shfl_sync(0xffffffffu, pb, src), y1 = __shfl_sync(0xffffffffu, pb, src + 4);
+      const uint32_t sel = (g & 1) ? 0x7632u : 0x5410u;
+      const uint32_t pb0 = __byte_perm(x0, x1, sel);
+      const uint32_t pb1 = __byte_perm(y0, y1, sel);
 
       const uint8_t* vt = smem + L::kOffRv + (r % L::kNR) * kRvSlot + kPage * kResRow;
       const int vrow = 16 * warp + (lane & 7) + ((lane >> 4) & 1) * 8;

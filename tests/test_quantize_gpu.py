@@ -1,0 +1,58 @@
+"""CUDA quantisers against the oracle (itself bit-exact with the reference): bit-exact."""
+import pytest
+import torch
+
+from oracle import ffa_oracle as fo
+from ffa_speedtest_b200 import quantize as Q
+from ffa_speedtest_b200.synth import make_decode_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def same(a: torch.Tensor, b: torch.Tensor) -> bool:
+    a, b = a.cpu().contiguous(), b.cpu().contiguous()
+    if a.dtype.itemsize == 1:
+        return torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    return torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+def make_k(dt, T=203):
+    _, k, _ = make_decode_inputs(2, T, 8, 2, 128, seed=5, dtype=dt, n_heavy=2)
+    k[:, :, 0, 5] = 0.75
+    k[:, :, 1, 9] = 0.0
+    # large but inside e4m3's finite range: overflow makes NaN codes whose sign bit differs between
+    # x86 and CUDA arithmetic (NaN propagation), which is not a property of the quantiser
+    k[0, 3, 0, 0] = 440.0
+    k[0, 4, 1, 1] = -300.0
+    return k.contiguous()
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("f8", [torch.float8_e5m2, torch.float8_e4m3fn])
+def test_all_quantisers_bit_exact(dt, f8):
+    k = make_k(dt)
+    kd = k.cuda()
+    for got, ref in zip(Q.quantize_k_2bit_fp8_residual(kd, f8), fo.quantize_q2(k, f8)):
+        assert same(got, ref)
+    for got, ref in zip(Q.quantize_k_fp8_fp8_residual(kd, f8), fo.quantize_fp8fp8(k, f8)):
+        assert same(got, ref)
+    for got, ref in zip(Q.encode_k_fp4_fp8_residual(kd, f8), fo.quantize_fp4(k, f8)):
+        assert same(got, ref)
+    for got, ref in zip(Q.encode_k_nf4_fp8_residual(kd, f8), fo.quantize_nf4(k, f8)):
+        assert same(got, ref)
+    for page in (64, 128):
+        for got, ref in zip(Q.encode_k_nvfp4_fp8_residual(kd, f8, page), fo.quantize_nvfp4(k, f8, page)):
+            assert same(got, ref)
+
+
+def test_large_shape_properties():
+    """Config-1-sized K (cut to B=2): idempotence of the fp8 base and residual bound."""
+    _, k, _ = make_decode_inputs(2, 32768, 32, 8, 128, seed=1, device="cuda")
+    base, res = Q.quantize_k_fp8_fp8_residual(k, torch.float8_e4m3fn)
+    assert torch.equal(base.view(torch.uint8), k.to(torch.float8_e4m3fn).view(torch.uint8))
+    recon = base.float() + res.float()
+    assert (recon - k.float()).abs().max().item() <= 2.0 ** -4 * k.float().abs().max().item() / 8
+    base2, res2 = Q.quantize_k_fp8_fp8_residual(base.to(k.dtype), torch.float8_e4m3fn)
+    assert torch.equal(base2.view(torch.uint8), base.view(torch.uint8)) and bool((res2.view(torch.uint8) & 0x7f == 0).all())
+    codes, scale, zero, r = Q.quantize_k_2bit_fp8_residual(k, torch.float8_e5m2)
+    assert torch.equal(zero, k.amin(dim=1)) and int(codes.max()) <= 255
