@@ -46,6 +46,7 @@ class FfaDecodeArgs(C.Structure):
         ("out", C.c_void_p), ("kept_mask", C.c_void_p), ("threshold_out", C.c_void_p), ("partial_out", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("pages_per_chunk", C.c_int32), ("reserved", C.c_int32),
+        ("kv_rows", C.c_int64),
     ]
 
 

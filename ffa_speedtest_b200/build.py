@@ -14,7 +14,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT = PKG / "libffa_b200.so"
-SOURCES = ["ffa_lib.cu", "ffa_decode.cu", "ffa_quantize.cu", "ffa_kproj.cu", "ffa_static.cu"]
+SOURCES = ["ffa_lib.cu", "ffa_decode.cu", "ffa_decode_tma.cu", "ffa_quantize.cu", "ffa_kproj.cu", "ffa_static.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--use_fast_math=false",

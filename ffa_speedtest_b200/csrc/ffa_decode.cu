@@ -20,58 +20,14 @@
 // tile in fp16; p = exp2(s - page max) is rounded to fp16 for the P*V product while its fp32 sum is
 // kept; V is converted to fp16; pages merge in order with the reference's stage-2 recurrence.
 
-#include "ffa_common.cuh"
+#include "ffa_decode_shared.cuh"
 
 namespace ffa {
 
 namespace {
 
-constexpr int kThreads = 128;
-constexpr int kWarps = 4;       // each warp owns 16 tokens of every page
-constexpr int kSample = 16;     // threshold sample width (T_BS in the reference)
-constexpr int kResRow = 128;    // fp8 residual bytes per token per head
-constexpr int kVRow = 256;      // V bytes per token per head (fp16 / bf16)
-constexpr int kRvSlot = kPage * (kResRow + kVRow);
-
-__constant__ float c_nf4_book[16] = {
-    -1.0f, -0.6961928009986877f, -0.5229921340942383f, -0.39491748809814453f,
-    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
-    0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
-    0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
-
-template <int FMT> struct Fmt;
-template <> struct Fmt<FFA_K_FP8>   { static constexpr int kRow = 128; };
-template <> struct Fmt<FFA_K_Q2>    { static constexpr int kRow = 32; };
-template <> struct Fmt<FFA_K_FP4>   { static constexpr int kRow = 64; };
-template <> struct Fmt<FFA_K_NF4>   { static constexpr int kRow = 64; };
-template <> struct Fmt<FFA_K_NVFP4> { static constexpr int kRow = 64; };
-
-struct DecodeParams {
-  const uint8_t* q;
-  const uint8_t* kc;
-  const void* ks;
-  const void* kz;
-  const uint8_t* kr;
-  const uint8_t* v;
-  const int32_t* bt;
-  const float* th_in;
-  float* part_m;     // [B*HQ, nch]
-  float* part_l;     // [B*HQ, nch]
-  float* part_o;     // [B*HQ, nch, 128]
-  int8_t* mask;      // [B, HKV, NTBS] or null
-  float* th_out;     // [B, HQ] or null
-  int bt_stride;
-  int B, T, HQ, HKV, G;
-  int NP;            // real pages = ceil(T/64)
-  int NTB;           // ceil(T/BS)
-  int NTBS;          // mask entries per (b, hkv)
-  int BS;
-  int ppc;           // pages per chunk
-  int nch;           // chunks per (b, hkv)
-  float sm_scale, delta;
-  int q_dtype, scale_dtype;
-  int use_res, v_bf16;
-};
+constexpr int kThreads = kDecodeThreads;
+constexpr int kWarps = kDecodeWarps;
 
 // Dynamic shared memory layout
 template <int FMT, int DA>
@@ -499,14 +455,23 @@ __global__ void __launch_bounds__(kThreads) decode_stage1_kernel(const __grid_co
 }
 
 // Stage 2: merge the chunk partials of one q head in chunk order; one thread per output channel.
+// `nch` is the stride of the partial arrays.  With wc == 0 every row has nch partials; with wc > 0
+// (page ranges of wc pages cut across the flattened (b, kv-head, page) space) a row's kv-head has
+// one partial per range that overlaps its NP pages.
 __global__ void __launch_bounds__(kHeadDim) decode_merge_kernel(const float* __restrict__ part_m,
                                                                 const float* __restrict__ part_l,
-                                                                const float* __restrict__ part_o, int nch, void* out,
-                                                                int out_dtype, float* partial_out) {
+                                                                const float* __restrict__ part_o, int nch, int wc,
+                                                                int NP, int G, void* out, int out_dtype,
+                                                                float* partial_out) {
   const int64_t row = blockIdx.x;
   const int c = threadIdx.x;
+  int count = nch;
+  if (wc > 0) {
+    const int64_t u0 = (row / G) * NP;
+    count = static_cast<int>((u0 + NP - 1) / wc - u0 / wc) + 1;
+  }
   float m = -INFINITY, acc = 0.f, o = 0.f;
-  for (int i = 0; i < nch; ++i) {
+  for (int i = 0; i < count; ++i) {
     const float mi = part_m[row * nch + i];
     const float li = part_l[row * nch + i];
     if (li == 0.f || mi == -INFINITY) continue;
@@ -598,10 +563,12 @@ extern "C" int ffa_decode_plan(int32_t B, int32_t T, int32_t HKV, int32_t ppc_in
 }
 
 extern "C" size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, int32_t HKV, int32_t ppc_in) {
-  int ppc = 0, nch = 0;
+  int ppc = 0, nch = 0, wc = 0, nch_tma = 0;
   if (ffa_decode_plan(B, T, HKV, ppc_in, &ppc, &nch) != FFA_OK) return 0;
+  decode_tma_plan(B, HKV, (T + kPage - 1) / kPage, ppc_in, &wc, &nch_tma);
+  if (nch_tma > nch) nch = nch_tma;            // either kernel may run: size for the larger plan
   const size_t rows = static_cast<size_t>(B) * HQ;
-  return align_up(rows * nch * sizeof(float), 256) * 2 + align_up(rows * nch * kHeadDim * sizeof(float), 256);
+  return align_up(rows * nch * sizeof(float), 256) * 2 + align_up(rows * nch * kHeadDim * sizeof(float), 256) + 256;
 }
 
 extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
@@ -641,18 +608,27 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   p.q_dtype = a->q_dtype; p.scale_dtype = a->scale_dtype;
   p.use_res = a->use_residual ? 1 : 0;
   p.v_bf16 = a->v_dtype == FFA_BF16 ? 1 : 0;
-  ffa_decode_plan(a->B, a->T, a->HKV, a->pages_per_chunk, &p.ppc, &p.nch);
+  const bool want_tma = (a->reserved & 1) == 0;          // reserved bit 0: force the fp16 path
+  const bool use_tma = want_tma && decode_tma_supported(p);
+  if (use_tma) decode_tma_plan(a->B, a->HKV, p.NP, a->pages_per_chunk, &p.ppc, &p.nch);
+  else ffa_decode_plan(a->B, a->T, a->HKV, a->pages_per_chunk, &p.ppc, &p.nch);
 
   const size_t rows = static_cast<size_t>(a->B) * a->HQ;
   const size_t ml = align_up(rows * p.nch * sizeof(float), 256);
-  const size_t need = ml * 2 + align_up(rows * p.nch * kHeadDim * sizeof(float), 256);
+  const size_t po = align_up(rows * p.nch * kHeadDim * sizeof(float), 256);
+  const size_t need = ml * 2 + po + 256;
   if (a->workspace_bytes < need) return FFA_E_WORKSPACE;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   p.part_m = reinterpret_cast<float*>(ws);
   p.part_l = reinterpret_cast<float*>(ws + ml);
   p.part_o = reinterpret_cast<float*>(ws + 2 * ml);
+  p.status = reinterpret_cast<int*>(ws + 2 * ml + po);
 
   int rc;
+  if (use_tma) {
+    const int64_t kv_rows = a->kv_rows > 0 ? a->kv_rows : static_cast<int64_t>(a->B) * a->T;
+    rc = launch_decode_tma(p, a->variant, a->fp8_format, kv_rows, stream);
+  } else
   switch (a->variant) {
     case FFA_K_FP8:   rc = launch_stage1_fmt<FFA_K_FP8>(p, a->fp8_format, stream); break;
     case FFA_K_Q2:    rc = launch_stage1_fmt<FFA_K_Q2>(p, a->fp8_format, stream); break;
@@ -662,8 +638,8 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
     default: return FFA_E_VARIANT;
   }
   if (rc != FFA_OK) return rc;
-  decode_merge_kernel<<<static_cast<unsigned>(rows), kHeadDim, 0, stream>>>(p.part_m, p.part_l, p.part_o, p.nch, a->out,
-                                                                             a->q_dtype, a->partial_out);
+  decode_merge_kernel<<<static_cast<unsigned>(rows), kHeadDim, 0, stream>>>(
+      p.part_m, p.part_l, p.part_o, p.nch, use_tma ? p.ppc : 0, p.NP, G, a->out, a->q_dtype, a->partial_out);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? FFA_OK : note_cuda_error(e, "decode_merge launch");
 }

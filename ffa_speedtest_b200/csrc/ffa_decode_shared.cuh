@@ -1,0 +1,67 @@
+// Declarations shared by the two decode kernels (ffa_decode.cu: fp16 tensor-core path fed by
+// cp.async; ffa_decode_tma.cu: fp8 tensor-core path fed by TMA).
+#pragma once
+
+#include "ffa_common.cuh"
+
+namespace ffa {
+
+constexpr int kDecodeThreads = 128;
+constexpr int kDecodeWarps = 4;   // each warp owns 16 tokens of every page
+constexpr int kSample = 16;       // threshold sample width (T_BS in the reference)
+constexpr int kResRow = 128;      // fp8 residual bytes per token per head
+constexpr int kVRow = 256;        // V bytes per token per head (fp16 / bf16)
+constexpr int kRvSlot = kPage * (kResRow + kVRow);
+
+static __constant__ float c_nf4_book[16] = {
+    -1.0f, -0.6961928009986877f, -0.5229921340942383f, -0.39491748809814453f,
+    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+    0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+    0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+
+template <int FMT> struct Fmt;
+template <> struct Fmt<FFA_K_FP8>   { static constexpr int kRow = 128; };
+template <> struct Fmt<FFA_K_Q2>    { static constexpr int kRow = 32; };
+template <> struct Fmt<FFA_K_FP4>   { static constexpr int kRow = 64; };
+template <> struct Fmt<FFA_K_NF4>   { static constexpr int kRow = 64; };
+template <> struct Fmt<FFA_K_NVFP4> { static constexpr int kRow = 64; };
+
+struct DecodeParams {
+  const uint8_t* q;
+  const uint8_t* kc;
+  const void* ks;
+  const void* kz;
+  const uint8_t* kr;
+  const uint8_t* v;
+  const int32_t* bt;
+  const float* th_in;
+  float* part_m;     // [B*HQ, nch]
+  float* part_l;     // [B*HQ, nch]
+  float* part_o;     // [B*HQ, nch, 128]
+  int8_t* mask;      // [B, HKV, NTBS] or null
+  float* th_out;     // [B, HQ] or null
+  int* status;       // device status word: set to 1 when a bounded wait gave up
+  int bt_stride;
+  int B, T, HQ, HKV, G;
+  int NP;            // real pages = ceil(T/64)
+  int NTB;           // ceil(T/BS)
+  int NTBS;          // mask entries per (b, hkv)
+  int BS;
+  int ppc;           // pages per chunk
+  int nch;           // chunks per (b, hkv)
+  float sm_scale, delta;
+  int q_dtype, scale_dtype;
+  int use_res, v_bf16;
+};
+
+
+// ffa_decode_tma.cu: returns FFA_OK after enqueueing stage 1, or a negative FFA_E_* code.
+// `kv_rows` is the number of token rows in the K/V tensors (B*T, or pages*64 for a pool).
+int launch_decode_tma(const DecodeParams& p, int variant, int f8, int64_t kv_rows, cudaStream_t stream);
+// Page ranges of the TMA kernel: `wc` pages per CTA over the flattened (b, kv-head, page) space
+// (about one CTA per resident slot: 2 per SM), `nch` = most partials any kv-head can receive.
+void decode_tma_plan(int B, int HKV, int NP, int wc_in, int* wc, int* nch);
+// true when the TMA path handles these arguments (bf16 q, driver entry point available)
+bool decode_tma_supported(const DecodeParams& p);
+
+}  // namespace ffa

@@ -1,0 +1,766 @@
+// FFA decode attention for B200, bf16-query fast path: TMA-fed shared-memory ring, fp8 tensor-core
+// tiles consumed without any per-element conversion.
+//
+// Same math and same reference semantics as ffa_decode.cu (coarse score -> page prune -> residual
+// refine -> online softmax * V; see the citations there), restructured around what bounds the
+// step on B200: the stream of K/V bytes from HBM.  The fp16 path spends ~1400 instructions per warp
+// per page, most of them address arithmetic for 16-byte copies and fp8->fp16 conversions; this
+// kernel removes both:
+//
+//   * One elected thread moves every tile with cp.async.bulk.tensor (TMA): the coarse tile of
+//     page j+3 is requested while page j is scored, residual + V of a page only after it survived
+//     the prune test.  Completion is tracked by mbarriers; tiles land 128B-swizzled so that the
+//     tensor-core fragment loads are bank-conflict free.
+//   * q is bf16 (8 significant bits).  Per head it is scaled by a power of two and split into two
+//     e4m3 "pieces" q*2^s = hi + lo/16, both exact.  The pieces sit on the N dimension of an
+//     m16n8k32 fp8 MMA whose A operand is the raw fp8 K bytes (e4m3 or e5m2), so
+//     acc_hi + acc_lo/16 = 2^s * (q . k) with every product exact and fp32 accumulation: the coarse
+//     score equals the reference's fp16 x fp16 -> fp32 dot up to summation order.
+//   * The refined score is (q . k_coarse) + (q . k_residual), the second dot again an fp8 MMA on
+//     the raw residual bytes.  The reference rounds (k_coarse + k_residual) to fp16 before its
+//     second dot; skipping that rounding changes a refined score by < 2^-11 of |q||k| (it cannot
+//     change the kept set, which only depends on the coarse scores).
+//   * P is rounded to fp16 like the reference, then split exactly into two bf16 pieces on the N
+//     dimension of a bf16 MMA whose A operand is V^T straight from ldmatrix - no V conversion.
+//
+// 2-bit / 4-bit coarse formats still dequantise their codes to fp16 for the coarse dot (their
+// values are not fp8 numbers) but share everything else.
+#include <cuda.h>
+
+#include "ffa_decode_shared.cuh"
+#include "ffa_numeric.h"
+
+namespace ffa {
+
+namespace {
+
+constexpr int kThreads = kDecodeThreads;
+constexpr int kWarps = kDecodeWarps;
+constexpr int kPB = 3;          // coarse tiles requested ahead of the page being scored
+constexpr int kDA = 2;          // pages between scoring a page and refining it
+constexpr int kNBase = kPB + 1;
+constexpr int kNRv = kDA + 1;
+constexpr int kSpinLimit = 1 << 22;   // bounded mbarrier wait (each try_wait blocks for a while itself)
+
+template <int FMT>
+struct SmemT {
+  static constexpr int kBaseSlot = kPage * Fmt<FMT>::kRow;            // 8 KiB / 2 KiB / 4 KiB
+  static constexpr int kOffRv = kNBase * kBaseSlot;
+  static constexpr int kOffAux = kOffRv + kNRv * kRvSlot;
+  static constexpr bool kHasChannelScale = (FMT == FFA_K_Q2 || FMT == FFA_K_NF4);
+  static constexpr int kOffBars = kOffAux;                              // (kNBase + kNRv) x 8 B
+  static constexpr int kOffXchg = kOffBars + 64;                        // [2][2][4][8] f32
+  static constexpr int kOffTh = kOffXchg + 512;                         // [2][8] f32
+  static constexpr int kOffQinv = kOffTh + 64;                          // [8] f32
+  static constexpr int kOffS = kOffQinv + 32;
+  static constexpr int kOffZ = kOffS + 512;
+  static constexpr int kOffBook = kOffZ + 512;
+  static constexpr int kBytes = (kHasChannelScale ? kOffBook + 64 : kOffS) + 1024;   // + alignment slack
+};
+
+struct ScaleCtx {
+  const float* sS;
+  const float* sZ;
+  const float* book;
+  float page_scale;
+};
+
+// ---- mbarrier / TMA primitives ------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; returns false if it gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// 2-D tiled TMA load: box -> shared memory, completion counted in bytes on `bar`.  x is the byte
+// offset inside a token row (a multiple of 16), y the token row.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// D(16x8,f32) += A(16x32, fp8 F8A, row) * B(32x8, e4m3, col)
+template <int F8A>
+__device__ __forceinline__ void mma_fp8(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  if (F8A == FFA_E4M3) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.f32.e5m2.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// raw fp8 bytes of rows (16*warp+g) and (+8) from a 128B-swizzled [64 x 128 B] tile: this thread's
+// channels are [32t, 32t+32), register r holding channels 32t+4r .. 32t+4r+3
+__device__ __forceinline__ void load_fp8_rows(uint32_t (&ra)[8], uint32_t (&rb)[8], const uint8_t* tile, int warp,
+                                              int g, int t) {
+  const uint8_t* rowA = tile + (16 * warp + g) * 128;
+  const uint8_t* rowB = rowA + 8 * 128;
+  const int c0 = ((2 * t) ^ g) * 16, c1 = ((2 * t + 1) ^ g) * 16;    // (row & 7) == g for both rows
+  const uint4 a0 = *reinterpret_cast<const uint4*>(rowA + c0);
+  const uint4 a1 = *reinterpret_cast<const uint4*>(rowA + c1);
+  const uint4 b0 = *reinterpret_cast<const uint4*>(rowB + c0);
+  const uint4 b1 = *reinterpret_cast<const uint4*>(rowB + c1);
+  ra[0] = a0.x; ra[1] = a0.y; ra[2] = a0.z; ra[3] = a0.w; ra[4] = a1.x; ra[5] = a1.y; ra[6] = a1.z; ra[7] = a1.w;
+  rb[0] = b0.x; rb[1] = b0.y; rb[2] = b0.z; rb[3] = b0.w; rb[4] = b1.x; rb[5] = b1.y; rb[6] = b1.z; rb[7] = b1.w;
+}
+
+// q . k for the warp's 16 tokens from raw fp8 K bytes and the e4m3 pieces of q.
+// out[nt][0] : token g, head 4nt+t;  out[nt][1] : token g+8, head 4nt+t   (unscaled dot products)
+template <int F8, int NT>
+__device__ __forceinline__ void dot_fp8(float (&out)[NT][2], const uint32_t (&qb)[NT][4][2], const float (&qinv)[NT],
+                                        const uint8_t* tile, int warp, int g, int t) {
+  uint32_t ra[8], rb[8];
+  load_fp8_rows(ra, rb, tile, warp, g, t);
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      if (s & 1) mma_fp8<F8>(acc1, ra[2 * s], rb[2 * s], ra[2 * s + 1], rb[2 * s + 1], qb[nt][s][0], qb[nt][s][1]);
+      else       mma_fp8<F8>(acc0, ra[2 * s], rb[2 * s], ra[2 * s + 1], rb[2 * s + 1], qb[nt][s][0], qb[nt][s][1]);
+    }
+    // columns 2t / 2t+1 hold the hi / lo piece of head 4nt+t; lo was stored times 16
+    out[nt][0] = ((acc0[0] + acc1[0]) + (acc0[1] + acc1[1]) * 0.0625f) * qinv[nt];
+    out[nt][1] = ((acc0[2] + acc1[2]) + (acc0[3] + acc1[3]) * 0.0625f) * qinv[nt];
+  }
+}
+
+// fp16 values of channels kb..kb+3 of one token row of a 2-bit / 4-bit coarse tile
+template <int FMT>
+__device__ __forceinline__ void coarse_pair16(uint32_t& lo, uint32_t& hi, const uint32_t (&r)[4], int s, int kb,
+                                              const ScaleCtx& sc) {
+  if (FMT == FFA_K_Q2) {
+    const uint32_t byte = (r[s >> 2] >> (8 * (s & 3))) & 0xffu;
+    const float4 S = *reinterpret_cast<const float4*>(sc.sS + kb);
+    const float4 Z = *reinterpret_cast<const float4*>(sc.sZ + kb);
+    lo = pack_h2(fmaf(static_cast<float>(byte & 3u), S.x, Z.x), fmaf(static_cast<float>((byte >> 2) & 3u), S.y, Z.y));
+    hi = pack_h2(fmaf(static_cast<float>((byte >> 4) & 3u), S.z, Z.z), fmaf(static_cast<float>(byte >> 6), S.w, Z.w));
+  } else {
+    const uint32_t two = (r[s >> 1] >> (16 * (s & 1))) & 0xffffu;
+    if (FMT == FFA_K_FP4) {
+      lo = e2m1x2_to_h2(two);
+      hi = e2m1x2_to_h2(two >> 8);
+    } else if (FMT == FFA_K_NVFP4) {
+      const float2 a = unpack_h2(e2m1x2_to_h2(two));
+      const float2 b = unpack_h2(e2m1x2_to_h2(two >> 8));
+      lo = pack_h2(a.x * sc.page_scale, a.y * sc.page_scale);
+      hi = pack_h2(b.x * sc.page_scale, b.y * sc.page_scale);
+    } else {
+      const float4 S = *reinterpret_cast<const float4*>(sc.sS + kb);
+      lo = pack_h2(sc.book[two & 15u] * S.x, sc.book[(two >> 4) & 15u] * S.y);
+      hi = pack_h2(sc.book[(two >> 8) & 15u] * S.z, sc.book[(two >> 12) & 15u] * S.w);
+    }
+  }
+}
+
+// q . k_coarse for 2-bit / 4-bit formats: codes -> fp16 -> m16n8k16 against fp16 q (odd columns 0)
+template <int FMT, int NT>
+__device__ __forceinline__ void dot_f16(float (&out)[NT][2], const uint32_t (&qh)[NT][8][2], const uint8_t* tile,
+                                        const ScaleCtx& sc, int warp, int g, int t) {
+  constexpr int ROW = Fmt<FMT>::kRow;
+  uint32_t ra[4], rb[4];
+  const uint8_t* rowA = tile + (16 * warp + g) * ROW;
+  const uint8_t* rowB = rowA + 8 * ROW;
+  if (FMT == FFA_K_Q2) {
+    const uint2 a = *reinterpret_cast<const uint2*>(rowA + 8 * t);
+    const uint2 b = *reinterpret_cast<const uint2*>(rowB + 8 * t);
+    ra[0] = a.x; ra[1] = a.y; rb[0] = b.x; rb[1] = b.y; ra[2] = ra[3] = rb[2] = rb[3] = 0;
+  } else {
+    const uint4 a = *reinterpret_cast<const uint4*>(rowA + 16 * t);
+    const uint4 b = *reinterpret_cast<const uint4*>(rowB + 16 * t);
+    ra[0] = a.x; ra[1] = a.y; ra[2] = a.z; ra[3] = a.w; rb[0] = b.x; rb[1] = b.y; rb[2] = b.z; rb[3] = b.w;
+  }
+  float acc[NT][2][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) { acc[nt][h][0] = acc[nt][h][1] = acc[nt][h][2] = acc[nt][h][3] = 0.f; }
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    const int kb = 32 * t + 4 * s;
+    uint32_t alo, ahi, blo, bhi;
+    coarse_pair16<FMT>(alo, ahi, ra, s, kb, sc);
+    coarse_pair16<FMT>(blo, bhi, rb, s, kb, sc);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mma_f16(acc[nt][s & 1], alo, blo, ahi, bhi, qh[nt][s][0], qh[nt][s][1]);
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    out[nt][0] = acc[nt][0][0] + acc[nt][1][0];
+    out[nt][1] = acc[nt][0][2] + acc[nt][1][2];
+  }
+}
+
+// two floats -> two e4m3 bytes (round to nearest even), first value in the low byte
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float a, float b) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;\n" : "=h"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t x) {
+  return unpack_h2(fp8x2_to_h2<FFA_E4M3>(x));
+}
+
+// One CTA walks a contiguous range of the flattened (batch x kv-head, page) space, `wc` pages
+// long; the part of the range inside one (b, kv-head) is a "segment" and produces one partial.
+template <int FMT, int F8, int NT, bool VBF>
+__global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_constant__ DecodeParams p,
+                                                              const __grid_constant__ CUtensorMap tm_c,
+                                                              const __grid_constant__ CUtensorMap tm_r,
+                                                              const __grid_constant__ CUtensorMap tm_v) {
+  using L = SmemT<FMT>;
+  constexpr int ROW = Fmt<FMT>::kRow;
+  constexpr bool kFp8Coarse = (FMT == FFA_K_FP8);
+  extern __shared__ uint8_t smem_raw[];
+  // 128B-swizzled TMA tiles need 1024-byte alignment
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int G = p.G, T = p.T;
+
+  const uint32_t bars = smem_u32(smem + L::kOffBars);          // [0,kNBase): coarse, then kNRv: res+V
+  float* xchg = reinterpret_cast<float*>(smem + L::kOffXchg);
+  float* sTh = reinterpret_cast<float*>(smem + L::kOffTh);
+  float* sQinv = reinterpret_cast<float*>(smem + L::kOffQinv);
+  float* sS = reinterpret_cast<float*>(smem + L::kOffS);
+  float* sZ = reinterpret_cast<float*>(smem + L::kOffZ);
+  float* sBook = reinterpret_cast<float*>(smem + L::kOffBook);
+  const bool use_res = p.use_res != 0;
+  const bool sampled = p.th_in == nullptr;
+  bool timed_out = false;
+
+  const int64_t total_pages = static_cast<int64_t>(p.B) * p.HKV * p.NP;
+  int64_t g0 = static_cast<int64_t>(blockIdx.x) * p.ppc;
+  const int64_t g1 = min(total_pages, g0 + p.ppc);
+
+  for (bool first = true; g0 < g1; first = false) {
+    // ---- segment geometry ------------------------------------------------------------------------
+    const int unit = static_cast<int>(g0 / p.NP);
+    const int b = unit / p.HKV, hkv = unit % p.HKV;
+    const int64_t unit0 = static_cast<int64_t>(unit) * p.NP;
+    const int page_begin = static_cast<int>(g0 - unit0);
+    const int n = static_cast<int>(min(g1 - g0, static_cast<int64_t>(p.NP - page_begin)));
+    const int part = static_cast<int>(g0 / p.ppc - unit0 / p.ppc);     // partial slot of this segment
+    g0 += n;
+
+    auto page_row0 = [&](int page) -> int {
+      return p.bt ? p.bt[static_cast<int64_t>(b) * p.bt_stride + page] * kPage : b * T + page * kPage;
+    };
+    // local page j lives in coarse slot (j + 2) % kNBase: slots 2 and 3 are free while slots 0 and
+    // 1 hold the two threshold samples, so the first two pages are requested at once
+    auto base_slot = [&](int j) -> int { return (j + 2) % kNBase; };
+    auto base_parity = [&](int j) -> uint32_t {
+      const int slot = base_slot(j);
+      return static_cast<uint32_t>((j + 2) / kNBase - ((slot < 2 && !sampled) ? 1 : 0)) & 1u;
+    };
+    auto issue_base = [&](int j) {
+      const int slot = base_slot(j);
+      mbar_expect_tx(bars + 8 * slot, L::kBaseSlot);
+      tma_load_2d(smem_u32(smem + slot * L::kBaseSlot), &tm_c, hkv * ROW, page_row0(page_begin + j), bars + 8 * slot);
+    };
+
+    if (!first) __syncthreads();        // the previous segment is done with shared memory
+    if (tid == 0) {
+#pragma unroll
+      for (int i = 0; i < kNBase + kNRv; ++i) {
+        if (!first) asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(bars + 8 * i) : "memory");
+        mbar_init(bars + 8 * i, 1);
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      // get the first tiles moving before anything else
+      if (sampled) {
+        const int tok1 = (p.NTB - 1) * kSample;
+        mbar_expect_tx(bars + 0, L::kBaseSlot);
+        tma_load_2d(smem_u32(smem), &tm_c, hkv * ROW, page_row0(0), bars + 0);
+        mbar_expect_tx(bars + 8, L::kBaseSlot);
+        tma_load_2d(smem_u32(smem + L::kBaseSlot), &tm_c, hkv * ROW, page_row0(tok1 / kPage), bars + 8);
+      }
+      for (int j = 0; j < 2 && j < n; ++j) issue_base(j);
+    }
+
+    if (L::kHasChannelScale) {
+      const int64_t o = (static_cast<int64_t>(b) * p.HKV + hkv) * kHeadDim + tid;
+      sS[tid] = load_as_float(p.ks, o, p.scale_dtype);
+      if (FMT == FFA_K_Q2) sZ[tid] = load_as_float(p.kz, o, p.scale_dtype);
+      if (FMT == FFA_K_NF4 && tid < 16) sBook[tid] = c_nf4_book[tid];
+    }
+    ScaleCtx sc{sS, sZ, sBook, 1.0f};
+    auto block_scale = [&](int blk) -> float {
+      return load_as_float(p.ks, (static_cast<int64_t>(b) * p.NTB + blk) * p.HKV + hkv, p.scale_dtype);
+    };
+
+    // ---- q operands (q is bf16 on this path) -------------------------------------------------------
+    // B-fragment column n = g of n-tile nt is head 4nt + g/2, piece g&1 (hi / lo x16) for the fp8
+    // MMAs, and (q as fp16 / zero) for the fp16 MMA of the 2-bit / 4-bit coarse formats.
+    uint32_t qb[NT][4][2];
+    uint32_t qh[kFp8Coarse ? 1 : NT][kFp8Coarse ? 1 : 8][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int hc = 4 * nt + (g >> 1);
+      const bool lo_piece = (g & 1) != 0;
+      uint32_t raw[16];                                       // 32 bf16 channels 32t .. 32t+31
+      if (hc < G) {
+        const uint4* src = reinterpret_cast<const uint4*>(
+            p.q + ((static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G + hc) * kHeadDim + 32 * t) * 2);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 v4 = src[i];
+          raw[4 * i] = v4.x; raw[4 * i + 1] = v4.y; raw[4 * i + 2] = v4.z; raw[4 * i + 3] = v4.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) raw[i] = 0u;
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        amax = fmaxf(amax, fabsf(__uint_as_float(raw[i] << 16)));
+        amax = fmaxf(amax, fabsf(__uint_as_float(raw[i] & 0xffff0000u)));
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      // power of two that brings the head's largest |q| into [128, 256)
+      int e = 0;
+      if (amax > 0.f && amax < INFINITY) e = 134 - static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);
+      e = max(-100, min(100, e));
+      const float up = __int_as_float((127 + e) << 23), down = __int_as_float((127 - e) << 23);
+      if (warp == 0 && t == 0 && !lo_piece) sQinv[hc] = down;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float x0 = __uint_as_float(raw[2 * r] << 16) * up, x1 = __uint_as_float(raw[2 * r] & 0xffff0000u) * up;
+        const float x2 = __uint_as_float(raw[2 * r + 1] << 16) * up, x3 = __uint_as_float(raw[2 * r + 1] & 0xffff0000u) * up;
+        const uint32_t h01 = f32x2_to_e4m3x2(x0, x1), h23 = f32x2_to_e4m3x2(x2, x3);
+        uint32_t w = h01 | (h23 << 16);
+        if (lo_piece) {
+          const float2 d01 = e4m3x2_to_f32x2(h01), d23 = e4m3x2_to_f32x2(h23);
+          w = f32x2_to_e4m3x2((x0 - d01.x) * 16.f, (x1 - d01.y) * 16.f) |
+              (f32x2_to_e4m3x2((x2 - d23.x) * 16.f, (x3 - d23.y) * 16.f) << 16);
+        }
+        qb[nt][r >> 1][r & 1] = w;                            // register r: channels 32t+4r .. +3
+      }
+      if (!kFp8Coarse) {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          // bf16 -> fp16 like the reference's q.to(float16)
+          qh[kFp8Coarse ? 0 : nt][kFp8Coarse ? 0 : s][0] = lo_piece ? 0u : bf16x2_to_h2(raw[2 * s]);
+          qh[kFp8Coarse ? 0 : nt][kFp8Coarse ? 0 : s][1] = lo_piece ? 0u : bf16x2_to_h2(raw[2 * s + 1]);
+        }
+      }
+    }
+    __syncthreads();
+    float qinv[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) qinv[nt] = sQinv[4 * nt + t];
+
+    // unscaled coarse dots of one tile -> [nt][token g / g+8]; `slice` selects which 16 rows
+    auto coarse_dots = [&](float (&out)[NT][2], const uint8_t* tile, int slice) {
+      if constexpr (kFp8Coarse) dot_fp8<F8, NT>(out, qb, qinv, tile, slice, g, t);
+      else dot_f16<FMT, NT>(out, qh, tile, sc, slice, g, t);
+    };
+    auto to_log2 = [&](float d) -> float { return (d * p.sm_scale) * kLog2e; };
+
+    // ---- prune thresholds (reference ...q2fp8.py:55-82) ---------------------------------------------
+    // Two 16-token samples of the coarse K: tokens [0,16) and [(NTB-1)*16, +16).
+    float th[NT];
+    if (!sampled) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int h = 4 * nt + t;
+        th[nt] = h < G ? p.th_in[static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G + h] : 0.f;
+      }
+    } else {
+      if (warp < 2) {
+        timed_out |= !mbar_wait(bars + 8 * warp, 0);
+        const int blk = warp == 0 ? 0 : p.NTB - 1;
+        const int tok0 = blk * kSample;
+        if (FMT == FFA_K_NVFP4) sc.page_scale = block_scale(blk);
+        float d[NT][2];
+        coarse_dots(d, smem + warp * L::kBaseSlot, (tok0 % kPage) / 16);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const float s0 = tok0 + g < T ? to_log2(d[nt][0]) : -INFINITY;
+          const float s1 = tok0 + g + 8 < T ? to_log2(d[nt][1]) : -INFINITY;
+          float mm = fmaxf(s0, s1);
+#pragma unroll
+          for (int off = 4; off < 32; off <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+          if (g == 0) sTh[warp * 8 + 4 * nt + t] = mm;
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) th[nt] = fmaxf(sTh[4 * nt + t], sTh[8 + 4 * nt + t]) - p.delta;
+    }
+    if (p.th_out && page_begin == 0 && warp == 0 && g == 0) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int h = 4 * nt + t;
+        if (h < G) p.th_out[static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G + h] = th[nt];
+      }
+    }
+
+    // ---- page pipeline -----------------------------------------------------------------------------
+    auto issue_rv = [&](int j) {
+      const int slot = j % kNRv;
+      const uint32_t bar = bars + 8 * (kNBase + slot);
+      const uint32_t dst = smem_u32(smem + L::kOffRv + slot * kRvSlot);
+      const int row = page_row0(page_begin + j);
+      mbar_expect_tx(bar, (use_res ? kPage * kResRow : 0) + kPage * kVRow);
+      if (use_res) tma_load_2d(dst, &tm_r, hkv * kResRow, row, bar);
+      tma_load_2d(dst + kPage * kResRow, &tm_v, hkv * kVRow, row, bar);
+      tma_load_2d(dst + kPage * kResRow + kPage * 128, &tm_v, hkv * kVRow + 128, row, bar);
+    };
+
+    float run_m[NT], run_l[NT], run_o[NT][8][2];
+    float hist[kDA][NT][2];          // unscaled coarse dots of the last kDA scored pages
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      run_m[nt] = -INFINITY;
+      run_l[nt] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) run_o[nt][i][0] = run_o[nt][i][1] = 0.f;
+#pragma unroll
+      for (int d = 0; d < kDA; ++d) hist[d][nt][0] = hist[d][nt][1] = 0.f;
+    }
+    uint32_t keepq = 0;
+    uint32_t rv_fills = 0;           // bit s: parity of the number of fills issued into res+V slot s
+
+    // (the __syncthreads after the sample scoring, or after the q set-up, orders every warp's reads
+    // of slots 0 and 1 before they are refilled)
+    if (tid == 0) {
+      for (int j = 2; j < kPB && j < n; ++j) issue_base(j);
+    }
+
+    for (int it = 0; it < n + kDA; ++it) {
+      const int j = it, r = it - kDA;
+      if (tid == 0 && j + kPB < n) issue_base(j + kPB);
+
+      const bool do_score = j < n;
+      const bool do_refine = r >= 0 && ((keepq >> (kDA - 1)) & 1u);
+      float cm[NT], rm[NT], dc[NT][2], sref[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) { cm[nt] = rm[nt] = -INFINITY; dc[nt][0] = dc[nt][1] = 0.f; sref[nt][0] = sref[nt][1] = 0.f; }
+
+      if (do_score) {
+        const int page = page_begin + j;
+        timed_out |= !mbar_wait(bars + 8 * base_slot(j), base_parity(j));
+        if (FMT == FFA_K_NVFP4) sc.page_scale = block_scale((page * kPage) / p.BS);
+        coarse_dots(dc, smem + base_slot(j) * L::kBaseSlot, warp);
+        const int tok = page * kPage + 16 * warp + g;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const float s0 = tok < T ? to_log2(dc[nt][0]) : -INFINITY;
+          const float s1 = tok + 8 < T ? to_log2(dc[nt][1]) : -INFINITY;
+          float mm = fmaxf(s0, s1);
+#pragma unroll
+          for (int off = 4; off < 32; off <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+          cm[nt] = mm;
+        }
+      }
+      if (do_refine) {
+        const int page = page_begin + r;
+        const uint8_t* slot = smem + L::kOffRv + (r % kNRv) * kRvSlot;
+        // the slot was filled once since the bit was last toggled (pruned pages issue no load)
+        timed_out |= !mbar_wait(bars + 8 * (kNBase + r % kNRv), ((rv_fills >> (r % kNRv)) & 1u) ^ 1u);
+        float dr[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) dr[nt][0] = dr[nt][1] = 0.f;
+        if (use_res) dot_fp8<F8, NT>(dr, qb, qinv, slot, warp, g, t);
+        const int tok = page * kPage + 16 * warp + g;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          sref[nt][0] = tok < T ? to_log2(hist[kDA - 1][nt][0] + dr[nt][0]) : -INFINITY;
+          sref[nt][1] = tok + 8 < T ? to_log2(hist[kDA - 1][nt][1] + dr[nt][1]) : -INFINITY;
+          float mm = fmaxf(sref[nt][0], sref[nt][1]);
+#pragma unroll
+          for (int off = 4; off < 32; off <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+          rm[nt] = mm;
+        }
+      }
+      // shift the history of coarse dots
+#pragma unroll
+      for (int d = kDA - 1; d > 0; --d)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) { hist[d][nt][0] = hist[d - 1][nt][0]; hist[d][nt][1] = hist[d - 1][nt][1]; }
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) { hist[0][nt][0] = dc[nt][0]; hist[0][nt][1] = dc[nt][1]; }
+
+      float* xb = xchg + (it & 1) * 64;
+      if (g == 0) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          xb[warp * 8 + 4 * nt + t] = cm[nt];
+          xb[32 + warp * 8 + 4 * nt + t] = rm[nt];
+        }
+      }
+      __syncthreads();
+      bool below = true;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int h = 4 * nt + t;
+        cm[nt] = fmaxf(fmaxf(xb[h], xb[8 + h]), fmaxf(xb[16 + h], xb[24 + h]));
+        rm[nt] = fmaxf(fmaxf(xb[32 + h], xb[40 + h]), fmaxf(xb[48 + h], xb[56 + h]));
+        below = below && (h >= G || cm[nt] < th[nt]);
+      }
+
+      bool keep = false;
+      if (do_score) {
+        keep = !__all_sync(0xffffffffu, below);     // pruned only if every head is strictly below
+        if (keep) rv_fills ^= 1u << (j % kNRv);
+        if (tid == 0) {
+          if (keep) issue_rv(j);
+          if (p.mask) p.mask[(static_cast<int64_t>(b) * p.HKV + hkv) * p.NTBS + page_begin + j] = keep ? 1 : 0;
+        }
+      }
+
+      if (do_refine) {
+        const int page = page_begin + r;
+        const uint8_t* vt = smem + L::kOffRv + (r % kNRv) * kRvSlot + kPage * kResRow;
+        const int vrow = 16 * warp + (lane & 7) + ((lane >> 4) & 1) * 8;
+        const int vsel = (lane >> 3) & 1;
+        const int valid = T - (page * kPage + 16 * warp);       // valid tokens in this warp's slice
+        const bool partial = (page + 1) * kPage > T;
+        uint32_t m01 = 0xffffffffu, m23 = 0xffffffffu;
+        if (partial) {
+          m01 = (2 * t < valid ? 0xffffu : 0u) | (2 * t + 1 < valid ? 0xffff0000u : 0u);
+          m23 = (2 * t + 8 < valid ? 0xffffu : 0u) | (2 * t + 9 < valid ? 0xffff0000u : 0u);
+        }
+        const int src = 8 * t + (g >> 1);
+        const uint32_t sel = (g & 1) ? 0x7632u : 0x5410u;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          // p = exp2(s - page max), fp32 sum, fp16 rounding for the P.V product (...q2fp8.py:123-131)
+          const float p0 = sref[nt][0] == -INFINITY ? 0.f : ex2_approx(sref[nt][0] - rm[nt]);
+          const float p1 = sref[nt][1] == -INFINITY ? 0.f : ex2_approx(sref[nt][1] - rm[nt]);
+          const float l = p0 + p1;
+          uint32_t w0, w1;
+          if (VBF) {
+            // fp16(p) = hi + lo exactly, both bf16
+            const float f0 = __half2float(__float2half_rn(p0)), f1 = __half2float(__float2half_rn(p1));
+            const __nv_bfloat16 h0 = __float2bfloat16_rn(f0), h1 = __float2bfloat16_rn(f1);
+            const __nv_bfloat16 l0 = __float2bfloat16_rn(f0 - __bfloat162float(h0));
+            const __nv_bfloat16 l1 = __float2bfloat16_rn(f1 - __bfloat162float(h1));
+            w0 = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l0)) << 16);
+            w1 = static_cast<uint32_t>(__bfloat16_as_ushort(h1)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l1)) << 16);
+          } else {
+            w0 = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(p0)));
+            w1 = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(p1)));
+          }
+          // P^T fragment: tokens 2t, 2t+1 (and +8) of column g = (head 4nt + g/2, piece g&1)
+          const uint32_t x0 = __shfl_sync(0xffffffffu, w0, src), x1 = __shfl_sync(0xffffffffu, w0, src + 4);
+          const uint32_t y0 = __shfl_sync(0xffffffffu, w1, src), y1 = __shfl_sync(0xffffffffu, w1, src + 4);
+          const uint32_t pb0 = __byte_perm(x0, x1, sel), pb1 = __byte_perm(y0, y1, sel);
+
+          // stage-2 recurrence in page order (...q2fp8.py:162-167)
+          const float nm = fmaxf(run_m[nt], rm[nt]);
+          const float rp = nm == -INFINITY ? 0.f : ex2_approx(run_m[nt] - nm);
+          const float rb = nm == -INFINITY ? 0.f : ex2_approx(rm[nt] - nm);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint32_t a[4];
+            const int ch = 2 * i + vsel;
+            ldmatrix_x4_trans(a, smem_u32(vt + (ch >> 3) * (kPage * 128) + vrow * 128 + (((ch & 7) ^ (vrow & 7)) * 16)));
+            if (partial) { a[0] &= m01; a[1] &= m01; a[2] &= m23; a[3] &= m23; }
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
+            if (VBF) mma_bf16(o, a[0], a[1], a[2], a[3], pb0, pb1);
+            else mma_f16(o, a[0], a[1], a[2], a[3], pb0, pb1);
+            run_o[nt][i][0] = run_o[nt][i][0] * rp + (o[0] + o[1]) * rb;
+            run_o[nt][i][1] = run_o[nt][i][1] * rp + (o[2] + o[3]) * rb;
+          }
+          run_l[nt] = run_l[nt] * rp + l * rb;
+          run_m[nt] = nm;
+        }
+      }
+      keepq = (keepq << 1) | (keep ? 1u : 0u);
+    }
+
+    // ---- segment epilogue: add the four warps' token slices and write one partial -------------------
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(smem + L::kOffRv);          // [warp][head 8][128]
+    float* lred = red + kWarps * 8 * 128;                              // [warp][8]
+    float* mred = lred + kWarps * 8;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      float l = run_l[nt];
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+      const int h = 4 * nt + t;
+      if (g == 0) lred[warp * 8 + h] = l;
+      if (warp == 0 && g == 0) mred[h] = run_m[nt];
+      float* w = red + warp * 1024 + h * 128;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        w[16 * i + g] = run_o[nt][i][0];
+        w[16 * i + g + 8] = run_o[nt][i][1];
+      }
+    }
+    __syncthreads();
+    const int64_t row0 = static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G;
+    for (int h = 0; h < G; ++h) {
+      const float o = red[h * 128 + tid] + red[1024 + h * 128 + tid] + red[2048 + h * 128 + tid] +
+                      red[3072 + h * 128 + tid];
+      p.part_o[((row0 + h) * p.nch + part) * kHeadDim + tid] = o;
+    }
+    if (tid < G) {
+      p.part_m[(row0 + tid) * p.nch + part] = mred[tid];
+      p.part_l[(row0 + tid) * p.nch + part] = lred[tid] + lred[8 + tid] + lred[16 + tid] + lred[24 + tid];
+    }
+    if (p.mask && page_begin + n == p.NP) {
+      for (int i = p.NP + tid; i < p.NTBS; i += kThreads)
+        p.mask[(static_cast<int64_t>(b) * p.HKV + hkv) * p.NTBS + i] = 0;
+    }
+  }
+  if (timed_out && p.status) atomicExch(p.status, 1);
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// [rows, HKV*row_bytes] bytes, box = 64 rows x box_bytes
+bool make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t row_bytes_all_heads, int box_bytes,
+              bool swizzle128) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes_all_heads), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes_all_heads)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes), static_cast<cuuint32_t>(kPage)};
+  const cuuint32_t estr[2] = {1, 1};
+  return encode_tiled_fn()(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int FMT, int F8, int NT, bool VBF>
+int launch_one(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
+               cudaStream_t stream) {
+  using L = SmemT<FMT>;
+  auto kern = decode_tma_kernel<FMT, F8, NT, VBF>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+    if (e != cudaSuccess) return note_cuda_error(e, "cudaFuncSetAttribute(decode_tma)");
+    configured[dev] = true;
+  }
+  const int64_t total_pages = static_cast<int64_t>(p.B) * p.HKV * p.NP;
+  const unsigned grid = static_cast<unsigned>((total_pages + p.ppc - 1) / p.ppc);
+  kern<<<grid, kThreads, L::kBytes, stream>>>(p, mc, mr, mv);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FFA_OK : note_cuda_error(e, "decode_tma launch");
+}
+
+template <int FMT, int F8>
+int launch_nt(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
+              cudaStream_t stream) {
+  if (p.G <= 4)
+    return p.v_bf16 ? launch_one<FMT, F8, 1, true>(p, mc, mr, mv, stream)
+                    : launch_one<FMT, F8, 1, false>(p, mc, mr, mv, stream);
+  return p.v_bf16 ? launch_one<FMT, F8, 2, true>(p, mc, mr, mv, stream)
+                  : launch_one<FMT, F8, 2, false>(p, mc, mr, mv, stream);
+}
+
+template <int FMT>
+int launch_fmt(const DecodeParams& p, int f8, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
+               cudaStream_t stream) {
+  return f8 == FFA_E4M3 ? launch_nt<FMT, FFA_E4M3>(p, mc, mr, mv, stream)
+                        : launch_nt<FMT, FFA_E5M2>(p, mc, mr, mv, stream);
+}
+
+}  // namespace
+
+void decode_tma_plan(int B, int HKV, int NP, int wc_in, int* wc_out, int* nch_out) {
+  static int sms = [] {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    return n;
+  }();
+  const long long total = static_cast<long long>(B) * HKV * NP;
+  long long wc = wc_in;
+  if (wc <= 0) {
+    wc = (total + 2LL * sms - 1) / (2LL * sms);       // two resident CTAs per SM, one wave
+    if (wc < 4) wc = 4;                               // a CTA's set-up is worth a few pages
+  }
+  if (wc > total) wc = total;
+  if (wc < 1) wc = 1;
+  *wc_out = static_cast<int>(wc);
+  *nch_out = static_cast<int>((NP + wc - 1) / wc) + 1;
+}
+
+bool decode_tma_supported(const DecodeParams& p) {
+  // two exact e4m3 pieces need a bf16 query; row indices are 32-bit TMA coordinates
+  return p.q_dtype == FFA_BF16 && encode_tiled_fn() != nullptr;
+}
+
+int launch_decode_tma(const DecodeParams& p, int variant, int f8, int64_t kv_rows, cudaStream_t stream) {
+  if (kv_rows <= 0 || kv_rows > 0x7fffffffLL) return FFA_E_LIMIT;
+  alignas(64) CUtensorMap mc, mr, mv;
+  const int row_c = variant == FFA_K_FP8 ? 128 : (variant == FFA_K_Q2 ? 32 : 64);
+  if (!make_map(&mc, p.kc, kv_rows, static_cast<int64_t>(p.HKV) * row_c, row_c, variant == FFA_K_FP8))
+    return FFA_E_LAUNCH;
+  // without a residual the map is never used; point it at the coarse tensor to keep it valid
+  if (!make_map(&mr, p.kr ? p.kr : p.kc, kv_rows, static_cast<int64_t>(p.HKV) * (p.kr ? kResRow : row_c),
+                p.kr ? kResRow : row_c, p.kr != nullptr))
+    return FFA_E_LAUNCH;
+  if (!make_map(&mv, p.v, kv_rows, static_cast<int64_t>(p.HKV) * kVRow, 128, true)) return FFA_E_LAUNCH;
+  switch (variant) {
+    case FFA_K_FP8:   return launch_fmt<FFA_K_FP8>(p, f8, mc, mr, mv, stream);
+    case FFA_K_Q2:    return launch_fmt<FFA_K_Q2>(p, f8, mc, mr, mv, stream);
+    case FFA_K_FP4:   return launch_fmt<FFA_K_FP4>(p, f8, mc, mr, mv, stream);
+    case FFA_K_NF4:   return launch_fmt<FFA_K_NF4>(p, f8, mc, mr, mv, stream);
+    case FFA_K_NVFP4: return launch_fmt<FFA_K_NVFP4>(p, f8, mc, mr, mv, stream);
+    default: return FFA_E_VARIANT;
+  }
+}
+
+}  // namespace ffa

@@ -34,10 +34,15 @@ class DecodeWorkspace:
         nbytes = _lib.lib().ffa_decode_workspace_bytes(B, T, HQ, HKV, pages_per_chunk)
         ntbs = -(-T // BS) * (BS // SBS)
         self.scratch = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        self.scratch[-256:].zero_()      # status word: kernels only ever set it
         self.o = torch.empty((B, HQ, V), dtype=dtype, device=device)
         self.mask = torch.empty((B, HKV, ntbs), dtype=torch.int8, device=device)
         self.threshold = torch.empty((B, HQ), dtype=torch.float32, device=device)
         self.pages_per_chunk = pages_per_chunk
+
+    def status(self) -> int:
+        """Device status word (synchronises): 0 = ok, 1 = a bounded wait inside a kernel gave up."""
+        return int(self.scratch[-256:-252].view(torch.int32).item())
 
 
 def allocate_decode_workspace(q, v, *, BS: int = 128, SBS: Optional[int] = None, seq_len: Optional[int] = None,
@@ -86,8 +91,15 @@ def decode_call(
     out: Optional[torch.Tensor] = None,
     partial_out: Optional[torch.Tensor] = None,
     pages_per_chunk: int = 0,
+    kernel: str = "auto",
 ):
-    """Shape bookkeeping shared by the five entry points; tensors are already type-checked."""
+    """Shape bookkeeping shared by the five entry points; tensors are already type-checked.
+
+    ``kernel``: "auto" picks the TMA / fp8 tensor-core kernel when q is bfloat16 and the fp16
+    tensor-core kernel otherwise; "fp16" forces the latter (it follows the reference's fp16
+    rounding of the refined K tile to the letter)."""
+    if kernel not in ("auto", "fp16"):
+        raise ValueError(f"kernel must be 'auto' or 'fp16', got {kernel!r}")
     B, Tq, HQ, K = q.shape
     HKV, V = v.shape[2], v.shape[3]
     if block_table is None:
@@ -166,6 +178,8 @@ def decode_call(
     a.workspace = workspace.scratch.data_ptr()
     a.workspace_bytes = workspace.scratch.numel()
     a.pages_per_chunk = pages_per_chunk
+    a.reserved = 1 if kernel == "fp16" else 0
+    a.kv_rows = k_codes.shape[0] * k_codes.shape[1]
     _lib.check(_lib.lib().ffa_decode(a, _lib.current_stream(q.device)), "ffa_decode")
 
     if return_skip_ratio:

@@ -30,6 +30,7 @@ def attn_forward_decode_fp4(
     out: torch.Tensor | None = None,
     partial_out: torch.Tensor | None = None,
     pages_per_chunk: int = 0,
+    kernel: str = "auto",
     **kwargs,
 ):
     check_common(q, k_fp4, v, k_residual, "attn_forward_decode_fp4")
@@ -49,4 +50,4 @@ def attn_forward_decode_fp4(
         "fp4", q, k_fp4, v, k_residual=k_residual, scale=scale, BS=BS, SBS=SBS, delta=delta,
         return_skip_ratio=return_skip_ratio, precomputed_threshold=precomputed_threshold,
         use_fp8_residual=use_fp8_residual, block_table=block_table, seq_len=seq_len, workspace=workspace, out=out,
-        partial_out=partial_out, pages_per_chunk=pages_per_chunk)
+        partial_out=partial_out, pages_per_chunk=pages_per_chunk, kernel=kernel)

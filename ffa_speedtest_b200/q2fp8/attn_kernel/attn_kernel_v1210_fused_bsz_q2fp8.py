@@ -49,6 +49,7 @@ def attn_forward_decode_quantized(
     out: torch.Tensor | None = None,
     partial_out: torch.Tensor | None = None,
     pages_per_chunk: int = 0,
+    kernel: str = "auto",
     **kwargs,
 ):
     check_common(q, k_q, v, k_residual, "attn_forward_decode_quantized")
@@ -75,4 +76,4 @@ def attn_forward_decode_quantized(
         "q2", q, k_q, v, k_scale=k_scale, k_zero=k_zero, k_residual=k_residual, scale=scale, BS=BS, SBS=SBS,
         delta=delta, return_skip_ratio=return_skip_ratio, precomputed_threshold=precomputed_threshold,
         use_fp8_residual=use_fp8_residual, block_table=block_table, seq_len=seq_len, workspace=workspace, out=out,
-        partial_out=partial_out, pages_per_chunk=pages_per_chunk)
+        partial_out=partial_out, pages_per_chunk=pages_per_chunk, kernel=kernel)

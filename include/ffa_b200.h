@@ -85,7 +85,9 @@ typedef struct FfaDecodeArgs {
   void* workspace;          /* >= ffa_decode_workspace_bytes(...) bytes, 256-byte aligned       */
   size_t workspace_bytes;
   int32_t pages_per_chunk;  /* 0 = choose automatically                                         */
-  int32_t reserved;
+  int32_t reserved;         /* bit 0: use the fp16 tensor-core kernel even when the TMA/fp8 kernel
+                               applies (bf16 q); 0 otherwise                                    */
+  int64_t kv_rows;          /* token rows in the K/V tensors: pages*64 of a pool, 0 = B*T       */
 } FfaDecodeArgs;
 
 /* Replaces attn_forward_decode_quantized / _fp8fp8 / _fp4 / _nf4 / _nvfp4fp8 after validation:

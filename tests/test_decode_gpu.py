@@ -55,9 +55,10 @@ def check_output(o_gpu, o_ref):
     return max_abs
 
 
+@pytest.mark.parametrize("kernel", ["auto", "fp16"])
 @pytest.mark.parametrize("kind", KINDS)
 @pytest.mark.parametrize("name", SMALL_CASES)
-def test_against_reference_goldens(kind, name):
+def test_against_reference_goldens(kind, name, kernel):
     """Same seeded inputs as the golden: kept set identical to the reference's (1e-3 band),
     output within the north-star tolerance of the reference's fp32 output."""
     from ffa_speedtest_b200.decode import allocate_decode_workspace
@@ -66,8 +67,9 @@ def test_against_reference_goldens(kind, name):
     ws = allocate_decode_workspace(c.q.cuda(), c.v.cuda(), BS=c.BS, SBS=c.SBS)
     th = None if c.th is None else c.th.cuda()
     o = call(kind, c.q, coarse, c.v, res, BS=c.BS, SBS=c.SBS, delta=c.delta, precomputed_threshold=th,
-             use_fp8_residual=c.use_res, workspace=ws)
+             use_fp8_residual=c.use_res, workspace=ws, kernel=kernel)
     torch.cuda.synchronize()
+    assert ws.status() == 0
     _, parts = fo.decode_attention(c.q, coarse, c.v, res, BS=c.BS, SBS=c.SBS, delta=c.delta,
                                    precomputed_threshold=c.th, use_fp8_residual=c.use_res, return_parts=True)
     torch.testing.assert_close(ws.threshold.cpu(), parts["threshold"], rtol=1e-5, atol=1e-4)
@@ -78,15 +80,18 @@ def test_against_reference_goldens(kind, name):
         assert err <= 4e-3 * max(1.0, c.o_ref.abs().max().item())
 
 
+@pytest.mark.parametrize("kernel", ["auto", "fp16"])
 @pytest.mark.parametrize("fp8", ["e5m2", "e4m3"])
-def test_config0_q2fp8(fp8):
+def test_config0_q2fp8(fp8, kernel):
     """BASELINE config 0: B=1, 32 q / 8 kv heads, T=4096, page 64, delta 8."""
     from ffa_speedtest_b200.decode import allocate_decode_workspace
     z = np.load(GOLDEN / f"decode_q2_config0_{fp8}.npz")
     q, k, v = make_decode_inputs(1, 4096, 32, 8, 128, seed=0, dtype=torch.bfloat16)
     coarse, res = fo.make_coarse("q2", k, FP8[fp8], 64)
     ws = allocate_decode_workspace(q.cuda(), v.cuda(), BS=64, SBS=64)
-    o, skip = call("q2", q, coarse, v, res, BS=64, SBS=64, delta=8.0, workspace=ws, return_skip_ratio=True)
+    o, skip = call("q2", q, coarse, v, res, BS=64, SBS=64, delta=8.0, workspace=ws, return_skip_ratio=True,
+                   kernel=kernel)
+    assert ws.status() == 0
     mask_ref = torch.from_numpy(z["mask"])
     _, parts = fo.decode_attention(q, coarse, v, res, BS=64, SBS=64, delta=8.0, return_parts=True)
     assert band_ok(ws.mask.cpu(), mask_ref, parts["block_max"], parts["threshold"], 4)
@@ -94,13 +99,14 @@ def test_config0_q2fp8(fp8):
     check_output(o, torch.from_numpy(z["o"]))
 
 
+@pytest.mark.parametrize("kernel", ["auto", "fp16"])
 @pytest.mark.parametrize("kind", KINDS)
-def test_paged_block_table_matches_contiguous(kind):
+def test_paged_block_table_matches_contiguous(kind, kernel):
     """A seeded random permutation of pages gives bit-identical results to the identity layout."""
     B, T, HQ, HKV = 2, 64 * 9 + 17, 8, 2
     q, k, v = make_decode_inputs(B, T, HQ, HKV, 128, seed=21, n_heavy=3)
     coarse, res = fo.make_coarse(kind, k, torch.float8_e4m3fn, 64)
-    kw = dict(BS=64, SBS=64, delta=4.5)
+    kw = dict(BS=64, SBS=64, delta=4.5, kernel=kernel)
     o_ref = call(kind, q, coarse, v, res, **kw).clone()
 
     NP = -(-T // 64)
@@ -130,16 +136,43 @@ def test_chunking_is_invariant(ppc):
     assert (o - base).abs().max().item() <= 1.0 / 128      # one bf16 ulp at |o| < 2
 
 
-@pytest.mark.parametrize("T", [1, 15, 16, 17, 63, 64, 65, 127, 129])
-def test_short_and_ragged_sequences(T):
+@pytest.mark.parametrize("kernel", ["auto", "fp16"])
+@pytest.mark.parametrize("T", [1, 15, 16, 17, 63, 64, 65, 127, 129, 257])
+def test_short_and_ragged_sequences(T, kernel):
     q, k, v = make_decode_inputs(2, T, 8, 2, 128, seed=30 + T, n_heavy=0)
     for kind in ("fp8", "q2", "nvfp4"):
         coarse, res = fo.make_coarse(kind, k, torch.float8_e5m2, 64)
         if kind == "nvfp4" and coarse.scale.shape[1] == coarse.scale.shape[2]:
             continue    # ambiguous scale shape, covered by test_nvfp4_square_scale_is_read_transposed
-        o = call(kind, q, coarse, v, res, BS=64, delta=3.0)
+        o = call(kind, q, coarse, v, res, BS=64, delta=3.0, kernel=kernel)
         ref = fo.decode_attention(q, coarse, v, res, BS=64, delta=3.0, out_dtype=torch.float32)
         check_output(o, ref)
+
+
+def test_garbage_beyond_the_sequence_is_ignored():
+    """Pool rows past seq_len (uninitialised memory in a real cache, here NaN patterns) must not
+    leak into the result."""
+    B, T, HQ, HKV = 2, 64 * 3 + 9, 8, 2
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, 128, seed=77, n_heavy=2)
+    for kind in ("fp8", "q2"):
+        coarse, res = fo.make_coarse(kind, k, torch.float8_e4m3fn, 64)
+        ref = fo.decode_attention(q, coarse, v, res, BS=64, delta=5.0, out_dtype=torch.float32)
+        NP = 4
+        bt = make_block_table(B, NP, seed=3)
+
+        def pool(x, fill):
+            xp = torch.nn.functional.pad(x.view(torch.uint8) if x.dtype.itemsize == 1 else x.view(torch.int16),
+                                         (0, 0, 0, 0, 0, NP * 64 - T), value=fill)
+            xp = xp.reshape(B * NP, 64, *xp.shape[2:])
+            out = torch.empty_like(xp)
+            out[bt.reshape(-1).long()] = xp
+            return out.view(x.dtype)
+
+        paged = fo.CoarseK(kind, pool(coarse.codes, 0x7f), coarse.scale, coarse.zero, 128)
+        for kernel in ("auto", "fp16"):
+            o = call(kind, q, paged, pool(v, 0x7fff), pool(res, 0x7f), block_table=bt.cuda(), seq_len=T, BS=64,
+                     delta=5.0, kernel=kernel)
+            check_output(o, ref)
 
 
 def test_nvfp4_square_scale_is_read_transposed():
