@@ -106,6 +106,21 @@ size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, int32_t HKV,
 int ffa_decode_plan(int32_t B, int32_t T, int32_t HKV, int32_t pages_per_chunk_in,
                     int32_t* pages_per_chunk, int32_t* n_chunks);
 
+/* Size of the scratch array built into the library for ffa_decode_static_scratch (4 MiB). */
+#define FFA_STATIC_SCRATCH_BYTES (4u << 20)
+size_t ffa_static_scratch_bytes(void);
+
+/* The same decode step as ffa_decode for callers that cannot allocate device memory (a plug-in in a
+ * host that owns and has already partitioned all of it, a loop where cudaMalloc is forbidden because
+ * it stalls the device).  No counterpart in the reference, which allocates its scratch tensors on
+ * every call.  args->workspace and args->workspace_bytes are ignored: the partial results go to an
+ * array of FFA_STATIC_SCRATCH_BYTES that is part of the library image on every GPU that loads it.
+ * Returns FFA_E_LIMIT, launching nothing, when ffa_decode_workspace_bytes(...) for the shape exceeds
+ * that size.  The first call on a device resolves the array's device address; make it outside any
+ * stream capture.  Calls on one device share the array: do not let two of them overlap on the GPU.
+ * Allocates nothing. */
+int ffa_decode_static_scratch(const FfaDecodeArgs* args, ffa_stream_t stream);
+
 /* Merge R partial results (split-KV inside a GPU, or one per rank after an all-gather):
  * parts is [R, rows, 129] fp32 holding a normalised partial output (128) followed by its
  * base-2 LSE (-inf when the part kept nothing).  out is [rows, 128] in out_dtype.
