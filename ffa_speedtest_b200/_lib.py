@@ -54,9 +54,9 @@ class FfaKprojArgs(C.Structure):
     _fields_ = [
         ("variant", C.c_int32),
         ("B", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("HKV", C.c_int32), ("head_dim", C.c_int32),
-        ("io_dtype", C.c_int32), ("fp8_format", C.c_int32), ("page_size", C.c_int32),
+        ("io_dtype", C.c_int32), ("rope_dtype", C.c_int32), ("fp8_format", C.c_int32), ("page_size", C.c_int32),
         ("h", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p),
-        ("slot_table", C.c_void_p),
+        ("slot_table", C.c_void_p), ("slot_stride", C.c_int32), ("reserved", C.c_int32),
         ("codes", C.c_void_p), ("scale", C.c_void_p), ("zero", C.c_void_p), ("residual", C.c_void_p),
         ("k_rope_out", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
@@ -96,11 +96,10 @@ def lib() -> C.CDLL:
     for name in ("ffa_quantize_q2", "ffa_quantize_fp8fp8", "ffa_quantize_fp4", "ffa_quantize_nf4",
                  "ffa_quantize_nvfp4"):
         getattr(L, name).restype = C.c_int
-    if hasattr(L, "ffa_kproj_rope"):
-        L.ffa_kproj_rope.argtypes = [C.POINTER(FfaKprojArgs), C.c_void_p]
-        L.ffa_kproj_rope.restype = C.c_int
-        L.ffa_kproj_workspace_bytes.argtypes = [i32, i32, i32, i32]
-        L.ffa_kproj_workspace_bytes.restype = C.c_size_t
+    L.ffa_kproj_rope.argtypes = [C.POINTER(FfaKprojArgs), C.c_void_p]
+    L.ffa_kproj_rope.restype = C.c_int
+    L.ffa_kproj_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    L.ffa_kproj_workspace_bytes.restype = C.c_size_t
     L.ffa_last_cuda_error.restype = C.c_char_p
     L.ffa_abi_version.restype = C.c_int
     _lib = L

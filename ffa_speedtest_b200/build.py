@@ -36,7 +36,8 @@ def up_to_date() -> bool:
     if not OUT.exists():
         return False
     t = OUT.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "ffa_b200.h"]
+    deps = (list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+            + [PKG.parent / "include" / "ffa_b200.h"])
     return all(d.stat().st_mtime <= t for d in deps)
 
 

@@ -1,0 +1,482 @@
+// Fused K projection + bias + RoPE for B200 (sm_100a), feeding the cache quantisers.
+//
+// Replaces the reference's Triton kernels _kproj_rope_minmax_kernel / _kproj_rope_quant_kernel
+// (ffa-q2fp8/fused_kproj_rope_q2fp8.py:103-399 and the fp4 / nf4 siblings), which run the GEMM in
+// 16x32x16 tiles with even and odd output columns as separate strided dots, and run it twice
+// for the formats whose scale needs the whole sequence.  Here:
+//
+//   K_lin[M, N] = h[M, H] . W_k[N, H]^T  (+ bias)       M = B*T tokens, N = HKV*128, H = hidden
+//
+// is ONE tcgen05 GEMM: 128x128 output tiles (one kv-head wide, so RoPE pairs stay inside a tile),
+// bf16/fp16 operands moved by TMA into a 6-stage 128B-swizzled shared-memory ring, a single
+// elected thread issuing tcgen05.mma (M=128, N=128, K=16) with the fp32 accumulator in tensor
+// memory, and four epilogue warps that read the accumulator back with tcgen05.ld (one token row
+// per thread), add the bias, round to the activation dtype like F.linear, apply RoPE with the
+// caller's cos/sin tables in the reference's op order (x*cos + rotate_half(x)*sin, pairs (2j,2j+1))
+// and write post-RoPE K.  The quantise-and-scatter pass (ffa_quantize.cu) then reads that K, which
+// at T = 8192 is 16-32 MB and still L2-resident.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
+// warps 2..5 = epilogue (TMEM lane quarter = warp % 4).  Every mbarrier wait is bounded.
+#include <cuda.h>
+
+#include "ffa_common.cuh"
+#include "ffa_numeric.h"
+
+namespace ffa {
+
+// defined in ffa_quantize.cu
+int quantize_dispatch(int variant, const void* k, int k_dtype, int B, int T, int HKV, int fp8, int page_size,
+                      uint8_t* codes, void* scale, void* zero, uint8_t* residual, void* scratch,
+                      const int32_t* slot_table, int slot_stride, cudaStream_t st);
+
+namespace {
+
+constexpr int kBM = 128, kBN = 128, kBK = 64;       // tile; kBK bf16 = one 128-byte swizzle row
+constexpr int kStages = 6;
+constexpr int kTileBytes = kBM * kBK * 2;           // 16 KiB (A) and 16 KiB (B) per stage
+constexpr int kThreadsK = 192;
+constexpr int kSpin = 1 << 22;
+constexpr int kTmemCols = 256;                      // two 128-column fp32 accumulators
+
+struct KprojParams {
+  const void* bias;      // [N] in io dtype or null
+  const void* cos;       // [T, 128]
+  const void* sin;
+  void* k_out;           // [M, N] post-RoPE K in out dtype
+  int* status;
+  int M, T, N, H;
+  float* partial;        // [n_split, M, N] fp32 when n_split > 1
+  int m_tiles, n_split;
+  int io_dtype;          // FFA_F16 | FFA_BF16: h, W, bias
+  int rope_dtype;        // dtype of cos/sin; the RoPE arithmetic and k_out use promote(io, rope)
+};
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int spin = 0; spin < kSpin; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major [rows x 64] 16-bit tile stored with the 128-byte
+// swizzle: rows are 128 B apart, groups of 8 rows 1024 B apart (stride byte offset), descriptor
+// version 1 (sm_100), layout type 2 (SWIZZLE_128B).  Advancing by UMMA_K = 16 elements inside the
+// swizzle row is +32 B on the start address.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);        // start address, 16-byte units
+  d |= static_cast<uint64_t>(1) << 16;                             // leading byte offset (unused here)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                     // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                             // descriptor version
+  d |= static_cast<uint64_t>(2) << 61;                             // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulate, A and B both K-major, 16-bit format
+// `fmt` (0 = fp16, 1 = bf16), N = 128, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t taddr) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// bias + rounding to the activation dtype + RoPE for 32 consecutive channels of one token row,
+// in the reference's op order; writes K in the promoted dtype.
+__device__ __forceinline__ void rope_store_32(const float (&acc)[32], const KprojParams& p, int64_t m, int n_base,
+                                              int ch0) {
+  const bool rope32 = p.rope_dtype == FFA_F32;
+  const int out_dt = rope32 ? FFA_F32 : p.io_dtype;
+  const int64_t tok = m % p.T;
+  float kx[32], cs[32], sn[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float x = acc[i];
+    if (p.bias) x = __fadd_rn(x, num::load_elem(p.bias, n_base + ch0 + i, p.io_dtype));
+    kx[i] = num::round_to(x, p.io_dtype);                  // F.linear returns the activation dtype
+  }
+  if (rope32) {
+    const float4* c4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.cos) + tok * kHeadDim + ch0);
+    const float4* s4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.sin) + tok * kHeadDim + ch0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 c = c4[i], s = s4[i];
+      cs[4 * i] = c.x; cs[4 * i + 1] = c.y; cs[4 * i + 2] = c.z; cs[4 * i + 3] = c.w;
+      sn[4 * i] = s.x; sn[4 * i + 1] = s.y; sn[4 * i + 2] = s.z; sn[4 * i + 3] = s.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      cs[i] = num::load_elem(p.cos, tok * kHeadDim + ch0 + i, p.rope_dtype);
+      sn[i] = num::load_elem(p.sin, tok * kHeadDim + ch0 + i, p.rope_dtype);
+    }
+  }
+  float out[32];
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    // (x * cos) + (rotate_half(x) * sin): three separately rounded ops in the promoted dtype
+    const float a0 = num::round_to(__fmul_rn(kx[i], cs[i]), out_dt);
+    const float a1 = num::round_to(__fmul_rn(kx[i + 1], cs[i + 1]), out_dt);
+    const float b0 = num::round_to(__fmul_rn(-kx[i + 1], sn[i]), out_dt);
+    const float b1 = num::round_to(__fmul_rn(kx[i], sn[i + 1]), out_dt);
+    out[i] = num::round_to(__fadd_rn(a0, b0), out_dt);
+    out[i + 1] = num::round_to(__fadd_rn(a1, b1), out_dt);
+  }
+  const int64_t o = m * p.N + n_base + ch0;
+  if (out_dt == FFA_F32) {
+    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.k_out) + o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dst[i] = make_float4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+  } else {
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.k_out) + o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = out[8 * i + 2 * j], hi = out[8 * i + 2 * j + 1];
+        const uint32_t l16 = out_dt == FFA_BF16 ? num::f32_to_bf16_bits(lo) : __half_as_ushort(__float2half_rn(lo));
+        const uint32_t h16 = out_dt == FFA_BF16 ? num::f32_to_bf16_bits(hi) : __half_as_ushort(__float2half_rn(hi));
+        w[j] = l16 | (h16 << 16);
+      }
+      dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+struct KSmem {
+  static constexpr int kOffA = 0;
+  static constexpr int kOffB = kStages * kTileBytes;
+  // full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  static constexpr int kOffBars = 2 * kStages * kTileBytes;
+  static constexpr int kOffTmem = kOffBars + (2 * kStages + 4) * 8;
+  static constexpr int kBytes = kOffTmem + 16 + 1024;            // + alignment slack
+};
+
+// Persistent kernel: work item w -> (m tile, n tile, k split); CTA c takes items c, c + grid, ...
+// With n_split == 1 the epilogue is fused (bias, rounding, RoPE, store K); with n_split > 1 (few
+// tokens: the GEMM is then a stream over W_k and needs more CTAs than output tiles) each item
+// stores its fp32 partial tile and kproj_finish_kernel adds the splits and applies the epilogue.
+__global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_constant__ KprojParams p,
+                                                               const __grid_constant__ CUtensorMap tm_a,
+                                                               const __grid_constant__ CUtensorMap tm_b) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bars = smem_u32(smem + KSmem::kOffBars);
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages;
+  const uint32_t bar_tfull = bars + 16 * kStages, bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + KSmem::kOffTmem);
+  const int n_tiles = p.N / kBN;
+  const int k_iters = p.H / kBK / p.n_split;                 // per work item
+  const int n_items = p.m_tiles * n_tiles * p.n_split;
+  bool timed_out = false;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) {   // one warp allocates two accumulators' worth of tensor-memory columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto decode_item = [&](int w, int& m0, int& n0, int& k0) {
+    const int split = w % p.n_split;
+    const int tile = w / p.n_split;
+    n0 = (tile % n_tiles) * kBN;
+    m0 = (tile / n_tiles) * kBM;
+    k0 = split * k_iters * kBK;
+  };
+
+  if (warp == 0) {
+    // ---- TMA producer ---------------------------------------------------------------------------
+    if (lane == 0) {
+      int it = 0;
+      for (int w = blockIdx.x; w < n_items; w += gridDim.x) {
+        int m0, n0, k0;
+        decode_item(w, m0, n0, k0);
+        for (int k = 0; k < k_iters; ++k, ++it) {
+          const int s = it % kStages;
+          if (it >= kStages) timed_out |= !mbar_wait(bar_empty + 8 * s, ((it / kStages) - 1) & 1);
+          mbar_expect_tx(bar_full + 8 * s, 2 * kTileBytes);
+          tma_load_2d(smem_u32(smem + KSmem::kOffA + s * kTileBytes), &tm_a, k0 + k * kBK, m0, bar_full + 8 * s);
+          tma_load_2d(smem_u32(smem + KSmem::kOffB + s * kTileBytes), &tm_b, k0 + k * kBK, n0, bar_full + 8 * s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -----------------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(p.io_dtype == FFA_BF16 ? 1u : 0u);
+      int it = 0, local = 0;
+      for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++local) {
+        const int buf = local & 1;
+        // the epilogue must have drained this accumulator (two items ago)
+        if (local >= 2) timed_out |= !mbar_wait(bar_tempty + 8 * buf, ((local >> 1) - 1) & 1);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t tmem_d = tmem_base + buf * kBN;
+        for (int k = 0; k < k_iters; ++k, ++it) {
+          const int s = it % kStages;
+          timed_out |= !mbar_wait(bar_full + 8 * s, (it / kStages) & 1);
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint64_t da = smem_desc_sw128(smem_u32(smem + KSmem::kOffA + s * kTileBytes));
+          const uint64_t db = smem_desc_sw128(smem_u32(smem + KSmem::kOffB + s * kTileBytes));
+#pragma unroll
+          for (int kk = 0; kk < kBK / 16; ++kk) umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+          umma_commit(bar_empty + 8 * s);        // frees the stage once these MMAs have read it
+        }
+        umma_commit(bar_tfull + 8 * buf);        // accumulator complete
+      }
+    }
+  } else {
+    // ---- epilogue: one token row per thread --------------------------------------------------------
+    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    const int row = 32 * q + lane;
+    int local = 0;
+    for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++local) {
+      int m0, n0, k0;
+      decode_item(w, m0, n0, k0);
+      const int buf = local & 1;
+      const int64_t m = static_cast<int64_t>(m0) + row;
+      timed_out |= !mbar_wait(bar_tfull + 8 * buf, (local >> 1) & 1);
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        float v[32];
+        tmem_ld32(v, tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * kBN + 32 * c);
+        if (c == kBN / 32 - 1) {
+          // everything is in registers: hand the accumulator back to the MMA warp
+          asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+          __syncwarp();
+          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_tempty + 8 * buf) : "memory");
+        }
+        if (m < p.M) {
+          if (p.n_split == 1) {
+            rope_store_32(v, p, m, n0, 32 * c);
+          } else {
+            const int split = w % p.n_split;
+            float4* dst = reinterpret_cast<float4*>(p.partial + (static_cast<int64_t>(split) * p.M + m) * p.N + n0 + 32 * c);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+  if (timed_out && p.status) atomicExch(p.status, 2);
+}
+
+// Adds the k-split partial tiles in split order and applies the epilogue; one thread per 32 channels.
+__global__ void __launch_bounds__(128) kproj_finish_kernel(const __grid_constant__ KprojParams p) {
+  const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int groups = p.N / 32;
+  if (idx >= static_cast<int64_t>(p.M) * groups) return;
+  const int64_t m = idx / groups;
+  const int n = static_cast<int>(idx % groups) * 32;
+  float acc[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+  for (int s = 0; s < p.n_split; ++s) {
+    const float4* src = reinterpret_cast<const float4*>(p.partial + (static_cast<int64_t>(s) * p.M + m) * p.N + n);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 x = src[i];
+      acc[4 * i] += x.x; acc[4 * i + 1] += x.y; acc[4 * i + 2] += x.z; acc[4 * i + 3] += x.w;
+    }
+  }
+  rope_store_32(acc, p, m, (n / kHeadDim) * kHeadDim, n % kHeadDim);
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// [rows, cols] 16-bit row-major, box = 128 rows x 64 columns, 128-byte swizzle
+bool make_operand_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {kBK, kBM};
+  const cuuint32_t estr[2] = {1, 1};
+  return encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+size_t elem_size(int dt) { return dt == FFA_F32 ? 4 : 2; }
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+constexpr size_t kPartialCap = 16u << 20;      // k-split partial tiles never take more than this
+constexpr int kFewTiles = 74;                  // below half the SMs' worth of tiles, split K
+
+int sm_count() {
+  static int sms = [] {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    return n;
+  }();
+  return sms;
+}
+
+// Number of k splits for an [M, N] output with k_total_iters 64-wide k steps.
+int plan_split(int64_t M, int N, int k_total_iters) {
+  const int64_t tiles = ((M + kBM - 1) / kBM) * (N / kBN);
+  if (tiles >= kFewTiles) return 1;
+  int64_t limit = sm_count() / tiles;
+  const int64_t by_mem = static_cast<int64_t>(kPartialCap / (static_cast<size_t>(M) * N * 4));
+  if (by_mem < limit) limit = by_mem;
+  if (limit > 16) limit = 16;
+  int split = 1;
+  while (split * 2 <= limit && k_total_iters % (split * 2) == 0) split *= 2;
+  return split;
+}
+
+size_t partial_reserve(int64_t M, int N) {
+  const int64_t tiles = ((M + kBM - 1) / kBM) * (N / kBN);
+  if (tiles >= kFewTiles) return 0;
+  const size_t full = static_cast<size_t>(16) * M * N * 4;
+  return align256(full < kPartialCap ? full : kPartialCap);
+}
+
+}  // namespace
+}  // namespace ffa
+
+using namespace ffa;
+
+extern "C" size_t ffa_kproj_workspace_bytes(int32_t B, int32_t T, int32_t HKV, int32_t rope_dtype) {
+  if (B <= 0 || T <= 0 || HKV <= 0) return 0;
+  const int64_t M = static_cast<int64_t>(B) * T;
+  const int N = HKV * kHeadDim;
+  const size_t k_bytes = static_cast<size_t>(M) * N * elem_size(rope_dtype == FFA_F32 ? FFA_F32 : FFA_BF16);
+  return align256(k_bytes) + align256(ffa_quantize_scratch_bytes(B, HKV)) + partial_reserve(M, N) + 256;
+}
+
+extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  if (!a || !a->h || !a->w || !a->cos || !a->sin) return FFA_E_NULL;
+  if (a->B <= 0 || a->T <= 0 || a->HKV <= 0 || a->H <= 0 || a->head_dim != kHeadDim) return FFA_E_SHAPE;
+  if (a->H % kBK != 0) return FFA_E_SHAPE;
+  if (a->io_dtype != FFA_F16 && a->io_dtype != FFA_BF16) return FFA_E_DTYPE;
+  if (a->rope_dtype != FFA_F32 && a->rope_dtype != a->io_dtype) return FFA_E_DTYPE;
+  if (!encode_fn()) return FFA_E_LAUNCH;
+  const int64_t M = static_cast<int64_t>(a->B) * a->T;
+  const int N = a->HKV * kHeadDim;
+  if (M > 0x7fffffffLL) return FFA_E_LIMIT;
+  const int out_dt = a->rope_dtype == FFA_F32 ? FFA_F32 : a->io_dtype;
+
+  // workspace: [post-RoPE K][quantiser min/max][k-split partial tiles][status]
+  const size_t k_bytes = align256(static_cast<size_t>(M) * N * elem_size(out_dt));
+  const size_t q_bytes = align256(ffa_quantize_scratch_bytes(a->B, a->HKV));
+  const size_t p_bytes = partial_reserve(M, N);
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  if (!ws || a->workspace_bytes < k_bytes + q_bytes + p_bytes + 256) return FFA_E_WORKSPACE;
+  void* k_rope = a->k_rope_out ? a->k_rope_out : static_cast<void*>(ws);
+  const bool need_quant = a->variant >= 0;
+
+  alignas(64) CUtensorMap ma, mb;
+  if (!make_operand_map(&ma, a->h, M, a->H) || !make_operand_map(&mb, a->w, N, a->H)) return FFA_E_LAUNCH;
+
+  KprojParams p{};
+  p.bias = a->bias; p.cos = a->cos; p.sin = a->sin; p.k_out = k_rope;
+  p.status = reinterpret_cast<int*>(ws + k_bytes + q_bytes + p_bytes);
+  p.partial = reinterpret_cast<float*>(ws + k_bytes + q_bytes);
+  p.M = static_cast<int>(M); p.T = a->T; p.N = N; p.H = a->H;
+  p.m_tiles = static_cast<int>((M + kBM - 1) / kBM);
+  p.n_split = plan_split(M, N, a->H / kBK);
+  p.io_dtype = a->io_dtype; p.rope_dtype = a->rope_dtype;
+
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kproj_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KSmem::kBytes);
+    if (e != cudaSuccess) return note_cuda_error(e, "cudaFuncSetAttribute(kproj_rope)");
+    configured[dev] = true;
+  }
+  const int64_t items = static_cast<int64_t>(p.m_tiles) * (N / kBN) * p.n_split;
+  const unsigned grid = static_cast<unsigned>(items < sm_count() ? items : sm_count());
+  kproj_rope_kernel<<<grid, kThreadsK, KSmem::kBytes, st>>>(p, ma, mb);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return note_cuda_error(e, "kproj_rope launch");
+  if (p.n_split > 1) {
+    const int64_t threads = M * (N / 32);
+    kproj_finish_kernel<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, st>>>(p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return note_cuda_error(e, "kproj_finish launch");
+  }
+  if (!need_quant) return FFA_OK;
+  return quantize_dispatch(a->variant, k_rope, out_dt, a->B, a->T, a->HKV, a->fp8_format, a->page_size,
+                           static_cast<uint8_t*>(a->codes), a->scale, a->zero, static_cast<uint8_t*>(a->residual),
+                           ws + k_bytes, a->slot_table, a->slot_stride, st);
+}

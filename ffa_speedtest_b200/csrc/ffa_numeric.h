@@ -205,8 +205,16 @@ FFA_HD uint32_t q2_encode(float k, float scale, float zero, int dt, int fp8, uin
 #endif
   c = c < 0.f ? 0.f : (c > 3.f ? 3.f : c);
   if (r != r) c = 0.f;
-  const float deq = c * scale + zero;
+  // product and sum round separately like the two torch ops (they only differ from a fused
+  // multiply-add when scale has more than 22 significant bits, i.e. for fp32 K)
+#if defined(__CUDA_ARCH__)
+  const float deq = __fadd_rn(__fmul_rn(c, scale), zero);
+  *res = f32_to_fp8(__fsub_rn(k, deq), fp8);
+#else
+  volatile float prod = c * scale;
+  const float deq = prod + zero;
   *res = f32_to_fp8(k - deq, fp8);
+#endif
   return static_cast<uint32_t>(c);
 }
 FFA_HD void fp8fp8_encode(float k, int fp8, uint8_t* base, uint8_t* res) {

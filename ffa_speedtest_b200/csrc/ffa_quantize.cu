@@ -25,6 +25,19 @@ __device__ __forceinline__ float ord_decode(uint32_t u) {
   return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
 }
 
+// Output token row of input row (b*T + t): identity, or through a slot table [B, stride] of page
+// ids (page = 64 tokens) when the codes are scattered straight into a paged cache.
+struct RowMap {
+  const int32_t* table;
+  int stride;
+  int T;
+  __device__ __forceinline__ int64_t operator()(int64_t row) const {
+    if (!table) return row;
+    const int64_t b = row / T, t = row % T;
+    return static_cast<int64_t>(table[b * stride + t / kPage]) * kPage + t % kPage;
+  }
+};
+
 // scratch: [B, HKV*128] x {min, max} as ordered uints
 __global__ void minmax_init_kernel(uint32_t* mm, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -68,7 +81,7 @@ __global__ void q2_finalize_kernel(const uint32_t* mm, int n, int dt, void* scal
 __global__ void __launch_bounds__(256) q2_encode_kernel(const void* __restrict__ k, int dt, int T, int row_elems,
                                                         int64_t n_quads, int fp8, const void* __restrict__ scale,
                                                         const void* __restrict__ zero, uint8_t* __restrict__ codes,
-                                                        uint8_t* __restrict__ res) {
+                                                        uint8_t* __restrict__ res, RowMap map) {
   const int quads_per_row = row_elems / 4;
   for (int64_t qd = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; qd < n_quads;
        qd += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -86,8 +99,9 @@ __global__ void __launch_bounds__(256) q2_encode_kernel(const void* __restrict__
                         &r) << (2 * j);
       r4 |= static_cast<uint32_t>(r) << (8 * j);
     }
-    codes[qd] = static_cast<uint8_t>(byte);
-    reinterpret_cast<uint32_t*>(res)[qd] = r4;
+    const int64_t oq = map(row) * quads_per_row + c / 4;
+    codes[oq] = static_cast<uint8_t>(byte);
+    reinterpret_cast<uint32_t*>(res)[oq] = r4;
   }
 }
 
@@ -95,7 +109,8 @@ __global__ void __launch_bounds__(256) q2_encode_kernel(const void* __restrict__
 template <int KIND>   // 0 fp8fp8, 1 fp4, 2 nf4
 __global__ void __launch_bounds__(256) quad_encode_kernel(const void* __restrict__ k, int dt, int T, int row_elems,
                                                           int64_t n_quads, int fp8, const uint32_t* __restrict__ mm,
-                                                          uint8_t* __restrict__ codes, uint8_t* __restrict__ res) {
+                                                          uint8_t* __restrict__ codes, uint8_t* __restrict__ res,
+                                                          RowMap map) {
   const int quads_per_row = row_elems / 4;
   for (int64_t qd = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; qd < n_quads;
        qd += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -120,9 +135,10 @@ __global__ void __launch_bounds__(256) quad_encode_kernel(const void* __restrict
       }
       r4 |= static_cast<uint32_t>(r) << (8 * j);
     }
-    if (KIND == 0) reinterpret_cast<uint32_t*>(codes)[qd] = c4;
-    else reinterpret_cast<uint16_t*>(codes)[qd] = static_cast<uint16_t>(c4);
-    reinterpret_cast<uint32_t*>(res)[qd] = r4;
+    const int64_t oq = map(row) * quads_per_row + c / 4;
+    if (KIND == 0) reinterpret_cast<uint32_t*>(codes)[oq] = c4;
+    else reinterpret_cast<uint16_t*>(codes)[oq] = static_cast<uint16_t>(c4);
+    reinterpret_cast<uint32_t*>(res)[oq] = r4;
   }
 }
 
@@ -134,7 +150,7 @@ __global__ void nf4_finalize_kernel(const uint32_t* mm, int n, int dt, void* sca
 // nvfp4: one block per (b, page, kv-head): absmax over page x 128, then encode
 __global__ void __launch_bounds__(256) nvfp4_kernel(const void* __restrict__ k, int dt, int T, int HKV, int page,
                                                     int fp8, uint8_t* __restrict__ codes, void* __restrict__ scale,
-                                                    uint8_t* __restrict__ res) {
+                                                    uint8_t* __restrict__ res, RowMap map) {
   const int pg = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int n_pages = gridDim.x;
   const int t0 = pg * page, t1 = min(T, t0 + page);
@@ -166,15 +182,16 @@ __global__ void __launch_bounds__(256) nvfp4_kernel(const void* __restrict__ k, 
     uint8_t r0, r1;
     const uint32_t lo = nvfp4_encode(load_elem(k, e, dt), s, dt, fp8, &r0);
     const uint32_t hi = nvfp4_encode(load_elem(k, e + 1, dt), s, dt, fp8, &r1);
-    codes[e / 2] = static_cast<uint8_t>(lo | (hi << 4));
-    reinterpret_cast<uint16_t*>(res)[e / 2] = static_cast<uint16_t>(r0 | (static_cast<uint32_t>(r1) << 8));
+    const int64_t oe = (map(static_cast<int64_t>(b) * T + t) * HKV + h) * D + c;
+    codes[oe / 2] = static_cast<uint8_t>(lo | (hi << 4));
+    reinterpret_cast<uint16_t*>(res)[oe / 2] = static_cast<uint16_t>(r0 | (static_cast<uint32_t>(r1) << 8));
   }
 }
 
 int check_common(const void* k, int dt, int B, int T, int HKV, int fp8) {
   if (!k) return FFA_E_NULL;
   if (B <= 0 || T <= 0 || HKV <= 0) return FFA_E_SHAPE;
-  if (dt != FFA_F16 && dt != FFA_BF16) return FFA_E_DTYPE;
+  if (dt != FFA_F16 && dt != FFA_BF16 && dt != FFA_F32) return FFA_E_DTYPE;
   if (fp8 != FFA_E5M2 && fp8 != FFA_E4M3) return FFA_E_DTYPE;
   return FFA_OK;
 }
@@ -201,7 +218,59 @@ void launch_minmax(bool abs_only, const void* k, int dt, int B, int T, int HKV, 
   else minmax_kernel<false><<<grid, 256, 0, st>>>(k, dt, T, row_elems, tpb, mm);
 }
 
+int quantize_impl(int variant, const void* k, int dt, int B, int T, int HKV, int fp8, int page_size, uint8_t* codes,
+                  void* scale, void* zero, uint8_t* residual, void* scratch, RowMap map, cudaStream_t st) {
+  int rc = check_common(k, dt, B, T, HKV, fp8);
+  if (rc) return rc;
+  if (!codes || !residual) return FFA_E_NULL;
+  const int row_elems = HKV * D, n = B * row_elems;
+  const int64_t n_quads = static_cast<int64_t>(B) * T * row_elems / 4;
+  uint32_t* mm = static_cast<uint32_t*>(scratch);
+  switch (variant) {
+    case FFA_K_Q2:
+      if (!scale || !zero || !scratch) return FFA_E_NULL;
+      launch_minmax(false, k, dt, B, T, HKV, mm, st);
+      q2_finalize_kernel<<<(n + 255) / 256, 256, 0, st>>>(mm, n, dt, scale, zero);
+      q2_encode_kernel<<<stream_grid(n_quads), 256, 0, st>>>(k, dt, T, row_elems, n_quads, fp8, scale, zero, codes,
+                                                             residual, map);
+      return last_launch("ffa_quantize_q2");
+    case FFA_K_FP8:
+      quad_encode_kernel<0><<<stream_grid(n_quads), 256, 0, st>>>(k, dt, T, row_elems, n_quads, fp8, nullptr, codes,
+                                                                  residual, map);
+      return last_launch("ffa_quantize_fp8fp8");
+    case FFA_K_FP4:
+      quad_encode_kernel<1><<<stream_grid(n_quads), 256, 0, st>>>(k, dt, T, row_elems, n_quads, fp8, nullptr, codes,
+                                                                  residual, map);
+      return last_launch("ffa_quantize_fp4");
+    case FFA_K_NF4:
+      if (!scale || !scratch) return FFA_E_NULL;
+      launch_minmax(true, k, dt, B, T, HKV, mm, st);
+      nf4_finalize_kernel<<<(n + 255) / 256, 256, 0, st>>>(mm, n, dt, scale);
+      quad_encode_kernel<2><<<stream_grid(n_quads), 256, 0, st>>>(k, dt, T, row_elems, n_quads, fp8, mm, codes, residual,
+                                                                  map);
+      return last_launch("ffa_quantize_nf4");
+    case FFA_K_NVFP4: {
+      if (!scale) return FFA_E_NULL;
+      if (page_size <= 0) return FFA_E_SHAPE;
+      if (HKV > 65535 || B > 65535) return FFA_E_LIMIT;
+      dim3 grid((T + page_size - 1) / page_size, HKV, B);
+      nvfp4_kernel<<<grid, 256, 0, st>>>(k, dt, T, HKV, page_size, fp8, codes, scale, residual, map);
+      return last_launch("ffa_quantize_nvfp4");
+    }
+    default:
+      return FFA_E_VARIANT;
+  }
+}
+
 }  // namespace
+
+int quantize_dispatch(int variant, const void* k, int k_dtype, int B, int T, int HKV, int fp8, int page_size,
+                      uint8_t* codes, void* scale, void* zero, uint8_t* residual, void* scratch,
+                      const int32_t* slot_table, int slot_stride, cudaStream_t st) {
+  return quantize_impl(variant, k, k_dtype, B, T, HKV, fp8, page_size, codes, scale, zero, residual, scratch,
+                       RowMap{slot_table, slot_stride, T}, st);
+}
+
 }  // namespace ffa
 
 using namespace ffa;
@@ -213,72 +282,32 @@ extern "C" size_t ffa_quantize_scratch_bytes(int32_t B, int32_t HKV) {
 
 extern "C" int ffa_quantize_q2(const void* k, int32_t dt, int32_t B, int32_t T, int32_t HKV, int32_t fp8,
                                uint8_t* codes, void* scale, void* zero, uint8_t* residual, void* scratch,
-                               ffa_stream_t stream_) {
-  int rc = check_common(k, dt, B, T, HKV, fp8);
-  if (rc) return rc;
-  if (!codes || !scale || !zero || !residual || !scratch) return FFA_E_NULL;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
-  uint32_t* mm = static_cast<uint32_t*>(scratch);
-  const int row_elems = HKV * D, n = B * row_elems;
-  launch_minmax(false, k, dt, B, T, HKV, mm, st);
-  q2_finalize_kernel<<<(n + 255) / 256, 256, 0, st>>>(mm, n, dt, scale, zero);
-  const int64_t n_quads = static_cast<int64_t>(B) * T * row_elems / 4;
-  q2_encode_kernel<<<stream_grid(n_quads), 256, 0, st>>>(k, dt, T, row_elems, n_quads, fp8, scale, zero, codes,
-                                                         residual);
-  return last_launch("ffa_quantize_q2");
+                               ffa_stream_t stream) {
+  return quantize_impl(FFA_K_Q2, k, dt, B, T, HKV, fp8, 0, codes, scale, zero, residual, scratch, RowMap{nullptr, 0, T},
+                       reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffa_quantize_fp8fp8(const void* k, int32_t dt, int32_t B, int32_t T, int32_t HKV, int32_t fp8,
-                                   uint8_t* base, uint8_t* residual, ffa_stream_t stream_) {
-  int rc = check_common(k, dt, B, T, HKV, fp8);
-  if (rc) return rc;
-  if (!base || !residual) return FFA_E_NULL;
-  const int row_elems = HKV * D;
-  const int64_t n_quads = static_cast<int64_t>(B) * T * row_elems / 4;
-  quad_encode_kernel<0><<<stream_grid(n_quads), 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
-      k, dt, T, row_elems, n_quads, fp8, nullptr, base, residual);
-  return last_launch("ffa_quantize_fp8fp8");
+                                   uint8_t* base, uint8_t* residual, ffa_stream_t stream) {
+  return quantize_impl(FFA_K_FP8, k, dt, B, T, HKV, fp8, 0, base, nullptr, nullptr, residual, nullptr,
+                       RowMap{nullptr, 0, T}, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffa_quantize_fp4(const void* k, int32_t dt, int32_t B, int32_t T, int32_t HKV, int32_t fp8,
-                                uint8_t* codes, uint8_t* residual, ffa_stream_t stream_) {
-  int rc = check_common(k, dt, B, T, HKV, fp8);
-  if (rc) return rc;
-  if (!codes || !residual) return FFA_E_NULL;
-  const int row_elems = HKV * D;
-  const int64_t n_quads = static_cast<int64_t>(B) * T * row_elems / 4;
-  quad_encode_kernel<1><<<stream_grid(n_quads), 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
-      k, dt, T, row_elems, n_quads, fp8, nullptr, codes, residual);
-  return last_launch("ffa_quantize_fp4");
+                                uint8_t* codes, uint8_t* residual, ffa_stream_t stream) {
+  return quantize_impl(FFA_K_FP4, k, dt, B, T, HKV, fp8, 0, codes, nullptr, nullptr, residual, nullptr,
+                       RowMap{nullptr, 0, T}, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffa_quantize_nf4(const void* k, int32_t dt, int32_t B, int32_t T, int32_t HKV, int32_t fp8,
-                                uint8_t* codes, void* scale, uint8_t* residual, void* scratch,
-                                ffa_stream_t stream_) {
-  int rc = check_common(k, dt, B, T, HKV, fp8);
-  if (rc) return rc;
-  if (!codes || !scale || !residual || !scratch) return FFA_E_NULL;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
-  uint32_t* mm = static_cast<uint32_t*>(scratch);
-  const int row_elems = HKV * D, n = B * row_elems;
-  launch_minmax(true, k, dt, B, T, HKV, mm, st);
-  nf4_finalize_kernel<<<(n + 255) / 256, 256, 0, st>>>(mm, n, dt, scale);
-  const int64_t n_quads = static_cast<int64_t>(B) * T * row_elems / 4;
-  quad_encode_kernel<2><<<stream_grid(n_quads), 256, 0, st>>>(k, dt, T, row_elems, n_quads, fp8, mm, codes, residual);
-  return last_launch("ffa_quantize_nf4");
+                                uint8_t* codes, void* scale, uint8_t* residual, void* scratch, ffa_stream_t stream) {
+  return quantize_impl(FFA_K_NF4, k, dt, B, T, HKV, fp8, 0, codes, scale, nullptr, residual, scratch,
+                       RowMap{nullptr, 0, T}, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffa_quantize_nvfp4(const void* k, int32_t dt, int32_t B, int32_t T, int32_t HKV, int32_t fp8,
                                   int32_t page_size, uint8_t* codes, void* scale, uint8_t* residual,
-                                  ffa_stream_t stream_) {
-  int rc = check_common(k, dt, B, T, HKV, fp8);
-  if (rc) return rc;
-  if (!codes || !scale || !residual) return FFA_E_NULL;
-  if (page_size <= 0) return FFA_E_SHAPE;
-  const int n_pages = (T + page_size - 1) / page_size;
-  if (HKV > 65535 || B > 65535) return FFA_E_LIMIT;
-  dim3 grid(n_pages, HKV, B);
-  nvfp4_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(k, dt, T, HKV, page_size, fp8, codes, scale,
-                                                                          residual);
-  return last_launch("ffa_quantize_nvfp4");
+                                  ffa_stream_t stream) {
+  return quantize_impl(FFA_K_NVFP4, k, dt, B, T, HKV, fp8, page_size, codes, scale, nullptr, residual, nullptr,
+                       RowMap{nullptr, 0, T}, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -27,8 +27,8 @@ def _prep(k: torch.Tensor, fp8_dtype: torch.dtype):
         raise ValueError("k must be a CUDA tensor (this build has no CPU path)")
     if k.dim() != 4 or k.shape[-1] != 128:
         raise ValueError(f"k must be [B, T, HKV, 128], got {tuple(k.shape)}")
-    if k.dtype not in (torch.float16, torch.bfloat16):
-        raise ValueError(f"k must be float16 or bfloat16, got {k.dtype}")
+    if k.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise ValueError(f"k must be float16, bfloat16 or float32, got {k.dtype}")
     k = k.contiguous()
     B, T, HKV, D = k.shape
     return k, B, T, HKV, _lib.float_code(k.dtype), _lib.fp8_code(fp8_dtype), _lib.current_stream(k.device)

@@ -63,16 +63,20 @@ class SequenceShardedDecode:
     caller).  ``step`` runs the local decode into a ``[B, HQ, 129]`` partial, all-gathers the
     partials over the process group (NCCL over NVLink for CUDA groups) and merges them."""
 
-    def __init__(self, group, B: int, HQ: int, device, out_dtype: torch.dtype):
+    def __init__(self, group, B: int, HQ: int, device, out_dtype: torch.dtype, merge_fn=None):
         import torch.distributed as dist
         self.dist, self.group = dist, group
         self.world = dist.get_world_size(group)
         self.local = torch.empty((B, HQ, 129), dtype=torch.float32, device=device)
         self.gathered = torch.empty((self.world, B, HQ, 129), dtype=torch.float32, device=device)
         self.out = torch.empty((B, HQ, 128), dtype=out_dtype, device=device)
+        # the CUDA merge kernel by default; CPU-rank tests of the protocol pass their own
+        self._merge = merge_fn or (lambda parts, out: merge_partials(parts, out.dtype, out=out))
 
     def step(self, local_decode) -> torch.Tensor:
-        """``local_decode(partial_out=...)`` must enqueue this rank's decode writing the partial."""
+        """``local_decode(partial_out=...)`` must enqueue this rank's decode writing the partial
+        ``[B, HQ, 129]`` (normalised output, base-2 LSE; LSE = -inf if the rank kept nothing)."""
         local_decode(partial_out=self.local)
-        self.dist.all_gather_into_tensor(self.gathered, self.local, group=self.group)
-        return merge_partials(self.gathered, self.out.dtype, out=self.out)
+        # rank r's partial lands in gathered[r]; the flat view is the form every backend accepts
+        self.dist.all_gather_into_tensor(self.gathered.view(-1, *self.local.shape[1:]), self.local, group=self.group)
+        return self._merge(self.gathered, self.out)

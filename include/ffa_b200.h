@@ -149,6 +149,45 @@ int ffa_quantize_nf4(const void* k, int32_t k_dtype, int32_t B, int32_t T, int32
 int ffa_quantize_nvfp4(const void* k, int32_t k_dtype, int32_t B, int32_t T, int32_t HKV, int32_t fp8_format,
                        int32_t page_size, uint8_t* codes, void* scale, uint8_t* residual, ffa_stream_t stream);
 
+/*
+ * Fused K projection + bias + RoPE (+ quantise and scatter into the cache).  Replaces
+ *   kproj_rope_quantize_{triton,fused}   ffa-q2fp8/fused_kproj_rope_q2fp8.py:427-566 (two GEMM passes there)
+ *   kproj_rope_fp4_{triton,fused}        ffa-fp4fp8/fused_kproj_rope_fp4fp8.py:415-522
+ *   kproj_rope_nf4_{triton,fused}        ffa-nf4fp8/fused_kproj_rope_nf4fp8.py:440-580
+ * and the fp8fp8 / nvfp4 variants whose "triton" path in the reference is a torch placeholder
+ * (ffa-fp8fp8/fused_kproj_rope_fp8fp8.py:92-113, ffa-nvfp4fp8/fused_kproj_rope_nvfp4fp8.py:143-166).
+ * K = rope(h . W_k^T + bias) is computed by one tcgen05 GEMM whose epilogue applies the bias, the
+ * rounding to the activation dtype and RoPE; the variant's quantiser then encodes K.
+ */
+typedef struct FfaKprojArgs {
+  int32_t variant;        /* FFA_K_* quantiser to run on K, or -1 to stop after RoPE               */
+  int32_t B, T, H, HKV;   /* h is [B, T, H]; H a multiple of 64                                    */
+  int32_t head_dim;       /* 128                                                                   */
+  int32_t io_dtype;       /* FFA_F16 | FFA_BF16: h, w_k, bias                                      */
+  int32_t rope_dtype;     /* FFA_F32 or io_dtype: cos / sin tables; K is produced in promote(io, rope) */
+  int32_t fp8_format;     /* FFA_E5M2 | FFA_E4M3                                                   */
+  int32_t page_size;      /* nvfp4 scale page                                                      */
+  const void* h;          /* [B*T, H]                                                              */
+  const void* w;          /* [HKV*128, H] (out, in), contiguous                                    */
+  const void* bias;       /* [HKV*128] or NULL                                                     */
+  const void* cos;        /* [T, 128]                                                              */
+  const void* sin;
+  const int32_t* slot_table; /* [B, slot_stride] page ids to scatter token rows into a paged cache, or NULL
+                                for the reference layout [B, T, HKV, .]                            */
+  int32_t slot_stride;
+  int32_t reserved;
+  void* codes;            /* outputs in the reference layouts (or pool layout with slot_table)     */
+  void* scale;
+  void* zero;
+  void* residual;
+  void* k_rope_out;       /* optional [B, T, HKV, 128] post-RoPE K in the promoted dtype           */
+  void* workspace;        /* >= ffa_kproj_workspace_bytes(...)                                     */
+  size_t workspace_bytes;
+} FfaKprojArgs;
+
+int ffa_kproj_rope(const FfaKprojArgs* args, ffa_stream_t stream);
+size_t ffa_kproj_workspace_bytes(int32_t B, int32_t T, int32_t HKV, int32_t rope_dtype);
+
 /* Text of the last CUDA runtime error seen by this library on the calling thread ("" if none). */
 const char* ffa_last_cuda_error(void);
 /* Library version, bumped when the ABI changes. */

@@ -1,0 +1,127 @@
+"""Fused K-projection + RoPE (tcgen05 GEMM) and the quantise/scatter pass behind it."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ffa_oracle as fo
+from tests.helpers import GOLDEN, KINDS
+from ffa_speedtest_b200 import kproj as KP
+from ffa_speedtest_b200.synth import make_block_table, make_kproj_inputs
+
+pytestmark = pytest.mark.gpu
+E4 = torch.float8_e4m3fn
+
+
+def status():
+    """Device status word of the last call: 0 unless a bounded wait inside the GEMM gave up."""
+    return int(KP.kproj_fused.last_workspace[-256:-252].view(torch.int32).item())
+
+
+def rope_tables(T, start, dtype=torch.float32):
+    cos, sin = fo.rope_tables(T + start, 128, base=500000.0)
+    return cos[start:].contiguous().to(dtype), sin[start:].contiguous().to(dtype)
+
+
+@pytest.mark.parametrize("T,H,HKV,B", [(1, 512, 2, 2), (70, 512, 2, 2), (300, 4096, 8, 1), (129, 1024, 1, 3)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rope32", [True, False])
+def test_post_rope_k_matches_torch(T, H, HKV, B, dtype, rope32):
+    """K = rope(h W^T + b): same op order and roundings as the reference recipe; only the GEMM's
+    accumulation order differs, which can flip the last bit of the 16-bit K_lin."""
+    h, w = make_kproj_inputs(T, H, HKV, 128, B=B, seed=40 + T, dtype=dtype)
+    w = w * 4.0
+    bias = (0.1 * torch.randn(HKV * 128, generator=torch.Generator().manual_seed(1))).to(dtype)
+    cos, sin = rope_tables(T, 7, torch.float32 if rope32 else dtype)
+    want = fo.kproj_rope(h, w, cos, sin, HKV, 128, bias=bias)
+    (got,) = KP.kproj_fused(None, h.cuda(), w.cuda(), cos.cuda(), sin.cuda(), HKV, 128, bias=bias.cuda())
+    assert status() == 0
+    assert got.dtype == want.dtype and got.shape == want.shape
+    err = (got.float().cpu() - want.float()).abs()
+    ulp = 2.0 ** (-7 if dtype == torch.bfloat16 else -10)
+    scale = want.float().abs().max().item()
+    assert err.max().item() <= 2.5 * ulp * scale, err.max().item()
+    assert err.mean().item() <= 0.05 * ulp * scale, err.mean().item()
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("T", [1, 70])
+def test_against_reference_goldens_with_its_smoke_tolerances(kind, T):
+    """Reference kproj_rope_*_reference outputs (CPU, bf16) vs the fused path, judged with the
+    reference's own smoke-test tolerances (ffa-q2fp8/fused_kproj_rope_q2fp8.py:606-615):
+    packed-byte mismatch <= 1 %, scale / zero max error <= 0.05, residual mean error <= 0.05."""
+    z = np.load(GOLDEN / f"kproj_{kind}_T{T}.npz")
+    B, T_, H, HKV, D, seed, start = (int(x) for x in z["meta"])
+    h, w = make_kproj_inputs(T_, H, HKV, D, B=B, seed=seed, dtype=torch.bfloat16)
+    w = w * 4.0
+    cos, sin = rope_tables(T_, start)
+    outs = KP.kproj_fused(kind, h.cuda(), w.cuda(), cos.cuda(), sin.cuda(), HKV, D, fp8_dtype=E4, page_size=64)
+    assert status() == 0
+    refs = [z[f"out{i}"] for i in range(len(outs))]
+    for i, (got, ref) in enumerate(zip(outs, refs)):
+        got = got.cpu()
+        last = i == len(outs) - 1
+        if last:                                    # fp8 residual
+            r = torch.from_numpy(ref).view(E4).float()
+            assert (got.float() - r).abs().mean().item() <= 0.05
+        elif i == 0:                                # packed codes (fp8 base for fp8fp8)
+            g = got.view(torch.uint8).numpy()
+            assert (g != ref).mean() <= 0.01, f"{(g != ref).mean():.4f} of packed bytes differ"
+        else:                                       # scales / zeros (fp32: the tables are fp32)
+            assert got.dtype == torch.float32
+            r = torch.from_numpy(ref.view(np.float32) if ref.dtype != np.float32 else ref)
+            assert (got - r).abs().max().item() <= 0.05
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_fused_equals_reference_recipe_given_same_k(kind):
+    """Quantising the K returned by the fused kernel with the standalone quantiser reproduces the
+    fused outputs bit for bit (the epilogue adds nothing of its own)."""
+    from ffa_speedtest_b200 import quantize as Q
+    T, H, HKV, B = 200, 1024, 2, 2
+    h, w = make_kproj_inputs(T, H, HKV, 128, B=B, seed=77, dtype=torch.bfloat16)
+    cos, sin = rope_tables(T, 3)
+    *outs, k = KP.kproj_fused(kind, h.cuda(), (w * 4).cuda(), cos.cuda(), sin.cuda(), HKV, 128, fp8_dtype=E4,
+                              return_k=True)
+    again = KP._QUANT[kind](k, E4, 64)
+    for a, b in zip(outs, again):
+        assert torch.equal(a.view(torch.uint8) if a.dtype.itemsize == 1 else a, b.view(torch.uint8) if b.dtype.itemsize == 1 else b)
+    ref = fo.QUANTIZERS[kind](k.cpu(), E4) if kind != "nvfp4" else fo.quantize_nvfp4(k.cpu(), E4, 64)
+    for a, b in zip(outs, ref):
+        a = a.cpu()
+        assert torch.equal(a.view(torch.uint8) if a.dtype.itemsize == 1 else a, b.view(torch.uint8) if b.dtype.itemsize == 1 else b)
+
+
+def test_scatter_into_paged_cache():
+    """Codes and residual written through a random slot table land where the decode kernel's
+    block table will look for them."""
+    T, H, HKV, B = 64 * 3 + 20, 512, 2, 2
+    h, w = make_kproj_inputs(T, H, HKV, 128, B=B, seed=5, dtype=torch.bfloat16)
+    cos, sin = rope_tables(T, 0)
+    args = (h.cuda(), (w * 4).cuda(), cos.cuda(), sin.cuda(), HKV, 128)
+    codes, res = KP.kproj_fused("fp8", *args, fp8_dtype=E4)
+    NP = 4
+    bt = make_block_table(B, NP, seed=9).cuda()
+    pool_c = torch.zeros(B * NP, 64, HKV, 128, dtype=torch.uint8, device="cuda")
+    pool_r = torch.zeros_like(pool_c)
+    KP.kproj_fused("fp8", *args, fp8_dtype=E4, block_table=bt, out=(pool_c, pool_r))
+    for b in range(B):
+        for pg in range(NP):
+            t0, t1 = pg * 64, min(T, pg * 64 + 64)
+            slot = int(bt[b, pg])
+            assert torch.equal(pool_c[slot, : t1 - t0], codes.view(torch.uint8)[b, t0:t1])
+            assert torch.equal(pool_r[slot, : t1 - t0], res.view(torch.uint8)[b, t0:t1])
+
+
+def test_large_tile_count_against_cublas():
+    """T = 8192 (BASELINE config 3): 512 output tiles; cuBLAS + eager RoPE on the same GPU as a
+    second opinion (not the oracle: its accumulation order is its own)."""
+    T, H, HKV = 8192, 4096, 8
+    h, w = make_kproj_inputs(T, H, HKV, 128, B=1, seed=3, device="cuda")
+    cos, sin = KP.build_rope_cache(T + 11, 128, base=500000.0, device="cuda")
+    cos, sin = cos[11:].contiguous(), sin[11:].contiguous()
+    (got,) = KP.kproj_fused(None, h, w, cos, sin, HKV, 128)
+    assert status() == 0
+    want = KP.apply_rope(torch.nn.functional.linear(h, w).view(1, T, HKV, 128), cos, sin)
+    err = (got - want).abs()
+    scale = want.abs().max().item()
+    assert err.max().item() <= 2.5 * 2.0 ** -7 * scale and err.mean().item() <= 0.05 * 2.0 ** -7 * scale

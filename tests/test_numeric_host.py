@@ -57,14 +57,19 @@ def test_round_to_dtype(host, code, dt):
 
 
 def _u16(t):
+    if t.dtype == torch.float32:
+        return t.view(torch.int32).numpy().view(np.uint32).ravel()
     return t.view(torch.int16).numpy().view(np.uint16).ravel()
 
 
-@pytest.mark.parametrize("dtc,dt", [(1, torch.bfloat16), (0, torch.float16)])
+@pytest.mark.parametrize("dtc,dt", [(1, torch.bfloat16), (0, torch.float16), (2, torch.float32)])
 @pytest.mark.parametrize("fmt,f8", [(0, torch.float8_e5m2), (1, torch.float8_e4m3fn)])
 def test_quantisers(host, dtc, dt, fmt, f8):
     B, T, HKV = 2, 203, 2
-    _, k, _ = make_decode_inputs(B, T, 8, HKV, 128, seed=5, dtype=dt, n_heavy=2)
+    _, k, _ = make_decode_inputs(B, T, 8, HKV, 128, seed=5, dtype=torch.bfloat16 if dt == torch.float32 else dt,
+                                 n_heavy=2)
+    if dt == torch.float32:
+        k = k.float() * 1.0009765625      # values that need more than 16 bits
     k[:, :, 0, 5] = 0.75          # constant channel: exercises the scale floor
     k[:, :, 1, 9] = 0.0
     k = k.contiguous()
@@ -75,7 +80,8 @@ def test_quantisers(host, dtc, dt, fmt, f8):
         return np.zeros(m, dtype=t)
 
     c, s, z, r = fo.quantize_q2(k, f8)
-    oc, os_, oz, orr = buf(n // 4), buf(B * HKV * 128, np.uint16), buf(B * HKV * 128, np.uint16), buf(n)
+    st = np.uint32 if dt == torch.float32 else np.uint16
+    oc, os_, oz, orr = buf(n // 4), buf(B * HKV * 128, st), buf(B * HKV * 128, st), buf(n)
     host.ffa_host_quantize_q2(kp, dtc, B, T, HKV, fmt, vp(oc.ctypes.data), vp(os_.ctypes.data), vp(oz.ctypes.data),
                               vp(orr.ctypes.data))
     assert np.array_equal(oc, c.numpy().ravel()) and np.array_equal(os_, _u16(s)) and np.array_equal(oz, _u16(z))
@@ -93,14 +99,14 @@ def test_quantisers(host, dtc, dt, fmt, f8):
     assert np.array_equal(oc, c.numpy().ravel()) and np.array_equal(orr, r.view(torch.uint8).numpy().ravel())
 
     c, s, r = fo.quantize_nf4(k, f8)
-    oc, os_, orr = buf(n // 2), buf(B * HKV * 128, np.uint16), buf(n)
+    oc, os_, orr = buf(n // 2), buf(B * HKV * 128, st), buf(n)
     host.ffa_host_quantize_nf4(kp, dtc, B, T, HKV, fmt, vp(oc.ctypes.data), vp(os_.ctypes.data), vp(orr.ctypes.data))
     assert np.array_equal(oc, c.numpy().ravel()) and np.array_equal(os_, _u16(s))
     assert np.array_equal(orr, r.view(torch.uint8).numpy().ravel())
 
     c, s, r = fo.quantize_nvfp4(k, f8, 64)
     npg = (T + 63) // 64
-    oc, os_, orr = buf(n // 2), buf(B * npg * HKV, np.uint16), buf(n)
+    oc, os_, orr = buf(n // 2), buf(B * npg * HKV, st), buf(n)
     host.ffa_host_quantize_nvfp4(kp, dtc, B, T, HKV, fmt, 64, vp(oc.ctypes.data), vp(os_.ctypes.data),
                                  vp(orr.ctypes.data))
     assert np.array_equal(oc, c.numpy().ravel()) and np.array_equal(os_, _u16(s))

@@ -13,6 +13,8 @@ def same(a: torch.Tensor, b: torch.Tensor) -> bool:
     a, b = a.cpu().contiguous(), b.cpu().contiguous()
     if a.dtype.itemsize == 1:
         return torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    if a.dtype.itemsize == 4:
+        return torch.equal(a.view(torch.int32), b.view(torch.int32))
     return torch.equal(a.view(torch.int16), b.view(torch.int16))
 
 
@@ -27,10 +29,11 @@ def make_k(dt, T=203):
     return k.contiguous()
 
 
-@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("f8", [torch.float8_e5m2, torch.float8_e4m3fn])
 def test_all_quantisers_bit_exact(dt, f8):
-    k = make_k(dt)
+    """float32 K is what the reference's kproj recipe produces when the RoPE tables are fp32."""
+    k = make_k(torch.bfloat16).float() * 1.0009765625 if dt == torch.float32 else make_k(dt)
     kd = k.cuda()
     for got, ref in zip(Q.quantize_k_2bit_fp8_residual(kd, f8), fo.quantize_q2(k, f8)):
         assert same(got, ref)
