@@ -49,6 +49,8 @@ WORKLOADS = {
 }
 HQ, HKV, D, PAGE = 32, 8, 128, 64
 CODE_BYTES = {"fp8": 128, "q2": 32, "fp4": 64, "nf4": 64, "nvfp4": 64}
+# dram__bytes_read+write / algorithmic bytes of the stage-1 kernel, from the committed ncu capture
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.02
 METRIC = "decode_attn_achieved_hbm_TBps"   # BASELINE metric: decode-attn us/step and achieved HBM TB/s
 UNIT = "TB/s"
 
@@ -328,8 +330,11 @@ def main():
             },
             "roofline": {
                 "bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
-                "peak_source": peak_kind, "traffic": None,
-                "note": "achieved = algorithmic bytes / whole step (stage-1 kernel + merge kernel)",
+                "peak_source": peak_kind, "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE * step_bytes,
+                "traffic_unit": "bytes per launch",
+                "note": "achieved = algorithmic bytes / whole step (stage-1 kernel + merge kernel); traffic = "
+                        "dram read+write of an ncu capture at B=2 scaled by the bytes processed "
+                        "(profiles/decode_tma_fp8fp8_b2_t32k.md)",
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": q_host.numel() * 2,
                     "d2h_bytes_per_step": o_host.numel() * 2, "us_per_step": ms_e2e * 1e3 / n_e2e, "steps": n_e2e},

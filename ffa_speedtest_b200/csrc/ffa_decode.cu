@@ -565,7 +565,7 @@ extern "C" int ffa_decode_plan(int32_t B, int32_t T, int32_t HKV, int32_t ppc_in
 extern "C" size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, int32_t HKV, int32_t ppc_in) {
   int ppc = 0, nch = 0, wc = 0, nch_tma = 0;
   if (ffa_decode_plan(B, T, HKV, ppc_in, &ppc, &nch) != FFA_OK) return 0;
-  decode_tma_plan(B, HKV, (T + kPage - 1) / kPage, ppc_in, &wc, &nch_tma);
+  decode_tma_plan(B, HKV, (T + kPage - 1) / kPage, ppc_in, 4, &wc, &nch_tma);   // 4 CTAs per SM at most
   if (nch_tma > nch) nch = nch_tma;            // either kernel may run: size for the larger plan
   const size_t rows = static_cast<size_t>(B) * HQ;
   return align_up(rows * nch * sizeof(float), 256) * 2 + align_up(rows * nch * kHeadDim * sizeof(float), 256) + 256;
@@ -609,8 +609,15 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   p.use_res = a->use_residual ? 1 : 0;
   p.v_bf16 = a->v_dtype == FFA_BF16 ? 1 : 0;
   const bool want_tma = (a->reserved & 1) == 0;          // reserved bit 0: force the fp16 path
+  // Refine lag (pages between scoring and refining): the fp8 format keeps 2 pages of residual+V in
+  // flight with 2 CTAs per SM; the 2-/4-bit formats spend more instructions per page on dequantising
+  // and gain more from a third resident CTA (lag 1, smaller ring).  reserved bits 4-5 override.
+  const int lag_override = (a->reserved >> 4) & 3;
+  p.refine_lag = lag_override ? (lag_override == 1 ? 1 : 2) : (a->variant == FFA_K_FP8 ? 2 : 1);
   const bool use_tma = want_tma && decode_tma_supported(p);
-  if (use_tma) decode_tma_plan(a->B, a->HKV, p.NP, a->pages_per_chunk, &p.ppc, &p.nch);
+  if (use_tma)
+    decode_tma_plan(a->B, a->HKV, p.NP, a->pages_per_chunk, decode_tma_residency(a->variant, p.refine_lag), &p.ppc,
+                    &p.nch);
   else ffa_decode_plan(a->B, a->T, a->HKV, a->pages_per_chunk, &p.ppc, &p.nch);
 
   const size_t rows = static_cast<size_t>(a->B) * a->HQ;

@@ -52,6 +52,7 @@ struct DecodeParams {
   float sm_scale, delta;
   int q_dtype, scale_dtype;
   int use_res, v_bf16;
+  int refine_lag;    // TMA kernel: pages between scoring and refining a page (1 or 2)
 };
 
 
@@ -60,7 +61,9 @@ struct DecodeParams {
 int launch_decode_tma(const DecodeParams& p, int variant, int f8, int64_t kv_rows, cudaStream_t stream);
 // Page ranges of the TMA kernel: `wc` pages per CTA over the flattened (b, kv-head, page) space
 // (about one CTA per resident slot: 2 per SM), `nch` = most partials any kv-head can receive.
-void decode_tma_plan(int B, int HKV, int NP, int wc_in, int* wc, int* nch);
+void decode_tma_plan(int B, int HKV, int NP, int wc_in, int ctas_per_sm, int* wc, int* nch);
+// resident CTAs per SM of the TMA kernel for a coarse format and refine lag
+int decode_tma_residency(int variant, int refine_lag);
 // true when the TMA path handles these arguments (bf16 q, driver entry point available)
 bool decode_tma_supported(const DecodeParams& p);
 

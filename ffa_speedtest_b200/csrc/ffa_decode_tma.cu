@@ -37,13 +37,13 @@ namespace {
 constexpr int kThreads = kDecodeThreads;
 constexpr int kWarps = kDecodeWarps;
 constexpr int kPB = 3;          // coarse tiles requested ahead of the page being scored
-constexpr int kDA = 2;          // pages between scoring a page and refining it
 constexpr int kNBase = kPB + 1;
-constexpr int kNRv = kDA + 1;
 constexpr int kSpinLimit = 1 << 22;   // bounded mbarrier wait (each try_wait blocks for a while itself)
 
-template <int FMT>
+// DA = pages between scoring a page and refining it; DA + 1 residual+V slots
+template <int FMT, int DA>
 struct SmemT {
+  static constexpr int kNRv = DA + 1;
   static constexpr int kBaseSlot = kPage * Fmt<FMT>::kRow;            // 8 KiB / 2 KiB / 4 KiB
   static constexpr int kOffRv = kNBase * kBaseSlot;
   static constexpr int kOffAux = kOffRv + kNRv * kRvSlot;
@@ -238,12 +238,13 @@ __device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t x) {
 
 // One CTA walks a contiguous range of the flattened (batch x kv-head, page) space, `wc` pages
 // long; the part of the range inside one (b, kv-head) is a "segment" and produces one partial.
-template <int FMT, int F8, int NT, bool VBF>
+template <int FMT, int F8, int NT, bool VBF, int kDA>
 __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_constant__ DecodeParams p,
                                                               const __grid_constant__ CUtensorMap tm_c,
                                                               const __grid_constant__ CUtensorMap tm_r,
                                                               const __grid_constant__ CUtensorMap tm_v) {
-  using L = SmemT<FMT>;
+  using L = SmemT<FMT, kDA>;
+  constexpr int kNRv = L::kNRv;
   constexpr int ROW = Fmt<FMT>::kRow;
   constexpr bool kFp8Coarse = (FMT == FFA_K_FP8);
   extern __shared__ uint8_t smem_raw[];
@@ -678,11 +679,11 @@ bool make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t row_bytes_
                            static_cast<CUtensorMapL2promotion>(promo), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int FMT, int F8, int NT, bool VBF>
+template <int FMT, int F8, int NT, bool VBF, int DA>
 int launch_one(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
                cudaStream_t stream) {
-  using L = SmemT<FMT>;
-  auto kern = decode_tma_kernel<FMT, F8, NT, VBF>;
+  using L = SmemT<FMT, DA>;
+  auto kern = decode_tma_kernel<FMT, F8, NT, VBF, DA>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -698,26 +699,29 @@ int launch_one(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& 
   return e == cudaSuccess ? FFA_OK : note_cuda_error(e, "decode_tma launch");
 }
 
-template <int FMT, int F8>
+template <int FMT, int F8, int DA>
 int launch_nt(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
               cudaStream_t stream) {
   if (p.G <= 4)
-    return p.v_bf16 ? launch_one<FMT, F8, 1, true>(p, mc, mr, mv, stream)
-                    : launch_one<FMT, F8, 1, false>(p, mc, mr, mv, stream);
-  return p.v_bf16 ? launch_one<FMT, F8, 2, true>(p, mc, mr, mv, stream)
-                  : launch_one<FMT, F8, 2, false>(p, mc, mr, mv, stream);
+    return p.v_bf16 ? launch_one<FMT, F8, 1, true, DA>(p, mc, mr, mv, stream)
+                    : launch_one<FMT, F8, 1, false, DA>(p, mc, mr, mv, stream);
+  return p.v_bf16 ? launch_one<FMT, F8, 2, true, DA>(p, mc, mr, mv, stream)
+                  : launch_one<FMT, F8, 2, false, DA>(p, mc, mr, mv, stream);
 }
 
 template <int FMT>
 int launch_fmt(const DecodeParams& p, int f8, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
                cudaStream_t stream) {
-  return f8 == FFA_E4M3 ? launch_nt<FMT, FFA_E4M3>(p, mc, mr, mv, stream)
-                        : launch_nt<FMT, FFA_E5M2>(p, mc, mr, mv, stream);
+  if (p.refine_lag == 1)
+    return f8 == FFA_E4M3 ? launch_nt<FMT, FFA_E4M3, 1>(p, mc, mr, mv, stream)
+                          : launch_nt<FMT, FFA_E5M2, 1>(p, mc, mr, mv, stream);
+  return f8 == FFA_E4M3 ? launch_nt<FMT, FFA_E4M3, 2>(p, mc, mr, mv, stream)
+                        : launch_nt<FMT, FFA_E5M2, 2>(p, mc, mr, mv, stream);
 }
 
 }  // namespace
 
-void decode_tma_plan(int B, int HKV, int NP, int wc_in, int* wc_out, int* nch_out) {
+void decode_tma_plan(int B, int HKV, int NP, int wc_in, int ctas_per_sm, int* wc_out, int* nch_out) {
   static int sms = [] {
     int dev = 0, n = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
@@ -728,13 +732,22 @@ void decode_tma_plan(int B, int HKV, int NP, int wc_in, int* wc_out, int* nch_ou
   const long long total = static_cast<long long>(B) * HKV * NP;
   long long wc = wc_in;
   if (wc <= 0) {
-    wc = (total + 2LL * sms - 1) / (2LL * sms);       // two resident CTAs per SM, one wave
+    const long long slots = static_cast<long long>(ctas_per_sm) * sms;   // resident CTAs: one wave
+    wc = (total + slots - 1) / slots;
     if (wc < 4) wc = 4;                               // a CTA's set-up is worth a few pages
   }
   if (wc > total) wc = total;
   if (wc < 1) wc = 1;
   *wc_out = static_cast<int>(wc);
   *nch_out = static_cast<int>((NP + wc - 1) / wc) + 1;
+}
+
+int decode_tma_residency(int variant, int refine_lag) {
+  // shared memory per CTA: 4 coarse slots + (lag + 1) x 24 KiB, out of 227 KiB per SM
+  const int base = (variant == FFA_K_FP8 ? 8 : (variant == FFA_K_Q2 ? 2 : 4)) * 1024 * kNBase;
+  const int bytes = base + (refine_lag + 1) * kRvSlot + 4096;
+  const int n = (227 * 1024) / bytes;
+  return n < 1 ? 1 : (n > 4 ? 4 : n);
 }
 
 bool decode_tma_supported(const DecodeParams& p) {
