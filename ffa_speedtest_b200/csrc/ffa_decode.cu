@@ -568,7 +568,8 @@ extern "C" size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, i
   decode_tma_plan(B, HKV, (T + kPage - 1) / kPage, ppc_in, 4, &wc, &nch_tma);   // 4 CTAs per SM at most
   if (nch_tma > nch) nch = nch_tma;            // either kernel may run: size for the larger plan
   const size_t rows = static_cast<size_t>(B) * HQ;
-  return align_up(rows * nch * sizeof(float), 256) * 2 + align_up(rows * nch * kHeadDim * sizeof(float), 256) + 256;
+  return kArrivalBytes + align_up(rows * nch * sizeof(float), 256) * 2 +
+         align_up(rows * nch * kHeadDim * sizeof(float), 256) + 256;
 }
 
 extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
@@ -623,13 +624,17 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   const size_t rows = static_cast<size_t>(a->B) * a->HQ;
   const size_t ml = align_up(rows * p.nch * sizeof(float), 256);
   const size_t po = align_up(rows * p.nch * kHeadDim * sizeof(float), 256);
-  const size_t need = ml * 2 + po + 256;
+  const size_t need = kArrivalBytes + ml * 2 + po + 256;
   if (a->workspace_bytes < need) return FFA_E_WORKSPACE;
+  if (static_cast<size_t>(a->B) * a->HKV * sizeof(int) > kArrivalBytes) return FFA_E_LIMIT;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
-  p.part_m = reinterpret_cast<float*>(ws);
-  p.part_l = reinterpret_cast<float*>(ws + ml);
-  p.part_o = reinterpret_cast<float*>(ws + 2 * ml);
-  p.status = reinterpret_cast<int*>(ws + 2 * ml + po);
+  p.arrivals = reinterpret_cast<int*>(ws);
+  p.part_m = reinterpret_cast<float*>(ws + kArrivalBytes);
+  p.part_l = reinterpret_cast<float*>(ws + kArrivalBytes + ml);
+  p.part_o = reinterpret_cast<float*>(ws + kArrivalBytes + 2 * ml);
+  p.status = reinterpret_cast<int*>(ws + kArrivalBytes + 2 * ml + po);
+  p.out = a->out;
+  p.partial_out = a->partial_out;
 
   int rc;
   if (use_tma) {
@@ -645,8 +650,9 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
     default: return FFA_E_VARIANT;
   }
   if (rc != FFA_OK) return rc;
+  if (use_tma) return FFA_OK;          // the last segment of every (b, kv-head) merged in-kernel
   decode_merge_kernel<<<static_cast<unsigned>(rows), kHeadDim, 0, stream>>>(
-      p.part_m, p.part_l, p.part_o, p.nch, use_tma ? p.ppc : 0, p.NP, G, a->out, a->q_dtype, a->partial_out);
+      p.part_m, p.part_l, p.part_o, p.nch, 0, p.NP, G, a->out, a->q_dtype, a->partial_out);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? FFA_OK : note_cuda_error(e, "decode_merge launch");
 }

@@ -12,6 +12,9 @@ constexpr int kSample = 16;       // threshold sample width (T_BS in the referen
 constexpr int kResRow = 128;      // fp8 residual bytes per token per head
 constexpr int kVRow = 256;        // V bytes per token per head (fp16 / bf16)
 constexpr int kRvSlot = kPage * (kResRow + kVRow);
+// The first kArrivalBytes of a decode workspace hold the per-(b, kv-head) arrival counters of the TMA
+// kernel.  They must be zero before the first launch; every launch leaves them zero again.
+constexpr int kArrivalBytes = 64 * 1024;
 
 static __constant__ float c_nf4_book[16] = {
     -1.0f, -0.6961928009986877f, -0.5229921340942383f, -0.39491748809814453f,
@@ -41,6 +44,9 @@ struct DecodeParams {
   int8_t* mask;      // [B, HKV, NTBS] or null
   float* th_out;     // [B, HQ] or null
   int* status;       // device status word: set to 1 when a bounded wait gave up
+  int* arrivals;     // TMA kernel: per-(b, kv-head) count of finished segments; zero between launches
+  void* out;         // TMA kernel: final output [B*HQ, 128] in q_dtype (the last segment merges)
+  float* partial_out;  // optional [B*HQ, 129]
   int bt_stride;
   int B, T, HQ, HKV, G;
   int NP;            // real pages = ceil(T/64)

@@ -645,6 +645,74 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       for (int i = p.NP + tid; i < p.NTBS; i += kThreads)
         p.mask[(static_cast<int64_t>(b) * p.HKV + hkv) * p.NTBS + i] = 0;
     }
+
+    // ---- merge by the last segment of this (b, kv-head) to finish (stage 2, ...q2fp8.py:142-171) -----
+    // Every segment publishes its partial, then bumps the unit's arrival counter; whoever sees all the
+    // others already there merges the partials in page order and resets the counter for the next launch.
+    const int n_seg = static_cast<int>((unit0 + p.NP - 1) / p.ppc - unit0 / p.ppc) + 1;
+    int* s_flag = reinterpret_cast<int*>(mred + 8);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int prev = atomicAdd(p.arrivals + unit, 1);
+      *s_flag = (prev == n_seg - 1);
+      if (prev == n_seg - 1) p.arrivals[unit] = 0;
+    }
+    __syncthreads();
+    if (*s_flag) {
+      __threadfence();
+      // (m, l) of every (head, segment) into shared memory, then one warp per head with four
+      // channels per lane: all loads of a head are independent, so the merge costs two round trips
+      float* sm_m = red;
+      float* sm_l = red + 8 * 64;
+      const int per_head = n_seg;                       // <= 64 by construction of the page ranges
+      for (int idx = tid; idx < G * per_head; idx += kThreads) {
+        const int h = idx / per_head, i = idx % per_head;
+        sm_m[h * 64 + i] = __ldcg(p.part_m + (row0 + h) * p.nch + i);
+        sm_l[h * 64 + i] = __ldcg(p.part_l + (row0 + h) * p.nch + i);
+      }
+      __syncthreads();
+      for (int h = warp; h < G; h += kWarps) {
+        const int64_t row = row0 + h;
+        float top = -INFINITY;
+        for (int i = 0; i < per_head; ++i)
+          if (sm_l[h * 64 + i] != 0.f) top = fmaxf(top, sm_m[h * 64 + i]);
+        float acc = 0.f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i0 = 0; i0 < per_head; i0 += 8) {
+          float4 v[8];
+          float w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j;
+            const bool live = i < per_head && sm_l[h * 64 + i] != 0.f && sm_m[h * 64 + i] != -INFINITY;
+            w[j] = live ? exp2f(sm_m[h * 64 + i] - top) : 0.f;
+            v[j] = live ? __ldcg(reinterpret_cast<const float4*>(p.part_o + (row * p.nch + i) * kHeadDim) + lane)
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j;
+            if (i < per_head) acc += sm_l[h * 64 + i] * w[j];
+            o.x += v[j].x * w[j]; o.y += v[j].y * w[j]; o.z += v[j].z * w[j]; o.w += v[j].w * w[j];
+          }
+        }
+        const float inv = acc == 0.f ? 0.f : 1.f / acc;
+        const float r0 = o.x * inv, r1 = o.y * inv, r2 = o.z * inv, r3 = o.w * inv;
+        const int64_t e = row * kHeadDim + 4 * lane;
+        if (p.out) {
+          store_from_float(p.out, e, p.q_dtype, r0);
+          store_from_float(p.out, e + 1, p.q_dtype, r1);
+          store_from_float(p.out, e + 2, p.q_dtype, r2);
+          store_from_float(p.out, e + 3, p.q_dtype, r3);
+        }
+        if (p.partial_out) {
+          float* po = p.partial_out + row * (kHeadDim + 1);
+          po[4 * lane] = r0; po[4 * lane + 1] = r1; po[4 * lane + 2] = r2; po[4 * lane + 3] = r3;
+          if (lane == 0) po[kHeadDim] = acc == 0.f ? -INFINITY : top + log2f(acc);
+        }
+      }
+    }
   }
   if (timed_out && p.status) atomicExch(p.status, 1);
 }
@@ -736,6 +804,8 @@ void decode_tma_plan(int B, int HKV, int NP, int wc_in, int ctas_per_sm, int* wc
     wc = (total + slots - 1) / slots;
     if (wc < 4) wc = 4;                               // a CTA's set-up is worth a few pages
   }
+  // the in-kernel merge holds at most 64 partials per q head
+  if (wc < (NP + 62) / 63) wc = (NP + 62) / 63;
   if (wc > total) wc = total;
   if (wc < 1) wc = 1;
   *wc_out = static_cast<int>(wc);

@@ -32,12 +32,24 @@ int quantize_dispatch(int variant, const void* k, int k_dtype, int B, int T, int
 
 namespace {
 
-constexpr int kBM = 128, kBN = 128, kBK = 64;       // tile; kBK bf16 = one 128-byte swizzle row
-constexpr int kStages = 6;
-constexpr int kTileBytes = kBM * kBK * 2;           // 16 KiB (A) and 16 KiB (B) per stage
+constexpr int kBM = 128, kBK = 64;                  // tile rows; kBK 16-bit elements = one 128-byte swizzle row
+constexpr int kTileBytes = kBM * kBK * 2;           // 16 KiB: the A tile, and each 128 rows of the B tile
 constexpr int kThreadsK = 192;
 constexpr int kSpin = 1 << 22;
-constexpr int kTmemCols = 256;                      // two 128-column fp32 accumulators
+
+// Tile width BN: 128 (one kv-head) or 256 (two).  The wider tile halves the A traffic per flop and
+// is used whenever there are enough tiles to fill the GPU; shared memory holds as many 128B-swizzled
+// stages as fit, tensor memory two BN-column fp32 accumulators.
+template <int BN>
+struct Tile {
+  static constexpr int kStages = BN == 128 ? 6 : 4;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kTileBytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kOffBars = kStages * kStageBytes;       // full[], empty[], tmem_full[2], tmem_empty[2]
+  static constexpr int kOffTmem = kOffBars + (2 * kStages + 4) * 8;
+  static constexpr int kBytes = kOffTmem + 16 + 1024;           // + alignment slack
+};
 
 struct KprojParams {
   const void* bias;      // [N] in io dtype or null
@@ -92,9 +104,9 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
 }
 
 // Instruction descriptor for kind::f16: fp32 accumulate, A and B both K-major, 16-bit format
-// `fmt` (0 = fp16, 1 = bf16), N = 128, M = 128.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt) {
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
+// `fmt` (0 = fp16, 1 = bf16), N = bn, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t bn) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((bn >> 3) << 17) | ((kBM >> 4) << 24);
 }
 
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -187,29 +199,26 @@ __device__ __forceinline__ void rope_store_32(const float (&acc)[32], const Kpro
   }
 }
 
-struct KSmem {
-  static constexpr int kOffA = 0;
-  static constexpr int kOffB = kStages * kTileBytes;
-  // full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
-  static constexpr int kOffBars = 2 * kStages * kTileBytes;
-  static constexpr int kOffTmem = kOffBars + (2 * kStages + 4) * 8;
-  static constexpr int kBytes = kOffTmem + 16 + 1024;            // + alignment slack
-};
-
 // Persistent kernel: work item w -> (m tile, n tile, k split); CTA c takes items c, c + grid, ...
 // With n_split == 1 the epilogue is fused (bias, rounding, RoPE, store K); with n_split > 1 (few
 // tokens: the GEMM is then a stream over W_k and needs more CTAs than output tiles) each item
 // stores its fp32 partial tile and kproj_finish_kernel adds the splits and applies the epilogue.
+template <int BN>
 __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_constant__ KprojParams p,
                                                                const __grid_constant__ CUtensorMap tm_a,
                                                                const __grid_constant__ CUtensorMap tm_b) {
+  using TL = Tile<BN>;
+  constexpr int kStages = TL::kStages;
+  constexpr int kBN = BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t bars = smem_u32(smem + KSmem::kOffBars);
+  const uint32_t bars = smem_u32(smem + TL::kOffBars);
   const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages;
   const uint32_t bar_tfull = bars + 16 * kStages, bar_tempty = bar_tfull + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + KSmem::kOffTmem);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TL::kOffTmem);
+  auto a_tile = [&](int s) { return smem + s * TL::kStageBytes; };
+  auto b_tile = [&](int s) { return smem + s * TL::kStageBytes + kTileBytes; };
   const int n_tiles = p.N / kBN;
   const int k_iters = p.H / kBK / p.n_split;                 // per work item
   const int n_items = p.m_tiles * n_tiles * p.n_split;
@@ -223,7 +232,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
   }
   if (warp == 1) {   // one warp allocates two accumulators' worth of tensor-memory columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)),
-                 "r"(kTmemCols)
+                 "r"(TL::kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
@@ -250,16 +259,16 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
         for (int k = 0; k < k_iters; ++k, ++it) {
           const int s = it % kStages;
           if (it >= kStages) timed_out |= !mbar_wait(bar_empty + 8 * s, ((it / kStages) - 1) & 1);
-          mbar_expect_tx(bar_full + 8 * s, 2 * kTileBytes);
-          tma_load_2d(smem_u32(smem + KSmem::kOffA + s * kTileBytes), &tm_a, k0 + k * kBK, m0, bar_full + 8 * s);
-          tma_load_2d(smem_u32(smem + KSmem::kOffB + s * kTileBytes), &tm_b, k0 + k * kBK, n0, bar_full + 8 * s);
+          mbar_expect_tx(bar_full + 8 * s, TL::kStageBytes);
+          tma_load_2d(smem_u32(a_tile(s)), &tm_a, k0 + k * kBK, m0, bar_full + 8 * s);
+          tma_load_2d(smem_u32(b_tile(s)), &tm_b, k0 + k * kBK, n0, bar_full + 8 * s);
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer -----------------------------------------------------------------------------
     if (lane == 0) {
-      const uint32_t idesc = instr_desc(p.io_dtype == FFA_BF16 ? 1u : 0u);
+      const uint32_t idesc = instr_desc(p.io_dtype == FFA_BF16 ? 1u : 0u, kBN);
       int it = 0, local = 0;
       for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++local) {
         const int buf = local & 1;
@@ -271,8 +280,8 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
           const int s = it % kStages;
           timed_out |= !mbar_wait(bar_full + 8 * s, (it / kStages) & 1);
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          const uint64_t da = smem_desc_sw128(smem_u32(smem + KSmem::kOffA + s * kTileBytes));
-          const uint64_t db = smem_desc_sw128(smem_u32(smem + KSmem::kOffB + s * kTileBytes));
+          const uint64_t da = smem_desc_sw128(smem_u32(a_tile(s)));
+          const uint64_t db = smem_desc_sw128(smem_u32(b_tile(s)));
 #pragma unroll
           for (int kk = 0; kk < kBK / 16; ++kk) umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
           umma_commit(bar_empty + 8 * s);        // frees the stage once these MMAs have read it
@@ -304,7 +313,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
         }
         if (m < p.M) {
           if (p.n_split == 1) {
-            rope_store_32(v, p, m, n0, 32 * c);
+            rope_store_32(v, p, m, n0 + ((32 * c) / kHeadDim) * kHeadDim, (32 * c) % kHeadDim);
           } else {
             const int split = w % p.n_split;
             float4* dst = reinterpret_cast<float4*>(p.partial + (static_cast<int64_t>(split) * p.M + m) * p.N + n0 + 32 * c);
@@ -319,7 +328,8 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TL::kTmemCols)
+                 : "memory");
   }
   if (timed_out && p.status) atomicExch(p.status, 2);
 }
@@ -361,11 +371,11 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [rows, cols] 16-bit row-major, box = 128 rows x 64 columns, 128-byte swizzle
-bool make_operand_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols) {
+// [rows, cols] 16-bit row-major, box = box_rows rows x 64 columns, 128-byte swizzle
+bool make_operand_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int box_rows) {
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  const cuuint32_t box[2] = {kBK, kBM};
+  const cuuint32_t box[2] = {kBK, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1, 1};
   return encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -391,7 +401,7 @@ int sm_count() {
 
 // Number of k splits for an [M, N] output with k_total_iters 64-wide k steps.
 int plan_split(int64_t M, int N, int k_total_iters) {
-  const int64_t tiles = ((M + kBM - 1) / kBM) * (N / kBN);
+  const int64_t tiles = ((M + kBM - 1) / kBM) * (N / 128);
   if (tiles >= kFewTiles) return 1;
   int64_t limit = sm_count() / tiles;
   const int64_t by_mem = static_cast<int64_t>(kPartialCap / (static_cast<size_t>(M) * N * 4));
@@ -403,7 +413,7 @@ int plan_split(int64_t M, int N, int k_total_iters) {
 }
 
 size_t partial_reserve(int64_t M, int N) {
-  const int64_t tiles = ((M + kBM - 1) / kBM) * (N / kBN);
+  const int64_t tiles = ((M + kBM - 1) / kBM) * (N / 128);
   if (tiles >= kFewTiles) return 0;
   const size_t full = static_cast<size_t>(16) * M * N * 4;
   return align256(full < kPartialCap ? full : kPartialCap);
@@ -444,29 +454,36 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   void* k_rope = a->k_rope_out ? a->k_rope_out : static_cast<void*>(ws);
   const bool need_quant = a->variant >= 0;
 
+  // two heads per tile when that still leaves at least one tile per SM
+  const int64_t m_tiles = (M + kBM - 1) / kBM;
+  const int bn = (N % 256 == 0 && m_tiles * (N / 256) >= sm_count()) ? 256 : 128;
   alignas(64) CUtensorMap ma, mb;
-  if (!make_operand_map(&ma, a->h, M, a->H) || !make_operand_map(&mb, a->w, N, a->H)) return FFA_E_LAUNCH;
+  if (!make_operand_map(&ma, a->h, M, a->H, kBM) || !make_operand_map(&mb, a->w, N, a->H, bn)) return FFA_E_LAUNCH;
 
   KprojParams p{};
   p.bias = a->bias; p.cos = a->cos; p.sin = a->sin; p.k_out = k_rope;
   p.status = reinterpret_cast<int*>(ws + k_bytes + q_bytes + p_bytes);
   p.partial = reinterpret_cast<float*>(ws + k_bytes + q_bytes);
   p.M = static_cast<int>(M); p.T = a->T; p.N = N; p.H = a->H;
-  p.m_tiles = static_cast<int>((M + kBM - 1) / kBM);
-  p.n_split = plan_split(M, N, a->H / kBK);
+  p.m_tiles = static_cast<int>(m_tiles);
+  p.n_split = bn == 256 ? 1 : plan_split(M, N, a->H / kBK);
   p.io_dtype = a->io_dtype; p.rope_dtype = a->rope_dtype;
 
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kproj_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KSmem::kBytes);
+    cudaError_t e = cudaFuncSetAttribute(kproj_rope_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Tile<128>::kBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(kproj_rope_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<256>::kBytes);
     if (e != cudaSuccess) return note_cuda_error(e, "cudaFuncSetAttribute(kproj_rope)");
     configured[dev] = true;
   }
-  const int64_t items = static_cast<int64_t>(p.m_tiles) * (N / kBN) * p.n_split;
+  const int64_t items = static_cast<int64_t>(p.m_tiles) * (N / bn) * p.n_split;
   const unsigned grid = static_cast<unsigned>(items < sm_count() ? items : sm_count());
-  kproj_rope_kernel<<<grid, kThreadsK, KSmem::kBytes, st>>>(p, ma, mb);
+  if (bn == 256) kproj_rope_kernel<256><<<grid, kThreadsK, Tile<256>::kBytes, st>>>(p, ma, mb);
+  else kproj_rope_kernel<128><<<grid, kThreadsK, Tile<128>::kBytes, st>>>(p, ma, mb);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return note_cuda_error(e, "kproj_rope launch");
   if (p.n_split > 1) {

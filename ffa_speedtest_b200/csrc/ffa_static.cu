@@ -16,8 +16,9 @@
 //     cudaGetSymbolAddress with that device current).  Make that first call outside any stream
 //     capture; later calls do no set-up;
 //   * all calls on a device share the one array and each call leaves its partial results behind.
-//     The only part that must start from zero - the status word the kernels can set - is cleared
-//     on the stream at the start of every call; everything else is overwritten before it is read.
+//     The parts that must start from zero - the status word the kernels can set and the arrival
+//     counters at the head of the workspace - are cleared on the stream at the start of every call;
+//     everything else is overwritten before it is read.
 //     Two calls whose kernels overlap on the GPU (different streams without an ordering between
 //     them, or concurrent host threads on one device) would race on the array: serialise them.
 //   * no cudaMalloc, cudaFree or other allocating routine is called, here or in ffa_decode().
@@ -65,10 +66,15 @@ extern "C" int ffa_decode_static_scratch(const FfaDecodeArgs* args, ffa_stream_t
   void* scratch = nullptr;
   const int rc = static_scratch_address(&scratch);
   if (rc != FFA_OK) return rc;
-  // the status word sits in the last 256 bytes of the workspace the decode kernels are given
+  // the status word sits in the last 256 bytes of the workspace the decode kernels are given, the
+  // arrival counters in its first bytes (one int per batch x kv-head; calls of different shapes
+  // leave other data where a later call expects zeros)
   cudaError_t e = cudaMemsetAsync(static_cast<unsigned char*>(scratch) + need - 256, 0, 256,
                                   reinterpret_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return ffa::note_cuda_error(e, "cudaMemsetAsync(static scratch status)");
+  if (e == cudaSuccess)
+    e = cudaMemsetAsync(scratch, 0, (static_cast<size_t>(args->B) * args->HKV * sizeof(int) + 255) / 256 * 256,
+                        reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return ffa::note_cuda_error(e, "cudaMemsetAsync(static scratch)");
   FfaDecodeArgs local = *args;
   local.workspace = scratch;
   local.workspace_bytes = need;

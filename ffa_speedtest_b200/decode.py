@@ -34,7 +34,8 @@ class DecodeWorkspace:
         self.key = (B, T, HQ, HKV, V, BS, SBS, torch.device(device), dtype, pages_per_chunk)
         nbytes = _lib.lib().ffa_decode_workspace_bytes(B, T, HQ, HKV, pages_per_chunk)
         ntbs = -(-T // BS) * (BS // SBS)
-        self.scratch = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        self.scratch = torch.empty(max(nbytes, 65536 + 256), dtype=torch.uint8, device=device)
+        self.scratch[:65536].zero_()     # arrival counters: zero before first use, kernels keep them zero
         self.scratch[-256:].zero_()      # status word: kernels only ever set it
         self.o = torch.empty((B, HQ, V), dtype=dtype, device=device)
         self.mask = torch.empty((B, HKV, ntbs), dtype=torch.int8, device=device)

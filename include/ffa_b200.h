@@ -82,7 +82,9 @@ typedef struct FfaDecodeArgs {
   float* partial_out;       /* optional [B, HQ, 129] fp32: normalised output followed by the
                                base-2 log-sum-exp of the kept scores (-inf if none kept), the
                                form ffa_merge_partials consumes                                 */
-  void* workspace;          /* >= ffa_decode_workspace_bytes(...) bytes, 256-byte aligned       */
+  void* workspace;          /* >= ffa_decode_workspace_bytes(...) bytes, 256-byte aligned.  Its
+                               first 64 KiB and last 256 bytes must be zero before the first call;
+                               every call leaves them zero (unless a kernel reported a timeout)  */
   size_t workspace_bytes;
   int32_t pages_per_chunk;  /* 0 = choose automatically                                         */
   int32_t reserved;         /* bit 0: use the fp16 tensor-core kernel even when the TMA/fp8 kernel
