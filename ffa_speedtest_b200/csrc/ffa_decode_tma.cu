@@ -63,7 +63,37 @@ struct ScaleCtx {
   const float* sZ;
   const float* book;
   float page_scale;
+  // fp16 fast paths, taken only when every scale / zero involved is exactly an fp16 number:
+  // q2: value = fma(code, scale, zero) evaluated in fp16 with one rounding.  The reference rounds the
+  // exact sum to fp32 and then to fp16; the two differ by one fp16 ulp only when the fp32 rounding
+  // lands on an fp16 tie (about 2e-5 of the elements for bf16 scales), far below what the prune band
+  // or the output tolerance can see.  nvfp4: e2m1 value (2 significant bits) times a bf16 scale
+  // (8 bits) is exact in fp16, so the product needs no fp32 detour at all.
+  bool q2_fast;
+  uint32_t s2[16], z2[16];     // this thread's channels 32t+2i, 32t+2i+1 as f16x2
+  bool page_fast;
+  uint32_t page_scale_h2;
 };
+
+// two 2-bit codes (bits 0-1 and 2-3 of n) as an f16x2 of their integer values: the high bytes of
+// fp16 0, 1, 2, 3 are 0x00, 0x3C, 0x40, 0x42 and the low bytes are zero
+// The byte permute picks result bytes (0, hi(c0), 0, hi(c1)), i.e. selector nibbles (4, c0, 4, c1);
+// multiplying the four code bits by 0x410 drops c0 at bits 4-5 and c1 at bits 12-13 in one step.
+__device__ __forceinline__ uint32_t codes2_to_h2(uint32_t low4) {
+  const uint32_t sel = ((low4 * 0x410u) & 0x3030u) | 0x0404u;
+  return __byte_perm(0x42403C00u, 0u, sel);
+}
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+  const __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b), *reinterpret_cast<__half2*>(&c));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  const __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ bool exact_in_f16(float x) {
+  return __half2float(__float2half_rn(x)) == x;     // false for NaN and for values that overflow
+}
 
 // ---- mbarrier / TMA primitives ------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -166,6 +196,11 @@ __device__ __forceinline__ void coarse_pair16(uint32_t& lo, uint32_t& hi, const 
                                               const ScaleCtx& sc) {
   if (FMT == FFA_K_Q2) {
     const uint32_t byte = (r[s >> 2] >> (8 * (s & 3))) & 0xffu;
+    if (sc.q2_fast) {
+      lo = hfma2_u32(codes2_to_h2(byte & 0xfu), sc.s2[2 * s], sc.z2[2 * s]);
+      hi = hfma2_u32(codes2_to_h2(byte >> 4), sc.s2[2 * s + 1], sc.z2[2 * s + 1]);
+      return;
+    }
     const float4 S = *reinterpret_cast<const float4*>(sc.sS + kb);
     const float4 Z = *reinterpret_cast<const float4*>(sc.sZ + kb);
     lo = pack_h2(fmaf(static_cast<float>(byte & 3u), S.x, Z.x), fmaf(static_cast<float>((byte >> 2) & 3u), S.y, Z.y));
@@ -176,6 +211,11 @@ __device__ __forceinline__ void coarse_pair16(uint32_t& lo, uint32_t& hi, const 
       lo = e2m1x2_to_h2(two);
       hi = e2m1x2_to_h2(two >> 8);
     } else if (FMT == FFA_K_NVFP4) {
+      if (sc.page_fast) {
+        lo = hmul2_u32(e2m1x2_to_h2(two), sc.page_scale_h2);
+        hi = hmul2_u32(e2m1x2_to_h2(two >> 8), sc.page_scale_h2);
+        return;
+      }
       const float2 a = unpack_h2(e2m1x2_to_h2(two));
       const float2 b = unpack_h2(e2m1x2_to_h2(two >> 8));
       lo = pack_h2(a.x * sc.page_scale, a.y * sc.page_scale);
@@ -321,9 +361,26 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       if (FMT == FFA_K_Q2) sZ[tid] = load_as_float(p.kz, o, p.scale_dtype);
       if (FMT == FFA_K_NF4 && tid < 16) sBook[tid] = c_nf4_book[tid];
     }
-    ScaleCtx sc{sS, sZ, sBook, 1.0f};
-    auto block_scale = [&](int blk) -> float {
-      return load_as_float(p.ks, (static_cast<int64_t>(b) * p.NTB + blk) * p.HKV + hkv, p.scale_dtype);
+    ScaleCtx sc;
+    sc.sS = sS; sc.sZ = sZ; sc.book = sBook; sc.page_scale = 1.0f;
+    sc.q2_fast = false; sc.page_fast = false; sc.page_scale_h2 = 0u;
+    if (FMT == FFA_K_Q2) {
+      // uniform over the CTA: all 128 (scale, zero) pairs of this (b, kv-head) are fp16 numbers
+      sc.q2_fast = __syncthreads_and(exact_in_f16(sS[tid]) && exact_in_f16(sZ[tid])) != 0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        sc.s2[i] = pack_h2(sS[32 * t + 2 * i], sS[32 * t + 2 * i + 1]);
+        sc.z2[i] = pack_h2(sZ[32 * t + 2 * i], sZ[32 * t + 2 * i + 1]);
+      }
+    }
+    // sets the nvfp4 scale of a BS-token block (and whether the fp16 product is exact for it)
+    auto set_block_scale = [&](int blk) {
+      const float x = load_as_float(p.ks, (static_cast<int64_t>(b) * p.NTB + blk) * p.HKV + hkv, p.scale_dtype);
+      sc.page_scale = x;
+      // e2m1 (2 significant bits) x scale fits fp16's 11 bits if the scale has at most 9 (bf16 has 8),
+      // and stays a normal fp16 number if the scale is within [2^-13, 2^13)
+      sc.page_fast = (__float_as_uint(x) & 0x7fffu) == 0u && fabsf(x) >= 1.220703125e-4f && fabsf(x) < 8192.f;
+      sc.page_scale_h2 = pack_h2(x, x);
     };
 
     // ---- q operands (q is bf16 on this path) -------------------------------------------------------
@@ -410,7 +467,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
         timed_out |= !mbar_wait(bars + 8 * warp, 0);
         const int blk = warp == 0 ? 0 : p.NTB - 1;
         const int tok0 = blk * kSample;
-        if (FMT == FFA_K_NVFP4) sc.page_scale = block_scale(blk);
+        if (FMT == FFA_K_NVFP4) set_block_scale(blk);
         float d[NT][2];
         coarse_dots(d, smem + warp * L::kBaseSlot, (tok0 % kPage) / 16);
 #pragma unroll
@@ -480,7 +537,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       if (do_score) {
         const int page = page_begin + j;
         timed_out |= !mbar_wait(bars + 8 * base_slot(j), base_parity(j));
-        if (FMT == FFA_K_NVFP4) sc.page_scale = block_scale((page * kPage) / p.BS);
+        if (FMT == FFA_K_NVFP4) set_block_scale((page * kPage) / p.BS);
         coarse_dots(dc, smem + base_slot(j) * L::kBaseSlot, warp);
         const int tok = page * kPage + 16 * warp + g;
 #pragma unroll
