@@ -90,6 +90,13 @@ class ClockSampler:
                  "-i", str(index)], stdout=self.tmp, stderr=subprocess.DEVNULL)
         except OSError:
             pass
+        # nvidia-smi takes a few hundred ms to produce its first line: wait for it so that the samples
+        # cover the timed region and not its aftermath
+        if self.proc is not None:
+            t0 = time.time()
+            while time.time() - t0 < 3.0 and os.path.getsize(self.tmp.name) == 0:
+                time.sleep(0.02)
+        self.t_ready = time.time()
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -103,6 +110,7 @@ class ClockSampler:
         self.tmp.flush()
         rows = [r.split(", ") for r in Path(self.tmp.name).read_text().strip().splitlines() if r.strip()]
         os.unlink(self.tmp.name)
+        rows = rows[1:] if len(rows) > 2 else rows      # the first line predates the timed region
         sm, smax, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for r in rows:
@@ -297,6 +305,8 @@ def main():
     e1.record()
     barrier()
     ms_e2e = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
+    if ws.status() != 0:
+        raise SystemExit("a bounded wait inside the decode kernel gave up (status word set): results are invalid")
 
     if world > 1:
         t = torch.tensor([ms, ms_e2e, kept, step_bytes], dtype=torch.float64, device=dev)

@@ -626,13 +626,13 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   const size_t po = align_up(rows * p.nch * kHeadDim * sizeof(float), 256);
   const size_t need = kArrivalBytes + ml * 2 + po + 256;
   if (a->workspace_bytes < need) return FFA_E_WORKSPACE;
-  if (static_cast<size_t>(a->B) * a->HKV * sizeof(int) > kArrivalBytes) return FFA_E_LIMIT;
+  if (static_cast<size_t>(a->B) * a->HKV * sizeof(int) > kArrivalBytes - 256) return FFA_E_LIMIT;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   p.arrivals = reinterpret_cast<int*>(ws);
   p.part_m = reinterpret_cast<float*>(ws + kArrivalBytes);
   p.part_l = reinterpret_cast<float*>(ws + kArrivalBytes + ml);
   p.part_o = reinterpret_cast<float*>(ws + kArrivalBytes + 2 * ml);
-  p.status = reinterpret_cast<int*>(ws + kArrivalBytes + 2 * ml + po);
+  p.status = reinterpret_cast<int*>(ws + kArrivalBytes - 256);      // fixed place: end of the counter block
   p.out = a->out;
   p.partial_out = a->partial_out;
 

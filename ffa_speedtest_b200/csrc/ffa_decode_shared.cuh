@@ -13,7 +13,8 @@ constexpr int kResRow = 128;      // fp8 residual bytes per token per head
 constexpr int kVRow = 256;        // V bytes per token per head (fp16 / bf16)
 constexpr int kRvSlot = kPage * (kResRow + kVRow);
 // The first kArrivalBytes of a decode workspace hold the per-(b, kv-head) arrival counters of the TMA
-// kernel.  They must be zero before the first launch; every launch leaves them zero again.
+// kernel (zero before the first launch; every launch leaves them zero again); its last 256 bytes hold
+// the status word that a kernel sets when a bounded wait gave up.
 constexpr int kArrivalBytes = 64 * 1024;
 
 static __constant__ float c_nf4_book[16] = {

@@ -38,7 +38,7 @@ constexpr int kThreads = kDecodeThreads;
 constexpr int kWarps = kDecodeWarps;
 constexpr int kPB = 3;          // coarse tiles requested ahead of the page being scored
 constexpr int kNBase = kPB + 1;
-constexpr int kSpinLimit = 1 << 22;   // bounded mbarrier wait (each try_wait blocks for a while itself)
+constexpr unsigned long long kWaitLimitNs = 200ull * 1000 * 1000;   // 0.2 s per mbarrier wait, then give up
 
 // DA = pages between scoring a page and refining it; DA + 1 residual+V slots
 template <int FMT, int DA>
@@ -103,8 +103,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Bounded wait for the phase with the given parity; returns false if it gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int spin = 0; spin < kSpinLimit; ++spin) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, bool gave_up_before = false) {
+  // Bounded in wall-clock time: a wait that has not completed after kWaitLimitNs gives up (the caller
+  // records it in the status word and carries on, so the kernel still terminates promptly); a thread
+  // that already gave up once does not wait again.
+  if (gave_up_before) return false;
+  unsigned long long t0 = 0;
+  for (int spin = 0;; ++spin) {
     uint32_t done;
     asm volatile(
         "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -112,8 +117,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     if (done) return true;
+    if ((spin & 63) == 63) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) return false;
+    }
   }
-  return false;
 }
 // 2-D tiled TMA load: box -> shared memory, completion counted in bytes on `bar`.  x is the byte
 // offset inside a token row (a multiple of 16), y the token row.
@@ -304,6 +314,25 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
   const bool use_res = p.use_res != 0;
   const bool sampled = p.th_in == nullptr;
   bool timed_out = false;
+  // diagnostics of the first wait that gave up: site (1 sample, 2 coarse tile, 3 residual+V),
+  // iteration, pages in the segment, segment ordinal within the CTA
+  int gave_up_site = 0, gave_up_it = 0, gave_up_n = 0, gave_up_seg = 0;
+  int seg_n = 0, seg_ord = -1;
+  auto wait_or_note = [&](uint32_t bar, uint32_t parity, int site, int it) {
+    if (!mbar_wait(bar, parity, timed_out)) {
+      if (!timed_out) { gave_up_site = site; gave_up_it = it; gave_up_n = seg_n; gave_up_seg = seg_ord; }
+      timed_out = true;
+    }
+  };
+
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < kNBase + kNRv; ++i) mbar_init(bars + 8 * i, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  __syncthreads();
+  uint32_t fills = 0;          // bit i: parity of the number of loads issued on barrier i
 
   const int64_t total_pages = static_cast<int64_t>(p.B) * p.HKV * p.NP;
   int64_t g0 = static_cast<int64_t>(blockIdx.x) * p.ppc;
@@ -318,42 +347,34 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
     const int n = static_cast<int>(min(g1 - g0, static_cast<int64_t>(p.NP - page_begin)));
     const int part = static_cast<int>(g0 / p.ppc - unit0 / p.ppc);     // partial slot of this segment
     g0 += n;
+    seg_n = n; ++seg_ord;
 
     auto page_row0 = [&](int page) -> int {
       return p.bt ? p.bt[static_cast<int64_t>(b) * p.bt_stride + page] * kPage : b * T + page * kPage;
     };
     // local page j lives in coarse slot (j + 2) % kNBase: slots 2 and 3 are free while slots 0 and
-    // 1 hold the two threshold samples, so the first two pages are requested at once
+    // 1 hold the two threshold samples, so the first two pages are requested at once.  Every thread
+    // keeps `fills` (bit i: parity of the number of loads issued on barrier i so far), so the
+    // barriers live for the whole kernel and the phase to wait for is the bit at the time of waiting:
+    // no barrier gets a second load before every thread has waited for the first.
     auto base_slot = [&](int j) -> int { return (j + 2) % kNBase; };
-    auto base_parity = [&](int j) -> uint32_t {
-      const int slot = base_slot(j);
-      return static_cast<uint32_t>((j + 2) / kNBase - ((slot < 2 && !sampled) ? 1 : 0)) & 1u;
+    auto issue_tile = [&](int slot, int page) {       // called by all threads
+      fills ^= 1u << slot;
+      if (tid == 0) {
+        mbar_expect_tx(bars + 8 * slot, L::kBaseSlot);
+        tma_load_2d(smem_u32(smem + slot * L::kBaseSlot), &tm_c, hkv * ROW, page_row0(page), bars + 8 * slot);
+      }
     };
-    auto issue_base = [&](int j) {
-      const int slot = base_slot(j);
-      mbar_expect_tx(bars + 8 * slot, L::kBaseSlot);
-      tma_load_2d(smem_u32(smem + slot * L::kBaseSlot), &tm_c, hkv * ROW, page_row0(page_begin + j), bars + 8 * slot);
-    };
+    auto issue_base = [&](int j) { issue_tile(base_slot(j), page_begin + j); };
+    auto wait_fill = [&](int i, int site, int it) { wait_or_note(bars + 8 * i, ((fills >> i) & 1u) ^ 1u, site, it); };
 
     if (!first) __syncthreads();        // the previous segment is done with shared memory
-    if (tid == 0) {
-#pragma unroll
-      for (int i = 0; i < kNBase + kNRv; ++i) {
-        if (!first) asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(bars + 8 * i) : "memory");
-        mbar_init(bars + 8 * i, 1);
-      }
-      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      // get the first tiles moving before anything else
-      if (sampled) {
-        const int tok1 = (p.NTB - 1) * kSample;
-        mbar_expect_tx(bars + 0, L::kBaseSlot);
-        tma_load_2d(smem_u32(smem), &tm_c, hkv * ROW, page_row0(0), bars + 0);
-        mbar_expect_tx(bars + 8, L::kBaseSlot);
-        tma_load_2d(smem_u32(smem + L::kBaseSlot), &tm_c, hkv * ROW, page_row0(tok1 / kPage), bars + 8);
-      }
-      for (int j = 0; j < 2 && j < n; ++j) issue_base(j);
+    // get the first tiles moving before anything else
+    if (sampled) {
+      issue_tile(0, 0);
+      issue_tile(1, ((p.NTB - 1) * kSample) / kPage);
     }
+    for (int j = 0; j < 2 && j < n; ++j) issue_base(j);
 
     if (L::kHasChannelScale) {
       const int64_t o = (static_cast<int64_t>(b) * p.HKV + hkv) * kHeadDim + tid;
@@ -464,7 +485,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       }
     } else {
       if (warp < 2) {
-        timed_out |= !mbar_wait(bars + 8 * warp, 0);
+        wait_fill(warp, 1, 0);
         const int blk = warp == 0 ? 0 : p.NTB - 1;
         const int tok0 = blk * kSample;
         if (FMT == FFA_K_NVFP4) set_block_scale(blk);
@@ -493,7 +514,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
     }
 
     // ---- page pipeline -----------------------------------------------------------------------------
-    auto issue_rv = [&](int j) {
+    auto issue_rv = [&](int j) {                      // thread 0 only; all threads toggle the bit
       const int slot = j % kNRv;
       const uint32_t bar = bars + 8 * (kNBase + slot);
       const uint32_t dst = smem_u32(smem + L::kOffRv + slot * kRvSlot);
@@ -516,17 +537,14 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       for (int d = 0; d < kDA; ++d) hist[d][nt][0] = hist[d][nt][1] = 0.f;
     }
     uint32_t keepq = 0;
-    uint32_t rv_fills = 0;           // bit s: parity of the number of fills issued into res+V slot s
 
     // (the __syncthreads after the sample scoring, or after the q set-up, orders every warp's reads
     // of slots 0 and 1 before they are refilled)
-    if (tid == 0) {
-      for (int j = 2; j < kPB && j < n; ++j) issue_base(j);
-    }
+    for (int j = 2; j < kPB && j < n; ++j) issue_base(j);
 
     for (int it = 0; it < n + kDA; ++it) {
       const int j = it, r = it - kDA;
-      if (tid == 0 && j + kPB < n) issue_base(j + kPB);
+      if (j + kPB < n) issue_base(j + kPB);
 
       const bool do_score = j < n;
       const bool do_refine = r >= 0 && ((keepq >> (kDA - 1)) & 1u);
@@ -536,7 +554,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
 
       if (do_score) {
         const int page = page_begin + j;
-        timed_out |= !mbar_wait(bars + 8 * base_slot(j), base_parity(j));
+        wait_fill(base_slot(j), 2, it);
         if (FMT == FFA_K_NVFP4) set_block_scale((page * kPage) / p.BS);
         coarse_dots(dc, smem + base_slot(j) * L::kBaseSlot, warp);
         const int tok = page * kPage + 16 * warp + g;
@@ -553,8 +571,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       if (do_refine) {
         const int page = page_begin + r;
         const uint8_t* slot = smem + L::kOffRv + (r % kNRv) * kRvSlot;
-        // the slot was filled once since the bit was last toggled (pruned pages issue no load)
-        timed_out |= !mbar_wait(bars + 8 * (kNBase + r % kNRv), ((rv_fills >> (r % kNRv)) & 1u) ^ 1u);
+        wait_fill(kNBase + r % kNRv, 3, it);      // pruned pages issue no load and toggle no bit
         float dr[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) dr[nt][0] = dr[nt][1] = 0.f;
@@ -599,7 +616,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       bool keep = false;
       if (do_score) {
         keep = !__all_sync(0xffffffffu, below);     // pruned only if every head is strictly below
-        if (keep) rv_fills ^= 1u << (j % kNRv);
+        if (keep) fills ^= 1u << (kNBase + j % kNRv);
         if (tid == 0) {
           if (keep) issue_rv(j);
           if (p.mask) p.mask[(static_cast<int64_t>(b) * p.HKV + hkv) * p.NTBS + page_begin + j] = keep ? 1 : 0;
@@ -771,7 +788,10 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       }
     }
   }
-  if (timed_out && p.status) atomicExch(p.status, 1);
+  if (timed_out && p.status && atomicCAS(p.status, 0, 1) == 0) {
+    p.status[1] = gave_up_site; p.status[2] = gave_up_it; p.status[3] = gave_up_n; p.status[4] = gave_up_seg;
+    p.status[5] = static_cast<int>(blockIdx.x); p.status[6] = tid;
+  }
 }
 
 // ---- host side ------------------------------------------------------------------------------------

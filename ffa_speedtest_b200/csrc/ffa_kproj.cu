@@ -35,7 +35,7 @@ namespace {
 constexpr int kBM = 128, kBK = 64;                  // tile rows; kBK 16-bit elements = one 128-byte swizzle row
 constexpr int kTileBytes = kBM * kBK * 2;           // 16 KiB: the A tile, and each 128 rows of the B tile
 constexpr int kThreadsK = 192;
-constexpr int kSpin = 1 << 22;
+constexpr unsigned long long kWaitLimitNs = 200ull * 1000 * 1000;   // 0.2 s per mbarrier wait, then give up
 
 // Tile width BN: 128 (one kv-head) or 256 (two).  The wider tile halves the A traffic per flop and
 // is used whenever there are enough tiles to fill the GPU; shared memory holds as many 128B-swizzled
@@ -70,8 +70,13 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int spin = 0; spin < kSpin; ++spin) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, bool gave_up_before = false) {
+  // Bounded in wall-clock time: a wait that has not completed after kWaitLimitNs gives up (the caller
+  // records it in the status word and carries on, so the kernel still terminates promptly); a thread
+  // that already gave up once does not wait again.
+  if (gave_up_before) return false;
+  unsigned long long t0 = 0;
+  for (int spin = 0;; ++spin) {
     uint32_t done;
     asm volatile(
         "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -79,8 +84,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     if (done) return true;
+    if ((spin & 63) == 63) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) return false;
+    }
   }
-  return false;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
@@ -258,7 +268,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
         decode_item(w, m0, n0, k0);
         for (int k = 0; k < k_iters; ++k, ++it) {
           const int s = it % kStages;
-          if (it >= kStages) timed_out |= !mbar_wait(bar_empty + 8 * s, ((it / kStages) - 1) & 1);
+          if (it >= kStages) timed_out |= !mbar_wait(bar_empty + 8 * s, ((it / kStages) - 1) & 1, timed_out);
           mbar_expect_tx(bar_full + 8 * s, TL::kStageBytes);
           tma_load_2d(smem_u32(a_tile(s)), &tm_a, k0 + k * kBK, m0, bar_full + 8 * s);
           tma_load_2d(smem_u32(b_tile(s)), &tm_b, k0 + k * kBK, n0, bar_full + 8 * s);
@@ -273,12 +283,12 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
       for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++local) {
         const int buf = local & 1;
         // the epilogue must have drained this accumulator (two items ago)
-        if (local >= 2) timed_out |= !mbar_wait(bar_tempty + 8 * buf, ((local >> 1) - 1) & 1);
+        if (local >= 2) timed_out |= !mbar_wait(bar_tempty + 8 * buf, ((local >> 1) - 1) & 1, timed_out);
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t tmem_d = tmem_base + buf * kBN;
         for (int k = 0; k < k_iters; ++k, ++it) {
           const int s = it % kStages;
-          timed_out |= !mbar_wait(bar_full + 8 * s, (it / kStages) & 1);
+          timed_out |= !mbar_wait(bar_full + 8 * s, (it / kStages) & 1, timed_out);
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
           const uint64_t da = smem_desc_sw128(smem_u32(a_tile(s)));
           const uint64_t db = smem_desc_sw128(smem_u32(b_tile(s)));
@@ -299,7 +309,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
       decode_item(w, m0, n0, k0);
       const int buf = local & 1;
       const int64_t m = static_cast<int64_t>(m0) + row;
-      timed_out |= !mbar_wait(bar_tfull + 8 * buf, (local >> 1) & 1);
+      timed_out |= !mbar_wait(bar_tfull + 8 * buf, (local >> 1) & 1, timed_out);
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll 1
       for (int c = 0; c < kBN / 32; ++c) {

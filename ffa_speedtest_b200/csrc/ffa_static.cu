@@ -66,14 +66,9 @@ extern "C" int ffa_decode_static_scratch(const FfaDecodeArgs* args, ffa_stream_t
   void* scratch = nullptr;
   const int rc = static_scratch_address(&scratch);
   if (rc != FFA_OK) return rc;
-  // the status word sits in the last 256 bytes of the workspace the decode kernels are given, the
-  // arrival counters in its first bytes (one int per batch x kv-head; calls of different shapes
-  // leave other data where a later call expects zeros)
-  cudaError_t e = cudaMemsetAsync(static_cast<unsigned char*>(scratch) + need - 256, 0, 256,
-                                  reinterpret_cast<cudaStream_t>(stream));
-  if (e == cudaSuccess)
-    e = cudaMemsetAsync(scratch, 0, (static_cast<size_t>(args->B) * args->HKV * sizeof(int) + 255) / 256 * 256,
-                        reinterpret_cast<cudaStream_t>(stream));
+  // the first 64 KiB of the workspace hold the arrival counters (one int per batch x kv-head) and,
+  // in their last 256 bytes, the status word: all of it has to read zero when the kernel starts
+  cudaError_t e = cudaMemsetAsync(scratch, 0, 64 * 1024, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return ffa::note_cuda_error(e, "cudaMemsetAsync(static scratch)");
   FfaDecodeArgs local = *args;
   local.workspace = scratch;

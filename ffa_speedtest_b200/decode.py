@@ -34,9 +34,8 @@ class DecodeWorkspace:
         self.key = (B, T, HQ, HKV, V, BS, SBS, torch.device(device), dtype, pages_per_chunk)
         nbytes = _lib.lib().ffa_decode_workspace_bytes(B, T, HQ, HKV, pages_per_chunk)
         ntbs = -(-T // BS) * (BS // SBS)
-        self.scratch = torch.empty(max(nbytes, 65536 + 256), dtype=torch.uint8, device=device)
-        self.scratch[:65536].zero_()     # arrival counters: zero before first use, kernels keep them zero
-        self.scratch[-256:].zero_()      # status word: kernels only ever set it
+        self.scratch = torch.empty(max(nbytes, 65536), dtype=torch.uint8, device=device)
+        self.scratch[:65536].zero_()     # arrival counters + status word: zero before first use
         self.o = torch.empty((B, HQ, V), dtype=dtype, device=device)
         self.mask = torch.empty((B, HKV, ntbs), dtype=torch.int8, device=device)
         self.threshold = torch.empty((B, HQ), dtype=torch.float32, device=device)
@@ -44,7 +43,7 @@ class DecodeWorkspace:
 
     def status(self) -> int:
         """Device status word (synchronises): 0 = ok, 1 = a bounded wait inside a kernel gave up."""
-        return int(self.scratch[-256:-252].view(torch.int32).item())
+        return int(self.scratch[65280:65284].view(torch.int32).item())
 
 
 def allocate_decode_workspace(q, v, *, BS: int = 128, SBS: Optional[int] = None, seq_len: Optional[int] = None,

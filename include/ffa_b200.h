@@ -83,8 +83,9 @@ typedef struct FfaDecodeArgs {
                                base-2 log-sum-exp of the kept scores (-inf if none kept), the
                                form ffa_merge_partials consumes                                 */
   void* workspace;          /* >= ffa_decode_workspace_bytes(...) bytes, 256-byte aligned.  Its
-                               first 64 KiB and last 256 bytes must be zero before the first call;
-                               every call leaves them zero (unless a kernel reported a timeout)  */
+                               first 64 KiB must be zero before the first call; every call leaves
+                               them zero, except the int at byte 65280, which a kernel sets when
+                               one of its bounded waits gave up (the results are then invalid)  */
   size_t workspace_bytes;
   int32_t pages_per_chunk;  /* 0 = choose automatically                                         */
   int32_t reserved;         /* bit 0: use the fp16 tensor-core kernel even when the TMA/fp8 kernel
