@@ -27,6 +27,7 @@ _ERRORS = {
     -5: "FFA_E_LAUNCH (CUDA runtime error)",
     -6: "FFA_E_VARIANT (unknown coarse-K format)",
     -7: "FFA_E_LIMIT (size beyond a compiled-in maximum)",
+    -8: "FFA_E_ALIGN (a tensor pointer is not 16-byte aligned)",
 }
 
 

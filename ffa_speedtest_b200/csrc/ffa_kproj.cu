@@ -20,6 +20,7 @@
 // warps 2..5 = epilogue (TMEM lane quarter = warp % 4).  Every mbarrier wait is bounded.
 #include <cuda.h>
 
+#include <cstdlib>
 #include "ffa_common.cuh"
 #include "ffa_numeric.h"
 
@@ -62,6 +63,7 @@ struct KprojParams {
   int m_tiles, n_split;
   int io_dtype;          // FFA_F16 | FFA_BF16: h, W, bias
   int rope_dtype;        // dtype of cos/sin; the RoPE arithmetic and k_out use promote(io, rope)
+  int debug;
 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -146,66 +148,99 @@ __device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t taddr) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// bias + rounding to the activation dtype + RoPE for 32 consecutive channels of one token row,
-// in the reference's op order; writes K in the promoted dtype.
-__device__ __forceinline__ void rope_store_32(const float (&acc)[32], const KprojParams& p, int64_t m, int n_base,
-                                              int ch0) {
-  const bool rope32 = p.rope_dtype == FFA_F32;
-  const int out_dt = rope32 ? FFA_F32 : p.io_dtype;
+// Epilogue of one token row x 32 channels (16 RoPE pairs): bias, rounding to the activation dtype
+// (F.linear returns it), then RoPE with the interleaved-pair rotate_half of the reference
+// (fused_kproj_rope_q2fp8.py:24-37): out = x * cos + rotate_half(x) * sin, every product and the sum
+// rounded separately in the promoted dtype like the three torch ops.  IO / ROPE are the FFA_* codes
+// of the activation dtype and of the cos/sin tables (ROPE is IO or FFA_F32).
+//
+// With 16-bit tables the whole rotation runs on packed pairs: the hardware's two-wide 16-bit
+// multiply and add round once to the 16-bit result, which is what rounding the exact fp32 product
+// (or sum) of two 16-bit numbers gives.
+template <int IO> struct Pack16;
+template <> struct Pack16<FFA_BF16> {
+  using T2 = __nv_bfloat162;
+  static __device__ __forceinline__ T2 from_floats(float lo, float hi) { return __floats2bfloat162_rn(lo, hi); }
+  static __device__ __forceinline__ float2 to_floats(T2 v) { return __bfloat1622float2(v); }
+};
+template <> struct Pack16<FFA_F16> {
+  using T2 = __half2;
+  static __device__ __forceinline__ T2 from_floats(float lo, float hi) { return __floats2half2_rn(lo, hi); }
+  static __device__ __forceinline__ float2 to_floats(T2 v) { return __half22float2(v); }
+};
+
+template <int IO, int ROPE>
+__device__ __forceinline__ void rope_store_32_t(const float (&acc)[32], const KprojParams& p, int64_t m, int n_base,
+                                                int ch0) {
+  using P = Pack16<IO>;
+  using T2 = typename P::T2;
   const int64_t tok = m % p.T;
-  float kx[32], cs[32], sn[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    float x = acc[i];
-    if (p.bias) x = __fadd_rn(x, num::load_elem(p.bias, n_base + ch0 + i, p.io_dtype));
-    kx[i] = num::round_to(x, p.io_dtype);                  // F.linear returns the activation dtype
-  }
-  if (rope32) {
-    const float4* c4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.cos) + tok * kHeadDim + ch0);
-    const float4* s4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.sin) + tok * kHeadDim + ch0);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float4 c = c4[i], s = s4[i];
-      cs[4 * i] = c.x; cs[4 * i + 1] = c.y; cs[4 * i + 2] = c.z; cs[4 * i + 3] = c.w;
-      sn[4 * i] = s.x; sn[4 * i + 1] = s.y; sn[4 * i + 2] = s.z; sn[4 * i + 3] = s.w;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      cs[i] = num::load_elem(p.cos, tok * kHeadDim + ch0 + i, p.rope_dtype);
-      sn[i] = num::load_elem(p.sin, tok * kHeadDim + ch0 + i, p.rope_dtype);
-    }
-  }
-  float out[32];
-#pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    // (x * cos) + (rotate_half(x) * sin): three separately rounded ops in the promoted dtype
-    const float a0 = num::round_to(__fmul_rn(kx[i], cs[i]), out_dt);
-    const float a1 = num::round_to(__fmul_rn(kx[i + 1], cs[i + 1]), out_dt);
-    const float b0 = num::round_to(__fmul_rn(-kx[i + 1], sn[i]), out_dt);
-    const float b1 = num::round_to(__fmul_rn(kx[i], sn[i + 1]), out_dt);
-    out[i] = num::round_to(__fadd_rn(a0, b0), out_dt);
-    out[i + 1] = num::round_to(__fadd_rn(a1, b1), out_dt);
-  }
   const int64_t o = m * p.N + n_base + ch0;
-  if (out_dt == FFA_F32) {
-    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.k_out) + o);
+  // activations: fp32 accumulator (+ bias) rounded to the activation dtype, as packed pairs
+  T2 x2[16];
+  if (p.bias) {
+    const uint4* b4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.bias) + n_base + ch0);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) dst[i] = make_float4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) {
+      const uint4 b = b4[i];
+      const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 bf = P::to_floats(*reinterpret_cast<const T2*>(&bw[j]));
+        x2[4 * i + j] = P::from_floats(__fadd_rn(acc[8 * i + 2 * j], bf.x), __fadd_rn(acc[8 * i + 2 * j + 1], bf.y));
+      }
+    }
   } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x2[i] = P::from_floats(acc[2 * i], acc[2 * i + 1]);
+  }
+  if (ROPE != FFA_F32) {
+    const uint4* c4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.cos) + tok * kHeadDim + ch0);
+    const uint4* s4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.sin) + tok * kHeadDim + ch0);
     uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.k_out) + o);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
+      const uint4 c = c4[i], s = s4[i];
+      const uint32_t cw[4] = {c.x, c.y, c.z, c.w}, sw[4] = {s.x, s.y, s.z, s.w};
       uint32_t w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float lo = out[8 * i + 2 * j], hi = out[8 * i + 2 * j + 1];
-        const uint32_t l16 = out_dt == FFA_BF16 ? num::f32_to_bf16_bits(lo) : __half_as_ushort(__float2half_rn(lo));
-        const uint32_t h16 = out_dt == FFA_BF16 ? num::f32_to_bf16_bits(hi) : __half_as_ushort(__float2half_rn(hi));
-        w[j] = l16 | (h16 << 16);
+        const T2 x = x2[4 * i + j];
+        // rotate_half of the pair (x0, x1) is (-x1, x0): swap the halves, flip the sign of the low one
+        const uint32_t xr = __byte_perm(*reinterpret_cast<const uint32_t*>(&x), 0u, 0x1032) ^ 0x00008000u;
+        const T2 a = __hmul2(x, *reinterpret_cast<const T2*>(&cw[j]));
+        const T2 b = __hmul2(*reinterpret_cast<const T2*>(&xr), *reinterpret_cast<const T2*>(&sw[j]));
+        const T2 r = __hadd2(a, b);
+        w[j] = *reinterpret_cast<const uint32_t*>(&r);
       }
       dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
     }
+  } else {
+    const float4* c4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.cos) + tok * kHeadDim + ch0);
+    const float4* s4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.sin) + tok * kHeadDim + ch0);
+    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.k_out) + o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 c = c4[i], s = s4[i];
+      const float2 xa = P::to_floats(x2[2 * i]), xb = P::to_floats(x2[2 * i + 1]);
+      float4 r;
+      r.x = __fadd_rn(__fmul_rn(xa.x, c.x), __fmul_rn(-xa.y, s.x));
+      r.y = __fadd_rn(__fmul_rn(xa.y, c.y), __fmul_rn(xa.x, s.y));
+      r.z = __fadd_rn(__fmul_rn(xb.x, c.z), __fmul_rn(-xb.y, s.z));
+      r.w = __fadd_rn(__fmul_rn(xb.y, c.w), __fmul_rn(xb.x, s.w));
+      dst[i] = r;
+    }
+  }
+}
+
+__device__ __forceinline__ void rope_store_32(const float (&acc)[32], const KprojParams& p, int64_t m, int n_base,
+                                              int ch0) {
+  if (p.io_dtype == FFA_BF16) {
+    if (p.rope_dtype == FFA_F32) rope_store_32_t<FFA_BF16, FFA_F32>(acc, p, m, n_base, ch0);
+    else rope_store_32_t<FFA_BF16, FFA_BF16>(acc, p, m, n_base, ch0);
+  } else {
+    if (p.rope_dtype == FFA_F32) rope_store_32_t<FFA_F16, FFA_F32>(acc, p, m, n_base, ch0);
+    else rope_store_32_t<FFA_F16, FFA_F16>(acc, p, m, n_base, ch0);
   }
 }
 
@@ -269,6 +304,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
         for (int k = 0; k < k_iters; ++k, ++it) {
           const int s = it % kStages;
           if (it >= kStages) timed_out |= !mbar_wait(bar_empty + 8 * s, ((it / kStages) - 1) & 1, timed_out);
+          if (p.debug & 1) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_full + 8 * s) : "memory"); continue; }
           mbar_expect_tx(bar_full + 8 * s, TL::kStageBytes);
           tma_load_2d(smem_u32(a_tile(s)), &tm_a, k0 + k * kBK, m0, bar_full + 8 * s);
           tma_load_2d(smem_u32(b_tile(s)), &tm_b, k0 + k * kBK, n0, bar_full + 8 * s);
@@ -293,7 +329,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
           const uint64_t da = smem_desc_sw128(smem_u32(a_tile(s)));
           const uint64_t db = smem_desc_sw128(smem_u32(b_tile(s)));
 #pragma unroll
-          for (int kk = 0; kk < kBK / 16; ++kk) umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < kBK / 16; ++kk) if (!(p.debug & 2)) umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
           umma_commit(bar_empty + 8 * s);        // frees the stage once these MMAs have read it
         }
         umma_commit(bar_tfull + 8 * buf);        // accumulator complete
@@ -321,7 +357,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
           __syncwarp();
           if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_tempty + 8 * buf) : "memory");
         }
-        if (m < p.M) {
+        if (m < p.M && !(p.debug & 4)) {
           if (p.n_split == 1) {
             rope_store_32(v, p, m, n0 + ((32 * c) / kHeadDim) * kHeadDim, (32 * c) % kHeadDim);
           } else {
@@ -478,6 +514,7 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   p.m_tiles = static_cast<int>(m_tiles);
   p.n_split = bn == 256 ? 1 : plan_split(M, N, a->H / kBK);
   p.io_dtype = a->io_dtype; p.rope_dtype = a->rope_dtype;
+  { const char* e = getenv("FFA_KPROJ_DEBUG"); p.debug = e ? atoi(e) : 0; }
 
   static bool configured[64] = {};
   int dev = 0;

@@ -58,6 +58,9 @@ FFA_HD uint16_t f32_to_bf16_bits(float f) {
 }
 
 FFA_HD float f16_bits_to_f32(uint16_t h) {
+#if defined(__CUDA_ARCH__)
+  return __half2float(__ushort_as_half(h));
+#endif
   const uint32_t sign = static_cast<uint32_t>(h & 0x8000u) << 16;
   const uint32_t e = (h >> 10) & 0x1fu, m = h & 0x3ffu;
   if (e == 0x1fu) return u2f(sign | 0x7f800000u | (m << 13));
@@ -120,23 +123,51 @@ FFA_HD void store_elem(void* p, int64_t i, int dt, float x) {
 }
 
 // ---- fp8 ------------------------------------------------------------------------------------
+// On the device the narrowing itself is the hardware's round-to-nearest-even conversion; it
+// saturates where torch overflows, so everything above the last value that still rounds down to
+// the largest finite number (464 for e4m3fn, 61440 for e5m2) is patched to torch's result.
 FFA_HD uint8_t f32_to_e4m3(float f) {
   const uint32_t u = f2u(f), a = u & 0x7fffffffu;
   const uint8_t sign = static_cast<uint8_t>((u >> 24) & 0x80u);
+#if defined(__CUDA_ARCH__)
+  if (a > 0x43e80000u) return sign | 0x7fu;                // |x| > 464, inf, NaN
+  uint16_t pair;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(pair) : "f"(0.f), "f"(f));
+  return static_cast<uint8_t>(pair & 0xffu);
+#else
   if (a >= 0x43f00000u) return sign | 0x7fu;               // |x| >= 480, inf, NaN
-  return sign | static_cast<uint8_t>(narrow_rne<3, 7>(a));  // [464, 480) carries into 0x7F too
+  return sign | static_cast<uint8_t>(narrow_rne<3, 7>(a));  // (464, 480) carries into 0x7F too
+#endif
 }
 FFA_HD uint8_t f32_to_e5m2(float f) {
   const uint32_t u = f2u(f), a = u & 0x7fffffffu;
   const uint8_t sign = static_cast<uint8_t>((u >> 24) & 0x80u);
   if (a > 0x7f800000u) return sign | 0x7fu;
+#if defined(__CUDA_ARCH__)
+  if (a >= 0x47700000u) return sign | 0x7cu;               // |x| >= 61440 rounds to infinity
+  uint16_t pair;
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;\n" : "=h"(pair) : "f"(0.f), "f"(f));
+  return static_cast<uint8_t>(pair & 0xffu);
+#else
   if (a >= 0x47800000u) return sign | 0x7cu;               // |x| >= 65536
   return sign | static_cast<uint8_t>(narrow_rne<2, 15>(a));
+#endif
 }
 FFA_HD uint8_t f32_to_fp8(float f, int fmt) { return fmt == kE4M3 ? f32_to_e4m3(f) : f32_to_e5m2(f); }
 
-FFA_HD float e5m2_to_f32(uint8_t b) { return f16_bits_to_f32(static_cast<uint16_t>(b) << 8); }
+FFA_HD float e5m2_to_f32(uint8_t b) {
+#if defined(__CUDA_ARCH__)
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(b) << 8));
+#else
+  return f16_bits_to_f32(static_cast<uint16_t>(b) << 8);
+#endif
+}
 FFA_HD float e4m3_to_f32(uint8_t b) {
+#if defined(__CUDA_ARCH__)
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h2) : "h"(static_cast<uint16_t>(b)));
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xffffu)));
+#endif
   const uint32_t sign = static_cast<uint32_t>(b & 0x80u) << 24;
   const uint32_t e = (b >> 3) & 0xfu, m = b & 7u;
   if ((b & 0x7fu) == 0x7fu) return u2f(sign | 0x7fc00000u);
@@ -195,7 +226,9 @@ FFA_HD void q2_scale_zero(float lo, float hi, int dt, float* scale, float* zero)
   *scale = round_to(span / 3.0f, dt);
   *zero = lo;
 }
-FFA_HD uint32_t q2_encode(float k, float scale, float zero, int dt, int fp8, uint8_t* res) {
+// Each *_f function returns the code and leaves the residual as a float (already rounded the way
+// the reference's dtype arithmetic rounds it); the caller narrows it to fp8.
+FFA_HD uint32_t q2_encode_f(float k, float scale, float zero, int dt, float* res_f) {
   const float d = round_to(k - zero, dt);
   const float r = round_to(d / scale, dt);
 #if defined(__CUDA_ARCH__)
@@ -209,35 +242,50 @@ FFA_HD uint32_t q2_encode(float k, float scale, float zero, int dt, int fp8, uin
   // multiply-add when scale has more than 22 significant bits, i.e. for fp32 K)
 #if defined(__CUDA_ARCH__)
   const float deq = __fadd_rn(__fmul_rn(c, scale), zero);
-  *res = f32_to_fp8(__fsub_rn(k, deq), fp8);
+  *res_f = __fsub_rn(k, deq);
 #else
   volatile float prod = c * scale;
   const float deq = prod + zero;
-  *res = f32_to_fp8(k - deq, fp8);
+  *res_f = k - deq;
 #endif
   return static_cast<uint32_t>(c);
+}
+FFA_HD uint32_t q2_encode(float k, float scale, float zero, int dt, int fp8, uint8_t* res) {
+  float rf;
+  const uint32_t c = q2_encode_f(k, scale, zero, dt, &rf);
+  *res = f32_to_fp8(rf, fp8);
+  return c;
 }
 FFA_HD void fp8fp8_encode(float k, int fp8, uint8_t* base, uint8_t* res) {
   const uint8_t b = f32_to_fp8(k, fp8);
   *base = b;
   *res = f32_to_fp8(k - fp8_to_f32(b, fp8), fp8);
 }
-FFA_HD uint32_t fp4_encode(float k, int dt, int fp8, uint8_t* res) {
+FFA_HD uint32_t fp4_encode_f(float k, int dt, float* res_f) {
   float lv;
   const uint32_t nib = e2m1_encode(k, &lv);
-  *res = f32_to_fp8(round_to(k - lv, dt), fp8);
+  *res_f = round_to(k - lv, dt);
   return nib;
+}
+FFA_HD uint32_t fp4_encode(float k, int dt, int fp8, uint8_t* res) {
+  float rf;
+  const uint32_t nib = fp4_encode_f(k, dt, &rf);
+  *res = f32_to_fp8(rf, fp8);
+  return nib;
+}
+// `level` is NF4_CODEBOOK[idx], looked up by the caller (a table in registers on the device)
+FFA_HD float nf4_residual_f(float k, float level, float absmax) {
+  // product and difference round separately (no fused multiply-add), as two torch ops do
+#if defined(__CUDA_ARCH__)
+  return __fsub_rn(k, __fmul_rn(level, absmax));
+#else
+  volatile float deq = level * absmax;
+  return k - deq;
+#endif
 }
 FFA_HD uint32_t nf4_encode_elem(float k, float absmax, int fp8, uint8_t* res) {
   const uint32_t idx = nf4_encode(k / absmax);
-  // product and difference round separately (no fused multiply-add), as two torch ops do
-#if defined(__CUDA_ARCH__)
-  const float deq = __fmul_rn(nf4_level(idx), absmax);
-  *res = f32_to_fp8(__fsub_rn(k, deq), fp8);
-#else
-  volatile float deq = nf4_level(idx) * absmax;
-  *res = f32_to_fp8(k - deq, fp8);
-#endif
+  *res = f32_to_fp8(nf4_residual_f(k, nf4_level(idx), absmax), fp8);
   return idx;
 }
 FFA_HD float nvfp4_scale(float absmax, int dt) {
@@ -245,13 +293,56 @@ FFA_HD float nvfp4_scale(float absmax, int dt) {
   const float s = round_to(absmax / 6.0f, dt);
   return s < floor_ ? floor_ : s;
 }
-FFA_HD uint32_t nvfp4_encode(float k, float scale, int dt, int fp8, uint8_t* res) {
+FFA_HD uint32_t nvfp4_encode_f(float k, float scale, int dt, float* res_f) {
   float lv;
   const uint32_t nib = e2m1_encode(round_to(k / scale, dt), &lv);
-  const float deq = round_to(lv * scale, dt);
-  *res = f32_to_fp8(round_to(k - deq, dt), fp8);
+  // product and difference are two torch ops: no fused multiply-add
+#if defined(__CUDA_ARCH__)
+  const float deq = round_to(__fmul_rn(lv, scale), dt);
+  *res_f = round_to(__fsub_rn(k, deq), dt);
+#else
+  volatile float prod = lv * scale;
+  const float deq = round_to(prod, dt);
+  *res_f = round_to(k - deq, dt);
+#endif
   return nib;
 }
+FFA_HD uint32_t nvfp4_encode(float k, float scale, int dt, int fp8, uint8_t* res) {
+  float rf;
+  const uint32_t nib = nvfp4_encode_f(k, scale, dt, &rf);
+  *res = f32_to_fp8(rf, fp8);
+  return nib;
+}
+
+#if defined(__CUDACC__)
+// Two floats -> two fp8 bytes (a in the low byte) with torch's overflow behaviour, one hardware
+// conversion for the pair.
+template <int F8>
+__device__ __forceinline__ uint32_t f32x2_to_fp8x2(float a, float b) {
+  uint16_t pair;
+  if (F8 == kE4M3) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(pair) : "f"(b), "f"(a));
+  else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;\n" : "=h"(pair) : "f"(b), "f"(a));
+  uint32_t out = pair;
+  const uint32_t ua = __float_as_uint(a), ub = __float_as_uint(b);
+  const uint32_t aa = ua & 0x7fffffffu, ab = ub & 0x7fffffffu;
+  if (F8 == kE4M3) {
+    if (aa > 0x43e80000u) out = (out & 0xff00u) | ((ua >> 24) & 0x80u) | 0x7fu;
+    if (ab > 0x43e80000u) out = (out & 0x00ffu) | ((((ub >> 24) & 0x80u) | 0x7fu) << 8);
+  } else {
+    if (aa >= 0x47700000u) out = (out & 0xff00u) | ((ua >> 24) & 0x80u) | (aa > 0x7f800000u ? 0x7fu : 0x7cu);
+    if (ab >= 0x47700000u) out = (out & 0x00ffu) | ((((ub >> 24) & 0x80u) | (ab > 0x7f800000u ? 0x7fu : 0x7cu)) << 8);
+  }
+  return out;
+}
+// two fp8 bytes -> two floats
+template <int F8>
+__device__ __forceinline__ float2 fp8x2_to_f32x2(uint32_t pair) {
+  uint32_t h2;
+  if (F8 == kE4M3) asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h2) : "h"(static_cast<uint16_t>(pair)));
+  else asm("cvt.rn.f16x2.e5m2x2 %0, %1;\n" : "=r"(h2) : "h"(static_cast<uint16_t>(pair)));
+  return __half22float2(*reinterpret_cast<const __half2*>(&h2));
+}
+#endif
 
 }  // namespace num
 }  // namespace ffa

@@ -38,6 +38,33 @@ struct RowMap {
   }
 };
 
+// ---- eight consecutive elements per thread ------------------------------------------------------
+// Every pass moves K in 16-byte (16-bit K) or 2 x 16-byte (fp32 K) loads of eight consecutive
+// channels and writes each output with one store of 2 to 8 bytes per thread, so a warp reads and
+// writes whole 128-byte lines.  DT and F8 are compile-time so the per-element code has no branches
+// on the element type.
+template <int DT>
+__device__ __forceinline__ void load8(const void* __restrict__ k, int64_t e, float (&x)[8]) {
+  if (DT == kF32) {
+    const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(k) + e);
+    const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(k) + e + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+  } else {
+    const uint4 v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(k) + e);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (DT == kBF16) {
+        x[2 * i] = __uint_as_float(w[i] << 16);
+        x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        x[2 * i] = f.x; x[2 * i + 1] = f.y;
+      }
+    }
+  }
+}
+
 // scratch: [B, HKV*128] x {min, max} as ordered uints
 __global__ void minmax_init_kernel(uint32_t* mm, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -47,28 +74,65 @@ __global__ void minmax_init_kernel(uint32_t* mm, int n) {
   }
 }
 
-// One block per (b, slab of tokens); thread i owns channels i, i+256, ... of the HKV*128 row.
-template <bool ABS>
-__global__ void __launch_bounds__(256) minmax_kernel(const void* __restrict__ k, int dt, int T, int row_elems,
+// One block per (b, slab of tokens).  A thread owns one group of eight channels and every
+// `lanes`-th token of the slab; the block folds its token lanes in shared memory before the
+// atomics, so each block issues one atomic pair per channel.
+template <bool ABS, int DT>
+__global__ void __launch_bounds__(256) minmax_kernel(const void* __restrict__ k, int T, int groups_per_row,
                                                      int tokens_per_block, uint32_t* mm) {
+  extern __shared__ float s_fold[];                 // [lanes][groups_per_row * 8][2]
   const int b = blockIdx.y;
   const int t0 = blockIdx.x * tokens_per_block;
   const int t1 = min(T, t0 + tokens_per_block);
-  for (int c = threadIdx.x; c < row_elems; c += blockDim.x) {
-    float lo = INFINITY, hi = -INFINITY;
-    for (int t = t0; t < t1; ++t) {
-      float v = load_elem(k, (static_cast<int64_t>(b) * T + t) * row_elems + c, dt);
-      if (ABS) v = fabsf(v);
-      lo = fminf(lo, v);
-      hi = fmaxf(hi, v);
+  const int row_elems = groups_per_row * 8;
+  const int lanes = groups_per_row >= 256 ? 1 : 256 / groups_per_row;
+  const int lane = groups_per_row >= 256 ? 0 : threadIdx.x / groups_per_row;
+  const int g0 = groups_per_row >= 256 ? threadIdx.x : threadIdx.x % groups_per_row;
+  if (lane < lanes) {
+    for (int g = g0; g < groups_per_row; g += 256) {
+      float lo[8], hi[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { lo[j] = INFINITY; hi[j] = -INFINITY; }
+      for (int t = t0 + lane; t < t1; t += lanes) {
+        float x[8];
+        load8<DT>(k, (static_cast<int64_t>(b) * T + t) * row_elems + 8 * g, x);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float v = ABS ? fabsf(x[j]) : x[j];
+          lo[j] = fminf(lo[j], v);
+          hi[j] = fmaxf(hi[j], v);
+        }
+      }
+      if (lanes == 1) {
+        uint32_t* slot = mm + 2 * (static_cast<int64_t>(b) * row_elems + 8 * g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (!ABS) atomicMin(slot + 2 * j, ord_encode(lo[j]));
+          atomicMax(slot + 2 * j + 1, ord_encode(hi[j]));
+        }
+      } else {
+        float* f = s_fold + (static_cast<size_t>(lane) * row_elems + 8 * g) * 2;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { f[2 * j] = lo[j]; f[2 * j + 1] = hi[j]; }
+      }
     }
-    uint32_t* slot = mm + 2 * (static_cast<int64_t>(b) * row_elems + c);
-    if (!ABS) atomicMin(slot, ord_encode(lo));
-    atomicMax(slot + 1, ord_encode(hi));
+  }
+  if (lanes > 1) {
+    __syncthreads();
+    for (int c = threadIdx.x; c < row_elems; c += 256) {
+      float lo = INFINITY, hi = -INFINITY;
+      for (int l = 0; l < lanes; ++l) {
+        lo = fminf(lo, s_fold[(static_cast<size_t>(l) * row_elems + c) * 2]);
+        hi = fmaxf(hi, s_fold[(static_cast<size_t>(l) * row_elems + c) * 2 + 1]);
+      }
+      uint32_t* slot = mm + 2 * (static_cast<int64_t>(b) * row_elems + c);
+      if (!ABS) atomicMin(slot, ord_encode(lo));
+      atomicMax(slot + 1, ord_encode(hi));
+    }
   }
 }
 
-// q2: finalise (scale, zero) per channel, then encode four channels per thread
+// q2: finalise (scale, zero) per channel
 __global__ void q2_finalize_kernel(const uint32_t* mm, int n, int dt, void* scale, void* zero) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -78,90 +142,143 @@ __global__ void q2_finalize_kernel(const uint32_t* mm, int n, int dt, void* scal
   store_elem(zero, i, dt, z);
 }
 
-__global__ void __launch_bounds__(256) q2_encode_kernel(const void* __restrict__ k, int dt, int T, int row_elems,
-                                                        int64_t n_quads, int fp8, const void* __restrict__ scale,
-                                                        const void* __restrict__ zero, uint8_t* __restrict__ codes,
-                                                        uint8_t* __restrict__ res, RowMap map) {
-  const int quads_per_row = row_elems / 4;
-  for (int64_t qd = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; qd < n_quads;
-       qd += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t row = qd / quads_per_row;          // b*T + t
-    const int c = static_cast<int>(qd % quads_per_row) * 4;
-    const int64_t b = row / T;
-    const int64_t e = row * row_elems + c;
-    const int64_t sidx = b * row_elems + c;
-    uint32_t byte = 0;
-    uint32_t r4 = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint8_t r;
-      byte |= q2_encode(load_elem(k, e + j, dt), load_elem(scale, sidx + j, dt), load_elem(zero, sidx + j, dt), dt, fp8,
-                        &r) << (2 * j);
-      r4 |= static_cast<uint32_t>(r) << (8 * j);
-    }
-    const int64_t oq = map(row) * quads_per_row + c / 4;
-    codes[oq] = static_cast<uint8_t>(byte);
-    reinterpret_cast<uint32_t*>(res)[oq] = r4;
-  }
-}
-
-// element-pair kernels (fp8fp8, fp4, nf4): thread handles 4 consecutive elements
-template <int KIND>   // 0 fp8fp8, 1 fp4, 2 nf4
-__global__ void __launch_bounds__(256) quad_encode_kernel(const void* __restrict__ k, int dt, int T, int row_elems,
-                                                          int64_t n_quads, int fp8, const uint32_t* __restrict__ mm,
-                                                          uint8_t* __restrict__ codes, uint8_t* __restrict__ res,
-                                                          RowMap map) {
-  const int quads_per_row = row_elems / 4;
-  for (int64_t qd = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; qd < n_quads;
-       qd += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t row = qd / quads_per_row;
-    const int c = static_cast<int>(qd % quads_per_row) * 4;
-    const int64_t e = row * row_elems + c;
-    uint32_t r4 = 0, c4 = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float x = load_elem(k, e + j, dt);
-      uint8_t r;
-      if (KIND == 0) {
-        uint8_t base;
-        fp8fp8_encode(x, fp8, &base, &r);
-        c4 |= static_cast<uint32_t>(base) << (8 * j);
-      } else if (KIND == 1) {
-        c4 |= fp4_encode(x, dt, fp8, &r) << (4 * j);
-      } else {
-        const int64_t b = row / T;
-        const float amax = fmaxf(ord_decode(mm[2 * (b * row_elems + c + j) + 1]), 1e-6f);
-        c4 |= nf4_encode_elem(x, amax, fp8, &r) << (4 * j);
-      }
-      r4 |= static_cast<uint32_t>(r) << (8 * j);
-    }
-    const int64_t oq = map(row) * quads_per_row + c / 4;
-    if (KIND == 0) reinterpret_cast<uint32_t*>(codes)[oq] = c4;
-    else reinterpret_cast<uint16_t*>(codes)[oq] = static_cast<uint16_t>(c4);
-    reinterpret_cast<uint32_t*>(res)[oq] = r4;
-  }
-}
-
 __global__ void nf4_finalize_kernel(const uint32_t* mm, int n, int dt, void* scale) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) store_elem(scale, i, dt, fmaxf(ord_decode(mm[2 * i + 1]), 1e-6f));
 }
 
-// nvfp4: one block per (b, page, kv-head): absmax over page x 128, then encode
-__global__ void __launch_bounds__(256) nvfp4_kernel(const void* __restrict__ k, int dt, int T, int HKV, int page,
-                                                    int fp8, uint8_t* __restrict__ codes, void* __restrict__ scale,
+// Encode pass of q2 / fp8fp8 / fp4 / nf4: a block walks token rows, a thread takes one group of
+// eight channels of the row.  Two rows are in flight per thread.
+enum { kEncFp8 = 0, kEncFp4 = 1, kEncNf4 = 2, kEncQ2 = 3 };
+
+template <int F8>
+__device__ __forceinline__ uint2 narrow8(const float (&r)[8]) {
+  return make_uint2(f32x2_to_fp8x2<F8>(r[0], r[1]) | (f32x2_to_fp8x2<F8>(r[2], r[3]) << 16),
+                    f32x2_to_fp8x2<F8>(r[4], r[5]) | (f32x2_to_fp8x2<F8>(r[6], r[7]) << 16));
+}
+
+// NF4 level of idx from a table spread over the lanes of the warp (lane i < 16 holds level i)
+__device__ __forceinline__ float nf4_level_shfl(float lane_level, uint32_t idx) {
+  return __shfl_sync(0xffffffffu, lane_level, static_cast<int>(idx));
+}
+
+template <int KIND, int DT, int F8>
+__device__ __forceinline__ void encode8(const float (&x)[8], const float (&p0)[8], const float (&p1)[8],
+                                        float lane_level, uint8_t* __restrict__ codes, uint8_t* __restrict__ res,
+                                        int64_t out_group, bool active) {
+  float r[8];
+  uint32_t c = 0, c_hi = 0;
+  if (KIND == kEncFp8) {
+    const uint2 base = narrow8<F8>(x);
+    c = base.x; c_hi = base.y;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 lo = fp8x2_to_f32x2<F8>((j < 2 ? base.x : base.y) >> (16 * (j & 1)));
+      r[2 * j] = x[2 * j] - lo.x;
+      r[2 * j + 1] = x[2 * j + 1] - lo.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (KIND == kEncFp4) {
+        c |= fp4_encode_f(x[j], DT, &r[j]) << (4 * j);
+      } else if (KIND == kEncNf4) {
+        const uint32_t idx = nf4_encode(x[j] / p0[j]);
+        r[j] = nf4_residual_f(x[j], nf4_level_shfl(lane_level, idx), p0[j]);
+        c |= idx << (4 * j);
+      } else {
+        c |= q2_encode_f(x[j], p0[j], p1[j], DT, &r[j]) << (2 * j);
+      }
+    }
+  }
+  if (!active) return;
+  if (KIND == kEncFp8) reinterpret_cast<uint2*>(codes)[out_group] = make_uint2(c, c_hi);
+  else if (KIND == kEncQ2) reinterpret_cast<uint16_t*>(codes)[out_group] = static_cast<uint16_t>(c);
+  else reinterpret_cast<uint32_t*>(codes)[out_group] = c;
+  reinterpret_cast<uint2*>(res)[out_group] = narrow8<F8>(r);
+}
+
+template <int KIND, int DT, int F8>
+__global__ void __launch_bounds__(256) encode_rows_kernel(const void* __restrict__ k, uint32_t rows, int T,
+                                                          int groups_per_row, const void* __restrict__ aux0,
+                                                          const void* __restrict__ aux1, uint8_t* __restrict__ codes,
+                                                          uint8_t* __restrict__ res, RowMap map) {
+  // aux0 / aux1: q2 scale / zero in K's dtype, nf4 the min/max scratch (ordered uints), else unused.
+  // Every thread runs every iteration (idle ones on zeros) so that warp shuffles stay legal.
+  const int row_elems = groups_per_row * 8;
+  const int rows_per_iter = groups_per_row >= 256 ? 1 : 256 / groups_per_row;
+  const int sub = groups_per_row >= 256 ? 0 : threadIdx.x / groups_per_row;
+  const int g0 = groups_per_row >= 256 ? threadIdx.x : threadIdx.x % groups_per_row;
+  const uint32_t stride = gridDim.x * rows_per_iter;
+  const uint32_t n_iter = (rows + 2 * stride - 1) / (2 * stride);
+  const float lane_level = KIND == kEncNf4 ? nf4_level(threadIdx.x & 15) : 0.f;
+  for (uint32_t it = 0; it < n_iter; ++it) {
+    const uint32_t row_a = 2 * it * stride + blockIdx.x * rows_per_iter + sub;
+    const uint32_t row_b = row_a + stride;
+    for (int gb = 0; gb < groups_per_row; gb += 256) {
+      const int g = gb + g0;
+      const bool lane_ok = sub < rows_per_iter && g < groups_per_row;
+      const bool va = lane_ok && row_a < rows, vb = lane_ok && row_b < rows;
+      float xa[8], xb[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) xa[j] = xb[j] = 0.f;
+      if (va) load8<DT>(k, static_cast<int64_t>(row_a) * row_elems + 8 * g, xa);
+      if (vb) load8<DT>(k, static_cast<int64_t>(row_b) * row_elems + 8 * g, xb);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint32_t r = half ? row_b : row_a;
+        const bool valid = half ? vb : va;
+        const uint32_t b = r / static_cast<uint32_t>(T);
+        float p0[8], p1[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { p0[j] = 1.f; p1[j] = 0.f; }
+        if (valid && KIND == kEncQ2) {
+          load8<DT>(aux0, static_cast<int64_t>(b) * row_elems + 8 * g, p0);
+          load8<DT>(aux1, static_cast<int64_t>(b) * row_elems + 8 * g, p1);
+        } else if (valid && KIND == kEncNf4) {
+          const uint4* mmv = reinterpret_cast<const uint4*>(static_cast<const uint32_t*>(aux0) +
+                                                            2 * (static_cast<int64_t>(b) * row_elems + 8 * g));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 v = mmv[j];
+            p0[2 * j] = fmaxf(ord_decode(v.y), 1e-6f);
+            p0[2 * j + 1] = fmaxf(ord_decode(v.w), 1e-6f);
+          }
+        }
+        encode8<KIND, DT, F8>(half ? xb : xa, p0, p1, lane_level, codes, res,
+                              valid ? map(r) * groups_per_row + g : 0, valid);
+      }
+    }
+  }
+}
+
+// nvfp4: one block per (b, page, kv-head): absmax over page x 128, then encode.  With the usual
+// 64-token page a thread keeps its 32 elements in registers between the two phases.
+template <int DT, int F8>
+__global__ void __launch_bounds__(256) nvfp4_kernel(const void* __restrict__ k, int T, int HKV, int page,
+                                                    uint8_t* __restrict__ codes, void* __restrict__ scale,
                                                     uint8_t* __restrict__ res, RowMap map) {
   const int pg = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int n_pages = gridDim.x;
   const int t0 = pg * page, t1 = min(T, t0 + page);
-  const int n_pairs = (t1 - t0) * (D / 2);
+  const int n_groups = (t1 - t0) * (D / 8);
   __shared__ float s_red[8];
   __shared__ float s_scale;
+  constexpr int kHeld = 4;                          // groups a thread keeps in registers
+  float held[kHeld][8];
   float amax = 0.f;
-  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-    const int t = t0 + i / (D / 2), c = (i % (D / 2)) * 2;
-    const int64_t e = ((static_cast<int64_t>(b) * T + t) * HKV + h) * D + c;
-    amax = fmaxf(amax, fmaxf(fabsf(load_elem(k, e, dt)), fabsf(load_elem(k, e + 1, dt))));
+  for (int i = threadIdx.x, n = 0; i < n_groups; i += blockDim.x, ++n) {
+    const int t = t0 + i / (D / 8), c = (i % (D / 8)) * 8;
+    float x[8];
+    load8<DT>(k, ((static_cast<int64_t>(b) * T + t) * HKV + h) * D + c, x);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
+#pragma unroll
+    for (int m = 0; m < kHeld; ++m)
+      if (m == n) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) held[m][j] = x[j];
+      }
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
@@ -170,21 +287,32 @@ __global__ void __launch_bounds__(256) nvfp4_kernel(const void* __restrict__ k, 
   if (threadIdx.x == 0) {
     float m = s_red[0];
     for (int w = 1; w < 8; ++w) m = fmaxf(m, s_red[w]);
-    const float s = nvfp4_scale(m, dt);
+    const float s = nvfp4_scale(m, DT);
     s_scale = s;
-    store_elem(scale, (static_cast<int64_t>(b) * n_pages + pg) * HKV + h, dt, s);
+    store_elem(scale, (static_cast<int64_t>(b) * n_pages + pg) * HKV + h, DT, s);
   }
   __syncthreads();
   const float s = s_scale;
-  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-    const int t = t0 + i / (D / 2), c = (i % (D / 2)) * 2;
-    const int64_t e = ((static_cast<int64_t>(b) * T + t) * HKV + h) * D + c;
-    uint8_t r0, r1;
-    const uint32_t lo = nvfp4_encode(load_elem(k, e, dt), s, dt, fp8, &r0);
-    const uint32_t hi = nvfp4_encode(load_elem(k, e + 1, dt), s, dt, fp8, &r1);
-    const int64_t oe = (map(static_cast<int64_t>(b) * T + t) * HKV + h) * D + c;
-    codes[oe / 2] = static_cast<uint8_t>(lo | (hi << 4));
-    reinterpret_cast<uint16_t*>(res)[oe / 2] = static_cast<uint16_t>(r0 | (static_cast<uint32_t>(r1) << 8));
+  for (int i = threadIdx.x, n = 0; i < n_groups; i += blockDim.x, ++n) {
+    const int t = t0 + i / (D / 8), c = (i % (D / 8)) * 8;
+    float x[8];
+    if (n < kHeld) {
+#pragma unroll
+      for (int m = 0; m < kHeld; ++m)
+        if (m == n) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] = held[m][j];
+        }
+    } else {
+      load8<DT>(k, ((static_cast<int64_t>(b) * T + t) * HKV + h) * D + c, x);
+    }
+    float r[8];
+    uint32_t cw = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cw |= nvfp4_encode_f(x[j], s, DT, &r[j]) << (4 * j);
+    const int64_t og = ((map(static_cast<int64_t>(b) * T + t) * HKV + h) * D + c) / 8;
+    reinterpret_cast<uint32_t*>(codes)[og] = cw;
+    reinterpret_cast<uint2*>(res)[og] = narrow8<F8>(r);
   }
 }
 
@@ -201,60 +329,88 @@ int last_launch(const char* what) {
   return e == cudaSuccess ? FFA_OK : note_cuda_error(e, what);
 }
 
-unsigned stream_grid(int64_t n_threads) {
-  const int64_t blocks = (n_threads + 255) / 256;
-  return static_cast<unsigned>(blocks < 148 * 16 ? (blocks < 1 ? 1 : blocks) : 148 * 16);
-}
+// dispatch a kernel template over the runtime element type and fp8 format
+#define FFA_DISPATCH_DT_F8(dt, fp8, CALL)                                  \
+  do {                                                                      \
+    if ((dt) == FFA_BF16) { if ((fp8) == FFA_E4M3) { CALL(kBF16, kE4M3); } else { CALL(kBF16, kE5M2); } } \
+    else if ((dt) == FFA_F16) { if ((fp8) == FFA_E4M3) { CALL(kF16, kE4M3); } else { CALL(kF16, kE5M2); } } \
+    else { if ((fp8) == FFA_E4M3) { CALL(kF32, kE4M3); } else { CALL(kF32, kE5M2); } }                    \
+  } while (0)
 
 void launch_minmax(bool abs_only, const void* k, int dt, int B, int T, int HKV, uint32_t* mm, cudaStream_t st) {
   const int row_elems = HKV * D;
   const int n = B * row_elems;
   minmax_init_kernel<<<(n + 255) / 256, 256, 0, st>>>(mm, n);
-  // enough blocks to fill the GPU, at least 16 tokens per block
+  const int gpr = row_elems / 8;
+  const int lanes = gpr >= 256 ? 1 : 256 / gpr;
+  // enough blocks to fill the GPU, at least 16 tokens per token lane
   int tpb = (T + 148 * 8 - 1) / (148 * 8);
-  if (tpb < 16) tpb = 16;
+  if (tpb < 16 * lanes) tpb = 16 * lanes;
   dim3 grid((T + tpb - 1) / tpb, B);
-  if (abs_only) minmax_kernel<true><<<grid, 256, 0, st>>>(k, dt, T, row_elems, tpb, mm);
-  else minmax_kernel<false><<<grid, 256, 0, st>>>(k, dt, T, row_elems, tpb, mm);
+  const size_t smem = lanes > 1 ? static_cast<size_t>(lanes) * row_elems * 2 * sizeof(float) : 0;
+#define FFA_MINMAX(DT_, F8_)                                                                   \
+  if (abs_only) minmax_kernel<true, DT_><<<grid, 256, smem, st>>>(k, T, gpr, tpb, mm);         \
+  else minmax_kernel<false, DT_><<<grid, 256, smem, st>>>(k, T, gpr, tpb, mm)
+  FFA_DISPATCH_DT_F8(dt, FFA_E4M3, FFA_MINMAX);
+#undef FFA_MINMAX
 }
+
+template <int KIND>
+void launch_encode(const void* k, int dt, int fp8, int B, int T, int HKV, const void* aux0, const void* aux1,
+                   uint8_t* codes, uint8_t* residual, RowMap map, cudaStream_t st) {
+  const int gpr = HKV * D / 8;
+  const int rows_per_iter = gpr >= 256 ? 1 : 256 / gpr;
+  const uint32_t rows = static_cast<uint32_t>(B) * static_cast<uint32_t>(T);
+  int64_t blocks = (static_cast<int64_t>(rows) + 2 * rows_per_iter - 1) / (2 * rows_per_iter);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+#define FFA_ENCODE(DT_, F8_)                                                                              \
+  encode_rows_kernel<KIND, DT_, F8_><<<static_cast<unsigned>(blocks), 256, 0, st>>>(k, rows, T, gpr, aux0, aux1, codes, \
+                                                                                    residual, map)
+  FFA_DISPATCH_DT_F8(dt, fp8, FFA_ENCODE);
+#undef FFA_ENCODE
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int quantize_impl(int variant, const void* k, int dt, int B, int T, int HKV, int fp8, int page_size, uint8_t* codes,
                   void* scale, void* zero, uint8_t* residual, void* scratch, RowMap map, cudaStream_t st) {
   int rc = check_common(k, dt, B, T, HKV, fp8);
   if (rc) return rc;
   if (!codes || !residual) return FFA_E_NULL;
+  if (static_cast<int64_t>(B) * T >= (int64_t{1} << 31)) return FFA_E_LIMIT;
+  if (!aligned16(k) || !aligned16(codes) || !aligned16(residual) || !aligned16(scale) || !aligned16(zero) ||
+      !aligned16(scratch))
+    return FFA_E_ALIGN;
   const int row_elems = HKV * D, n = B * row_elems;
-  const int64_t n_quads = static_cast<int64_t>(B) * T * row_elems / 4;
   uint32_t* mm = static_cast<uint32_t*>(scratch);
   switch (variant) {
     case FFA_K_Q2:
       if (!scale || !zero || !scratch) return FFA_E_NULL;
       launch_minmax(false, k, dt, B, T, HKV, mm, st);
       q2_finalize_kernel<<<(n + 255) / 256, 256, 0, st>>>(mm, n, dt, scale, zero);
-      q2_encode_kernel<<<stream_grid(n_quads), 256, 0, st>>>(k, dt, T, row_elems, n_quads, fp8, scale, zero, codes,
-                                                             residual, map);
+      launch_encode<kEncQ2>(k, dt, fp8, B, T, HKV, scale, zero, codes, residual, map, st);
       return last_launch("ffa_quantize_q2");
     case FFA_K_FP8:
-      quad_encode_kernel<0><<<stream_grid(n_quads), 256, 0, st>>>(k, dt, T, row_elems, n_quads, fp8, nullptr, codes,
-                                                                  residual, map);
+      launch_encode<kEncFp8>(k, dt, fp8, B, T, HKV, nullptr, nullptr, codes, residual, map, st);
       return last_launch("ffa_quantize_fp8fp8");
     case FFA_K_FP4:
-      quad_encode_kernel<1><<<stream_grid(n_quads), 256, 0, st>>>(k, dt, T, row_elems, n_quads, fp8, nullptr, codes,
-                                                                  residual, map);
+      launch_encode<kEncFp4>(k, dt, fp8, B, T, HKV, nullptr, nullptr, codes, residual, map, st);
       return last_launch("ffa_quantize_fp4");
     case FFA_K_NF4:
       if (!scale || !scratch) return FFA_E_NULL;
       launch_minmax(true, k, dt, B, T, HKV, mm, st);
       nf4_finalize_kernel<<<(n + 255) / 256, 256, 0, st>>>(mm, n, dt, scale);
-      quad_encode_kernel<2><<<stream_grid(n_quads), 256, 0, st>>>(k, dt, T, row_elems, n_quads, fp8, mm, codes, residual,
-                                                                  map);
+      launch_encode<kEncNf4>(k, dt, fp8, B, T, HKV, mm, nullptr, codes, residual, map, st);
       return last_launch("ffa_quantize_nf4");
     case FFA_K_NVFP4: {
       if (!scale) return FFA_E_NULL;
       if (page_size <= 0) return FFA_E_SHAPE;
       if (HKV > 65535 || B > 65535) return FFA_E_LIMIT;
       dim3 grid((T + page_size - 1) / page_size, HKV, B);
-      nvfp4_kernel<<<grid, 256, 0, st>>>(k, dt, T, HKV, page_size, fp8, codes, scale, residual, map);
+#define FFA_NVFP4(DT_, F8_) nvfp4_kernel<DT_, F8_><<<grid, 256, 0, st>>>(k, T, HKV, page_size, codes, scale, residual, map)
+      FFA_DISPATCH_DT_F8(dt, fp8, FFA_NVFP4);
+#undef FFA_NVFP4
       return last_launch("ffa_quantize_nvfp4");
     }
     default:

@@ -32,7 +32,8 @@ enum {
   FFA_E_WORKSPACE = -4,   /* workspace too small */
   FFA_E_LAUNCH = -5,      /* the CUDA runtime refused the launch (see ffa_last_cuda_error) */
   FFA_E_VARIANT = -6,     /* unknown coarse-K format */
-  FFA_E_LIMIT = -7        /* size beyond a compiled-in maximum */
+  FFA_E_LIMIT = -7,       /* size beyond a compiled-in maximum */
+  FFA_E_ALIGN = -8        /* a tensor pointer is not 16-byte aligned */
 };
 
 /* element types */
