@@ -394,15 +394,20 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
         sc.z2[i] = pack_h2(sZ[32 * t + 2 * i], sZ[32 * t + 2 * i + 1]);
       }
     }
-    // sets the nvfp4 scale of a BS-token block (and whether the fp16 product is exact for it)
-    auto set_block_scale = [&](int blk) {
-      const float x = load_as_float(p.ks, (static_cast<int64_t>(b) * p.NTB + blk) * p.HKV + hkv, p.scale_dtype);
+    // nvfp4: the scale of a BS-token block, and (apply) whether the fp16 product is exact for it.  The
+    // main loop loads the next page's scale one iteration ahead so the global load is off the path
+    // to the prune decision.
+    auto load_block_scale = [&](int blk) -> float {
+      return load_as_float(p.ks, (static_cast<int64_t>(b) * p.NTB + blk) * p.HKV + hkv, p.scale_dtype);
+    };
+    auto apply_block_scale = [&](float x) {
       sc.page_scale = x;
       // e2m1 (2 significant bits) x scale fits fp16's 11 bits if the scale has at most 9 (bf16 has 8),
       // and stays a normal fp16 number if the scale is within [2^-13, 2^13)
       sc.page_fast = (__float_as_uint(x) & 0x7fffu) == 0u && fabsf(x) >= 1.220703125e-4f && fabsf(x) < 8192.f;
       sc.page_scale_h2 = pack_h2(x, x);
     };
+    auto set_block_scale = [&](int blk) { apply_block_scale(load_block_scale(blk)); };
 
     // ---- q operands (q is bf16 on this path) -------------------------------------------------------
     // B-fragment column n = g of n-tile nt is head 4nt + g/2, piece g&1 (hi / lo x16) for the fp8
@@ -542,6 +547,8 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
     // of slots 0 and 1 before they are refilled)
     for (int j = 2; j < kPB && j < n; ++j) issue_base(j);
 
+    float ks_next = 0.f;
+    if (FMT == FFA_K_NVFP4) ks_next = load_block_scale((page_begin * kPage) / p.BS);
     for (int it = 0; it < n + kDA; ++it) {
       const int j = it, r = it - kDA;
       if (j + kPB < n) issue_base(j + kPB);
@@ -555,7 +562,10 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       if (do_score) {
         const int page = page_begin + j;
         wait_fill(base_slot(j), 2, it);
-        if (FMT == FFA_K_NVFP4) set_block_scale((page * kPage) / p.BS);
+        if (FMT == FFA_K_NVFP4) {
+          apply_block_scale(ks_next);
+          if (j + 1 < n) ks_next = load_block_scale(((page + 1) * kPage) / p.BS);
+        }
         coarse_dots(dc, smem + base_slot(j) * L::kBaseSlot, warp);
         const int tok = page * kPage + 16 * warp + g;
 #pragma unroll

@@ -20,7 +20,6 @@
 // warps 2..5 = epilogue (TMEM lane quarter = warp % 4).  Every mbarrier wait is bounded.
 #include <cuda.h>
 
-#include <cstdlib>
 #include "ffa_common.cuh"
 #include "ffa_numeric.h"
 
@@ -63,7 +62,6 @@ struct KprojParams {
   int m_tiles, n_split;
   int io_dtype;          // FFA_F16 | FFA_BF16: h, W, bias
   int rope_dtype;        // dtype of cos/sin; the RoPE arithmetic and k_out use promote(io, rope)
-  int debug;
 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -169,12 +167,34 @@ template <> struct Pack16<FFA_F16> {
   static __device__ __forceinline__ float2 to_floats(T2 v) { return __half22float2(v); }
 };
 
+// cos / sin of one token for 32 consecutive channels, as loaded (16-byte loads)
+template <int ROPE> struct RopeTables;
+template <> struct RopeTables<FFA_F32> {
+  float4 c[8], s[8];
+  __device__ __forceinline__ void load(const KprojParams& p, int64_t tok, int ch0) {
+    const float4* c4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.cos) + tok * kHeadDim + ch0);
+    const float4* s4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.sin) + tok * kHeadDim + ch0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { c[i] = c4[i]; s[i] = s4[i]; }
+  }
+};
+struct RopeTables16 {
+  uint4 c[4], s[4];
+  __device__ __forceinline__ void load(const KprojParams& p, int64_t tok, int ch0) {
+    const uint4* c4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.cos) + tok * kHeadDim + ch0);
+    const uint4* s4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.sin) + tok * kHeadDim + ch0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { c[i] = c4[i]; s[i] = s4[i]; }
+  }
+};
+template <> struct RopeTables<FFA_BF16> : RopeTables16 {};
+template <> struct RopeTables<FFA_F16> : RopeTables16 {};
+
 template <int IO, int ROPE>
-__device__ __forceinline__ void rope_store_32_t(const float (&acc)[32], const KprojParams& p, int64_t m, int n_base,
-                                                int ch0) {
+__device__ __forceinline__ void rope_apply_store(const float (&acc)[32], const RopeTables<ROPE>& tab,
+                                                 const KprojParams& p, int64_t m, int n_base, int ch0) {
   using P = Pack16<IO>;
   using T2 = typename P::T2;
-  const int64_t tok = m % p.T;
   const int64_t o = m * p.N + n_base + ch0;
   // activations: fp32 accumulator (+ bias) rounded to the activation dtype, as packed pairs
   T2 x2[16];
@@ -194,14 +214,12 @@ __device__ __forceinline__ void rope_store_32_t(const float (&acc)[32], const Kp
 #pragma unroll
     for (int i = 0; i < 16; ++i) x2[i] = P::from_floats(acc[2 * i], acc[2 * i + 1]);
   }
-  if (ROPE != FFA_F32) {
-    const uint4* c4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.cos) + tok * kHeadDim + ch0);
-    const uint4* s4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.sin) + tok * kHeadDim + ch0);
+  if constexpr (ROPE != FFA_F32) {
     uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.k_out) + o);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 c = c4[i], s = s4[i];
-      const uint32_t cw[4] = {c.x, c.y, c.z, c.w}, sw[4] = {s.x, s.y, s.z, s.w};
+      const uint32_t cw[4] = {tab.c[i].x, tab.c[i].y, tab.c[i].z, tab.c[i].w};
+      const uint32_t sw[4] = {tab.s[i].x, tab.s[i].y, tab.s[i].z, tab.s[i].w};
       uint32_t w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -216,12 +234,10 @@ __device__ __forceinline__ void rope_store_32_t(const float (&acc)[32], const Kp
       dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
     }
   } else {
-    const float4* c4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.cos) + tok * kHeadDim + ch0);
-    const float4* s4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.sin) + tok * kHeadDim + ch0);
     float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.k_out) + o);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float4 c = c4[i], s = s4[i];
+      const float4 c = tab.c[i], s = tab.s[i];
       const float2 xa = P::to_floats(x2[2 * i]), xb = P::to_floats(x2[2 * i + 1]);
       float4 r;
       r.x = __fadd_rn(__fmul_rn(xa.x, c.x), __fmul_rn(-xa.y, s.x));
@@ -231,6 +247,14 @@ __device__ __forceinline__ void rope_store_32_t(const float (&acc)[32], const Kp
       dst[i] = r;
     }
   }
+}
+
+template <int IO, int ROPE>
+__device__ __forceinline__ void rope_store_32_t(const float (&acc)[32], const KprojParams& p, int64_t m, int n_base,
+                                                int ch0) {
+  RopeTables<ROPE> tab;
+  tab.load(p, m % p.T, ch0);
+  rope_apply_store<IO, ROPE>(acc, tab, p, m, n_base, ch0);
 }
 
 __device__ __forceinline__ void rope_store_32(const float (&acc)[32], const KprojParams& p, int64_t m, int n_base,
@@ -244,11 +268,56 @@ __device__ __forceinline__ void rope_store_32(const float (&acc)[32], const Kpro
   }
 }
 
+// Fused epilogue of one token row of a finished [128, BN] accumulator: the heads of the tile share
+// the row's cos/sin, so each 32-channel slice of the tables is loaded once (the next slice while the
+// current one is used) and applied to every head.  All 32 lanes run the TMEM loads; rows beyond M
+// only skip the global loads and stores.  The accumulator is released once the last TMEM load has landed.
+template <int IO, int ROPE, int BN>
+__device__ __forceinline__ void epilogue_row(const KprojParams& p, uint32_t taddr, int64_t m, int n0,
+                                             uint32_t bar_release, int lane) {
+  constexpr int kHeads = BN / kHeadDim;
+  constexpr int kSlices = kHeadDim / 32;
+  const bool valid = m < p.M;
+  const int64_t tok = valid ? m % p.T : 0;
+  auto one_slice = [&](int c, const RopeTables<ROPE>& tab) {
+#pragma unroll
+    for (int hd = 0; hd < kHeads; ++hd) {
+      float v[32];
+      tmem_ld32(v, taddr + hd * kHeadDim + 32 * c);
+      if (c == kSlices - 1 && hd == kHeads - 1) {
+        // everything is in registers: hand the accumulator back to the MMA warp
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_release) : "memory");
+      }
+      if (valid) rope_apply_store<IO, ROPE>(v, tab, p, m, n0 + hd * kHeadDim, 32 * c);
+    }
+  };
+  if constexpr (ROPE == FFA_F32) {
+    // fp32 tables take 64 registers per slice: one slice at a time
+#pragma unroll 1
+    for (int c = 0; c < kSlices; ++c) {
+      RopeTables<ROPE> tab;
+      if (valid) tab.load(p, tok, 32 * c);
+      one_slice(c, tab);
+    }
+  } else {
+    // 16-bit tables (32 registers per slice) are double-buffered
+    RopeTables<ROPE> tab[2];
+    if (valid) tab[0].load(p, tok, 0);
+#pragma unroll
+    for (int c = 0; c < kSlices; ++c) {
+      if (valid && c + 1 < kSlices) tab[(c + 1) & 1].load(p, tok, 32 * (c + 1));
+      one_slice(c, tab[c & 1]);
+    }
+  }
+}
+
 // Persistent kernel: work item w -> (m tile, n tile, k split); CTA c takes items c, c + grid, ...
 // With n_split == 1 the epilogue is fused (bias, rounding, RoPE, store K); with n_split > 1 (few
 // tokens: the GEMM is then a stream over W_k and needs more CTAs than output tiles) each item
 // stores its fp32 partial tile and kproj_finish_kernel adds the splits and applies the epilogue.
-template <int BN>
+template <int BN, int IO, int ROPE>
 __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_constant__ KprojParams p,
                                                                const __grid_constant__ CUtensorMap tm_a,
                                                                const __grid_constant__ CUtensorMap tm_b) {
@@ -304,7 +373,6 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
         for (int k = 0; k < k_iters; ++k, ++it) {
           const int s = it % kStages;
           if (it >= kStages) timed_out |= !mbar_wait(bar_empty + 8 * s, ((it / kStages) - 1) & 1, timed_out);
-          if (p.debug & 1) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_full + 8 * s) : "memory"); continue; }
           mbar_expect_tx(bar_full + 8 * s, TL::kStageBytes);
           tma_load_2d(smem_u32(a_tile(s)), &tm_a, k0 + k * kBK, m0, bar_full + 8 * s);
           tma_load_2d(smem_u32(b_tile(s)), &tm_b, k0 + k * kBK, n0, bar_full + 8 * s);
@@ -314,7 +382,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
   } else if (warp == 1) {
     // ---- MMA issuer -----------------------------------------------------------------------------
     if (lane == 0) {
-      const uint32_t idesc = instr_desc(p.io_dtype == FFA_BF16 ? 1u : 0u, kBN);
+      const uint32_t idesc = instr_desc(IO == FFA_BF16 ? 1u : 0u, kBN);
       int it = 0, local = 0;
       for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++local) {
         const int buf = local & 1;
@@ -329,7 +397,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
           const uint64_t da = smem_desc_sw128(smem_u32(a_tile(s)));
           const uint64_t db = smem_desc_sw128(smem_u32(b_tile(s)));
 #pragma unroll
-          for (int kk = 0; kk < kBK / 16; ++kk) if (!(p.debug & 2)) umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < kBK / 16; ++kk) umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
           umma_commit(bar_empty + 8 * s);        // frees the stage once these MMAs have read it
         }
         umma_commit(bar_tfull + 8 * buf);        // accumulator complete
@@ -347,21 +415,22 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
       const int64_t m = static_cast<int64_t>(m0) + row;
       timed_out |= !mbar_wait(bar_tfull + 8 * buf, (local >> 1) & 1, timed_out);
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * kBN;
+      const uint32_t bar_release = bar_tempty + 8 * buf;
+      if (p.n_split == 1) {
+        epilogue_row<IO, ROPE, kBN>(p, taddr, m, n0, bar_release, lane);
+      } else {
+        const int split = w % p.n_split;
 #pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
-        float v[32];
-        tmem_ld32(v, tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * kBN + 32 * c);
-        if (c == kBN / 32 - 1) {
-          // everything is in registers: hand the accumulator back to the MMA warp
-          asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-          __syncwarp();
-          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_tempty + 8 * buf) : "memory");
-        }
-        if (m < p.M && !(p.debug & 4)) {
-          if (p.n_split == 1) {
-            rope_store_32(v, p, m, n0 + ((32 * c) / kHeadDim) * kHeadDim, (32 * c) % kHeadDim);
-          } else {
-            const int split = w % p.n_split;
+        for (int c = 0; c < kBN / 32; ++c) {
+          float v[32];
+          tmem_ld32(v, taddr + 32 * c);
+          if (c == kBN / 32 - 1) {
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_release) : "memory");
+          }
+          if (m < p.M) {
             float4* dst = reinterpret_cast<float4*>(p.partial + (static_cast<int64_t>(split) * p.M + m) * p.N + n0 + 32 * c);
 #pragma unroll
             for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -514,23 +583,38 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   p.m_tiles = static_cast<int>(m_tiles);
   p.n_split = bn == 256 ? 1 : plan_split(M, N, a->H / kBK);
   p.io_dtype = a->io_dtype; p.rope_dtype = a->rope_dtype;
-  { const char* e = getenv("FFA_KPROJ_DEBUG"); p.debug = e ? atoi(e) : 0; }
 
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kproj_rope_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Tile<128>::kBytes);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(kproj_rope_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<256>::kBytes);
-    if (e != cudaSuccess) return note_cuda_error(e, "cudaFuncSetAttribute(kproj_rope)");
-    configured[dev] = true;
-  }
   const int64_t items = static_cast<int64_t>(p.m_tiles) * (N / bn) * p.n_split;
   const unsigned grid = static_cast<unsigned>(items < sm_count() ? items : sm_count());
-  if (bn == 256) kproj_rope_kernel<256><<<grid, kThreadsK, Tile<256>::kBytes, st>>>(p, ma, mb);
-  else kproj_rope_kernel<128><<<grid, kThreadsK, Tile<128>::kBytes, st>>>(p, ma, mb);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  // one kernel per (tile width, activation dtype, table dtype); each raises its shared-memory limit
+  // the first time it runs on a device
+#define FFA_KPROJ_LAUNCH(BN_, IO_, ROPE_, SLOT_)                                                                   \
+  do {                                                                                                             \
+    static bool configured[64] = {};                                                                               \
+    if (dev >= 0 && dev < 64 && !configured[dev]) {                                                                \
+      cudaError_t ce = cudaFuncSetAttribute(kproj_rope_kernel<BN_, IO_, ROPE_>,                                     \
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<BN_>::kBytes);       \
+      if (ce != cudaSuccess) return note_cuda_error(ce, "cudaFuncSetAttribute(kproj_rope)");                       \
+      configured[dev] = true;                                                                                      \
+    }                                                                                                              \
+    kproj_rope_kernel<BN_, IO_, ROPE_><<<grid, kThreadsK, Tile<BN_>::kBytes, st>>>(p, ma, mb);                      \
+  } while (0)
+#define FFA_KPROJ_BN(BN_)                                                                                          \
+  do {                                                                                                             \
+    if (a->io_dtype == FFA_BF16) {                                                                                 \
+      if (a->rope_dtype == FFA_F32) FFA_KPROJ_LAUNCH(BN_, FFA_BF16, FFA_F32, 0);                                   \
+      else FFA_KPROJ_LAUNCH(BN_, FFA_BF16, FFA_BF16, 1);                                                           \
+    } else {                                                                                                       \
+      if (a->rope_dtype == FFA_F32) FFA_KPROJ_LAUNCH(BN_, FFA_F16, FFA_F32, 2);                                    \
+      else FFA_KPROJ_LAUNCH(BN_, FFA_F16, FFA_F16, 3);                                                             \
+    }                                                                                                              \
+  } while (0)
+  if (bn == 256) FFA_KPROJ_BN(256);
+  else FFA_KPROJ_BN(128);
+#undef FFA_KPROJ_BN
+#undef FFA_KPROJ_LAUNCH
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return note_cuda_error(e, "kproj_rope launch");
   if (p.n_split > 1) {
