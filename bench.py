@@ -283,7 +283,7 @@ def run_kproj(args, wl_name: str, wl: dict) -> dict:
                 "note": "few-token projection: streaming the 8 MiB weight from HBM is the floor; launch latency dominates"}
         metric, unit, value = "kproj_rope_quantize_TBps", "TB/s", byt / per_step_s / 1e12
         e2e_value = byt / s_e2e / 1e12
-    n_quant = {"q2": 4, "fp8": 1}[variant]
+    n_quant = {"q2": 4, "fp8": 0}[variant]            # fp8fp8 is quantised inside the GEMM epilogue
     n_gemm = 1 if T >= 4096 else 2                     # few-token shapes add the split-k finish kernel
     return {
         "metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": steps, "warmup": W,

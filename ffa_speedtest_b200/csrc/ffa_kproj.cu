@@ -62,7 +62,23 @@ struct KprojParams {
   int m_tiles, n_split;
   int io_dtype;          // FFA_F16 | FFA_BF16: h, W, bias
   int rope_dtype;        // dtype of cos/sin; the RoPE arithmetic and k_out use promote(io, rope)
+  // quantisation inside the epilogue (elementwise formats with 16-bit K): the codes and residual of
+  // token row m go to row slot_table[b][t / 64] * 64 + t % 64 of the pools (row m without a table)
+  uint8_t* codes;
+  uint8_t* residual;
+  const int32_t* slot_table;
+  int slot_stride;
 };
+
+// What the epilogue emits besides (or instead of) K: nothing, fp8 base + fp8 residual, or e2m1
+// codes + fp8 residual; the fp8 format is part of the mode so the conversions are compile-time.
+enum { kQuantNone = 0, kQuantFp8E4 = 1, kQuantFp8E5 = 2, kQuantFp4E4 = 3, kQuantFp4E5 = 4 };
+
+__device__ __forceinline__ int64_t out_row_of(const KprojParams& p, int64_t m) {
+  if (!p.slot_table) return m;
+  const int64_t b = m / p.T, t = m % p.T;
+  return static_cast<int64_t>(p.slot_table[b * p.slot_stride + t / kPage]) * kPage + t % kPage;
+}
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
@@ -190,9 +206,11 @@ struct RopeTables16 {
 template <> struct RopeTables<FFA_BF16> : RopeTables16 {};
 template <> struct RopeTables<FFA_F16> : RopeTables16 {};
 
-template <int IO, int ROPE>
+template <int IO, int ROPE, int QUANT>
 __device__ __forceinline__ void rope_apply_store(const float (&acc)[32], const RopeTables<ROPE>& tab,
-                                                 const KprojParams& p, int64_t m, int n_base, int ch0) {
+                                                 const KprojParams& p, int64_t m, int64_t out_row, int n_base,
+                                                 int ch0) {
+  static_assert(QUANT == kQuantNone || ROPE != FFA_F32, "the fused quantisers take 16-bit K");
   using P = Pack16<IO>;
   using T2 = typename P::T2;
   const int64_t o = m * p.N + n_base + ch0;
@@ -231,7 +249,34 @@ __device__ __forceinline__ void rope_apply_store(const float (&acc)[32], const R
         const T2 r = __hadd2(a, b);
         w[j] = *reinterpret_cast<const uint32_t*>(&r);
       }
-      dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      if (p.k_out) dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      if constexpr (QUANT != kQuantNone) {
+        // the reference quantisers on these eight K values (ffa_numeric.h has the per-element rules)
+        constexpr int kF8 = (QUANT == kQuantFp8E4 || QUANT == kQuantFp4E4) ? num::kE4M3 : num::kE5M2;
+        float kf[8], rf[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = P::to_floats(*reinterpret_cast<const T2*>(&w[j]));
+          kf[2 * j] = f.x; kf[2 * j + 1] = f.y;
+        }
+        const int64_t oe = out_row * p.N + n_base + ch0 + 8 * i;       // element index in the pools
+        if constexpr (QUANT == kQuantFp8E4 || QUANT == kQuantFp8E5) {
+          const uint2 base = num::narrow8<kF8>(kf);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 d = num::fp8x2_to_f32x2<kF8>((j < 2 ? base.x : base.y) >> (16 * (j & 1)));
+            rf[2 * j] = kf[2 * j] - d.x;
+            rf[2 * j + 1] = kf[2 * j + 1] - d.y;
+          }
+          *reinterpret_cast<uint2*>(p.codes + oe) = base;
+        } else {
+          uint32_t c = 0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) c |= num::fp4_encode_f(kf[j], IO, &rf[j]) << (4 * j);
+          *reinterpret_cast<uint32_t*>(p.codes + oe / 2) = c;
+        }
+        *reinterpret_cast<uint2*>(p.residual + oe) = num::narrow8<kF8>(rf);
+      }
     }
   } else {
     float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.k_out) + o);
@@ -249,36 +294,26 @@ __device__ __forceinline__ void rope_apply_store(const float (&acc)[32], const R
   }
 }
 
-template <int IO, int ROPE>
+template <int IO, int ROPE, int QUANT>
 __device__ __forceinline__ void rope_store_32_t(const float (&acc)[32], const KprojParams& p, int64_t m, int n_base,
                                                 int ch0) {
   RopeTables<ROPE> tab;
   tab.load(p, m % p.T, ch0);
-  rope_apply_store<IO, ROPE>(acc, tab, p, m, n_base, ch0);
-}
-
-__device__ __forceinline__ void rope_store_32(const float (&acc)[32], const KprojParams& p, int64_t m, int n_base,
-                                              int ch0) {
-  if (p.io_dtype == FFA_BF16) {
-    if (p.rope_dtype == FFA_F32) rope_store_32_t<FFA_BF16, FFA_F32>(acc, p, m, n_base, ch0);
-    else rope_store_32_t<FFA_BF16, FFA_BF16>(acc, p, m, n_base, ch0);
-  } else {
-    if (p.rope_dtype == FFA_F32) rope_store_32_t<FFA_F16, FFA_F32>(acc, p, m, n_base, ch0);
-    else rope_store_32_t<FFA_F16, FFA_F16>(acc, p, m, n_base, ch0);
-  }
+  rope_apply_store<IO, ROPE, QUANT>(acc, tab, p, m, QUANT != kQuantNone ? out_row_of(p, m) : m, n_base, ch0);
 }
 
 // Fused epilogue of one token row of a finished [128, BN] accumulator: the heads of the tile share
 // the row's cos/sin, so each 32-channel slice of the tables is loaded once (the next slice while the
 // current one is used) and applied to every head.  All 32 lanes run the TMEM loads; rows beyond M
 // only skip the global loads and stores.  The accumulator is released once the last TMEM load has landed.
-template <int IO, int ROPE, int BN>
+template <int IO, int ROPE, int QUANT, int BN>
 __device__ __forceinline__ void epilogue_row(const KprojParams& p, uint32_t taddr, int64_t m, int n0,
                                              uint32_t bar_release, int lane) {
   constexpr int kHeads = BN / kHeadDim;
   constexpr int kSlices = kHeadDim / 32;
   const bool valid = m < p.M;
   const int64_t tok = valid ? m % p.T : 0;
+  const int64_t out_row = (valid && QUANT != kQuantNone) ? out_row_of(p, m) : m;
   auto one_slice = [&](int c, const RopeTables<ROPE>& tab) {
 #pragma unroll
     for (int hd = 0; hd < kHeads; ++hd) {
@@ -290,7 +325,7 @@ __device__ __forceinline__ void epilogue_row(const KprojParams& p, uint32_t tadd
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_release) : "memory");
       }
-      if (valid) rope_apply_store<IO, ROPE>(v, tab, p, m, n0 + hd * kHeadDim, 32 * c);
+      if (valid) rope_apply_store<IO, ROPE, QUANT>(v, tab, p, m, out_row, n0 + hd * kHeadDim, 32 * c);
     }
   };
   if constexpr (ROPE == FFA_F32) {
@@ -317,7 +352,7 @@ __device__ __forceinline__ void epilogue_row(const KprojParams& p, uint32_t tadd
 // With n_split == 1 the epilogue is fused (bias, rounding, RoPE, store K); with n_split > 1 (few
 // tokens: the GEMM is then a stream over W_k and needs more CTAs than output tiles) each item
 // stores its fp32 partial tile and kproj_finish_kernel adds the splits and applies the epilogue.
-template <int BN, int IO, int ROPE>
+template <int BN, int IO, int ROPE, int QUANT>
 __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_constant__ KprojParams p,
                                                                const __grid_constant__ CUtensorMap tm_a,
                                                                const __grid_constant__ CUtensorMap tm_b) {
@@ -418,7 +453,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * kBN;
       const uint32_t bar_release = bar_tempty + 8 * buf;
       if (p.n_split == 1) {
-        epilogue_row<IO, ROPE, kBN>(p, taddr, m, n0, bar_release, lane);
+        epilogue_row<IO, ROPE, QUANT, kBN>(p, taddr, m, n0, bar_release, lane);
       } else {
         const int split = w % p.n_split;
 #pragma unroll 1
@@ -450,6 +485,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
 }
 
 // Adds the k-split partial tiles in split order and applies the epilogue; one thread per 32 channels.
+template <int IO, int ROPE, int QUANT>
 __global__ void __launch_bounds__(128) kproj_finish_kernel(const __grid_constant__ KprojParams p) {
   const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   const int groups = p.N / 32;
@@ -467,7 +503,7 @@ __global__ void __launch_bounds__(128) kproj_finish_kernel(const __grid_constant
       acc[4 * i] += x.x; acc[4 * i + 1] += x.y; acc[4 * i + 2] += x.z; acc[4 * i + 3] += x.w;
     }
   }
-  rope_store_32(acc, p, m, (n / kHeadDim) * kHeadDim, n % kHeadDim);
+  rope_store_32_t<IO, ROPE, QUANT>(acc, p, m, (n / kHeadDim) * kHeadDim, n % kHeadDim);
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -584,46 +620,70 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   p.n_split = bn == 256 ? 1 : plan_split(M, N, a->H / kBK);
   p.io_dtype = a->io_dtype; p.rope_dtype = a->rope_dtype;
 
+  // the elementwise formats are quantised inside the epilogue when K is 16-bit; K itself is then
+  // written only if the caller asked for it
+  int quant = kQuantNone;
+  if (need_quant && out_dt != FFA_F32 && (a->variant == FFA_K_FP8 || a->variant == FFA_K_FP4)) {
+    if (!a->codes || !a->residual) return FFA_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(a->codes) | reinterpret_cast<uintptr_t>(a->residual)) & 15u) return FFA_E_ALIGN;
+    quant = a->variant == FFA_K_FP8 ? (a->fp8_format == FFA_E4M3 ? kQuantFp8E4 : kQuantFp8E5)
+                                    : (a->fp8_format == FFA_E4M3 ? kQuantFp4E4 : kQuantFp4E5);
+    p.codes = static_cast<uint8_t*>(a->codes);
+    p.residual = static_cast<uint8_t*>(a->residual);
+    p.slot_table = a->slot_table;
+    p.slot_stride = a->slot_stride;
+    if (!a->k_rope_out) p.k_out = nullptr;
+  }
+
   const int64_t items = static_cast<int64_t>(p.m_tiles) * (N / bn) * p.n_split;
   const unsigned grid = static_cast<unsigned>(items < sm_count() ? items : sm_count());
+  const int64_t finish_threads = M * (N / 32);
+  const unsigned finish_grid = static_cast<unsigned>((finish_threads + 127) / 128);
   int dev = 0;
   cudaGetDevice(&dev);
-  // one kernel per (tile width, activation dtype, table dtype); each raises its shared-memory limit
-  // the first time it runs on a device
-#define FFA_KPROJ_LAUNCH(BN_, IO_, ROPE_, SLOT_)                                                                   \
+  // one kernel per (tile width, activation dtype, table dtype, fused quantiser); each raises its
+  // shared-memory limit the first time it runs on a device
+#define FFA_KPROJ_LAUNCH(BN_, IO_, ROPE_, Q_)                                                                      \
   do {                                                                                                             \
     static bool configured[64] = {};                                                                               \
     if (dev >= 0 && dev < 64 && !configured[dev]) {                                                                \
-      cudaError_t ce = cudaFuncSetAttribute(kproj_rope_kernel<BN_, IO_, ROPE_>,                                     \
+      cudaError_t ce = cudaFuncSetAttribute(kproj_rope_kernel<BN_, IO_, ROPE_, Q_>,                                 \
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<BN_>::kBytes);       \
       if (ce != cudaSuccess) return note_cuda_error(ce, "cudaFuncSetAttribute(kproj_rope)");                       \
       configured[dev] = true;                                                                                      \
     }                                                                                                              \
-    kproj_rope_kernel<BN_, IO_, ROPE_><<<grid, kThreadsK, Tile<BN_>::kBytes, st>>>(p, ma, mb);                      \
+    kproj_rope_kernel<BN_, IO_, ROPE_, Q_><<<grid, kThreadsK, Tile<BN_>::kBytes, st>>>(p, ma, mb);                  \
+    if (p.n_split > 1 && cudaPeekAtLastError() == cudaSuccess)                                                     \
+      kproj_finish_kernel<IO_, ROPE_, Q_><<<finish_grid, 128, 0, st>>>(p);                                         \
+  } while (0)
+#define FFA_KPROJ_Q(BN_, IO_)                                                                                      \
+  do {                                                                                                             \
+    switch (quant) {                                                                                               \
+      case kQuantFp8E4: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp8E4); break;                                       \
+      case kQuantFp8E5: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp8E5); break;                                       \
+      case kQuantFp4E4: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp4E4); break;                                       \
+      case kQuantFp4E5: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp4E5); break;                                       \
+      default: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantNone); break;                                                 \
+    }                                                                                                              \
   } while (0)
 #define FFA_KPROJ_BN(BN_)                                                                                          \
   do {                                                                                                             \
     if (a->io_dtype == FFA_BF16) {                                                                                 \
-      if (a->rope_dtype == FFA_F32) FFA_KPROJ_LAUNCH(BN_, FFA_BF16, FFA_F32, 0);                                   \
-      else FFA_KPROJ_LAUNCH(BN_, FFA_BF16, FFA_BF16, 1);                                                           \
+      if (a->rope_dtype == FFA_F32) FFA_KPROJ_LAUNCH(BN_, FFA_BF16, FFA_F32, kQuantNone);                          \
+      else FFA_KPROJ_Q(BN_, FFA_BF16);                                                                             \
     } else {                                                                                                       \
-      if (a->rope_dtype == FFA_F32) FFA_KPROJ_LAUNCH(BN_, FFA_F16, FFA_F32, 2);                                    \
-      else FFA_KPROJ_LAUNCH(BN_, FFA_F16, FFA_F16, 3);                                                             \
+      if (a->rope_dtype == FFA_F32) FFA_KPROJ_LAUNCH(BN_, FFA_F16, FFA_F32, kQuantNone);                           \
+      else FFA_KPROJ_Q(BN_, FFA_F16);                                                                              \
     }                                                                                                              \
   } while (0)
   if (bn == 256) FFA_KPROJ_BN(256);
   else FFA_KPROJ_BN(128);
 #undef FFA_KPROJ_BN
+#undef FFA_KPROJ_Q
 #undef FFA_KPROJ_LAUNCH
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return note_cuda_error(e, "kproj_rope launch");
-  if (p.n_split > 1) {
-    const int64_t threads = M * (N / 32);
-    kproj_finish_kernel<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, st>>>(p);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return note_cuda_error(e, "kproj_finish launch");
-  }
-  if (!need_quant) return FFA_OK;
+  if (!need_quant || quant != kQuantNone) return FFA_OK;
   return quantize_dispatch(a->variant, k_rope, out_dt, a->B, a->T, a->HKV, a->fp8_format, a->page_size,
                            static_cast<uint8_t*>(a->codes), a->scale, a->zero, static_cast<uint8_t*>(a->residual),
                            ws + k_bytes, a->slot_table, a->slot_stride, st);

@@ -334,6 +334,12 @@ __device__ __forceinline__ uint32_t f32x2_to_fp8x2(float a, float b) {
   }
   return out;
 }
+// eight floats -> eight fp8 bytes
+template <int F8>
+__device__ __forceinline__ uint2 narrow8(const float (&r)[8]) {
+  return make_uint2(f32x2_to_fp8x2<F8>(r[0], r[1]) | (f32x2_to_fp8x2<F8>(r[2], r[3]) << 16),
+                    f32x2_to_fp8x2<F8>(r[4], r[5]) | (f32x2_to_fp8x2<F8>(r[6], r[7]) << 16));
+}
 // two fp8 bytes -> two floats
 template <int F8>
 __device__ __forceinline__ float2 fp8x2_to_f32x2(uint32_t pair) {

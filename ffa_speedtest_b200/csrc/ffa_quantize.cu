@@ -151,12 +151,6 @@ __global__ void nf4_finalize_kernel(const uint32_t* mm, int n, int dt, void* sca
 // eight channels of the row.  Two rows are in flight per thread.
 enum { kEncFp8 = 0, kEncFp4 = 1, kEncNf4 = 2, kEncQ2 = 3 };
 
-template <int F8>
-__device__ __forceinline__ uint2 narrow8(const float (&r)[8]) {
-  return make_uint2(f32x2_to_fp8x2<F8>(r[0], r[1]) | (f32x2_to_fp8x2<F8>(r[2], r[3]) << 16),
-                    f32x2_to_fp8x2<F8>(r[4], r[5]) | (f32x2_to_fp8x2<F8>(r[6], r[7]) << 16));
-}
-
 // NF4 level of idx from a table spread over the lanes of the warp (lane i < 16 holds level i)
 __device__ __forceinline__ float nf4_level_shfl(float lane_level, uint32_t idx) {
   return __shfl_sync(0xffffffffu, lane_level, static_cast<int>(idx));

@@ -41,6 +41,21 @@ class DecodeWorkspace:
         self.threshold = torch.empty((B, HQ), dtype=torch.float32, device=device)
         self.pages_per_chunk = pages_per_chunk
 
+    def fits(self, B: int, T: int, HQ: int, HKV: int, V: int, BS: int, SBS: int, device, dtype,
+             pages_per_chunk: int) -> bool:
+        """True for the shape the workspace was made for and for shorter sequences of the same batch
+        (a cache that grows towards the allocated length)."""
+        kB, kT, kHQ, kHKV, kV, kBS, kSBS, kdev, kdt, kppc = self.key
+        if (B, HQ, HKV, V, BS, SBS, torch.device(device), dtype, pages_per_chunk) != \
+                (kB, kHQ, kHKV, kV, kBS, kSBS, kdev, kdt, kppc) or T > kT:
+            return False
+        return _lib.lib().ffa_decode_workspace_bytes(B, T, HQ, HKV, pages_per_chunk) <= self.scratch.numel()
+
+    def mask_view(self, B: int, HKV: int, ntbs: int) -> torch.Tensor:
+        """The kept-page mask of a call over ``ntbs`` pages per sequence (the buffer is sized for the
+        longest sequence; a call writes the first B*HKV*ntbs entries)."""
+        return self.mask.view(-1)[:B * HKV * ntbs].view(B, HKV, ntbs)
+
     def status(self) -> int:
         """Device status word (synchronises): 0 = ok, 1 = a bounded wait inside a kernel gave up."""
         return int(self.scratch[65280:65284].view(torch.int32).item())
@@ -145,7 +160,7 @@ def decode_call(
     if workspace is None:
         workspace = DecodeWorkspace(B, T, HQ, HKV, V, BS=BS, SBS=SBS, device=q.device, dtype=q.dtype,
                                     pages_per_chunk=pages_per_chunk)
-    elif workspace.key != (B, T, HQ, HKV, V, BS, SBS, q.device, q.dtype, pages_per_chunk):
+    elif not workspace.fits(B, T, HQ, HKV, V, BS, SBS, q.device, q.dtype, pages_per_chunk):
         raise ValueError("workspace was allocated for a different decode shape")
     o = workspace.o if out is None else out
     if o.shape != (B, HQ, V) or o.dtype != q.dtype or not o.is_contiguous():
@@ -184,8 +199,9 @@ def decode_call(
     _lib.check(_lib.lib().ffa_decode(a, _lib.current_stream(q.device)), "ffa_decode")
 
     if return_skip_ratio:
-        kept = workspace.mask.to(torch.int32).sum()
-        total = workspace.mask.numel()
+        mask = workspace.mask_view(B, HKV, NTBS)
+        kept = mask.to(torch.int32).sum()
+        total = mask.numel()
         skip_ratio = float((1.0 - (kept.float() / float(total))).item())
         return o, skip_ratio
     return o

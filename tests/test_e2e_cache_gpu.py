@@ -1,0 +1,44 @@
+"""Paged append-in-place fp8fp8 cache against the contiguous call on the same tokens."""
+import pytest
+import torch
+
+from ffa_speedtest_b200 import quantize as Q
+from ffa_speedtest_b200.fp8fp8.attn_kernel.attn_kernel_v1210_fused_bsz_fp8fp8 import attn_forward_decode_fp8fp8
+from ffa_speedtest_b200.fp8fp8.e2e.fp8fp8_cache import PagedFP8Fp8Cache
+from ffa_speedtest_b200.synth import make_decode_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("f8", [torch.float8_e5m2, torch.float8_e4m3fn])
+def test_prefill_then_token_by_token_matches_contiguous(f8):
+    B, T, HQ, HKV, D = 2, 333, 32, 8, 128
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, D, seed=11, device="cuda")
+    cache = PagedFP8Fp8Cache(B, HKV, max_seq_len=512, fp8_dtype=f8)
+    prefill = 300
+    cache.update(k[:, :prefill], v[:, :prefill], layer_idx=0)
+    for t in range(prefill, T):
+        cache.update(k[:, t:t + 1], v[:, t:t + 1], layer_idx=0)
+        if t in (prefill, 319, 320, T - 1):        # page boundary at 320
+            base, res = Q.quantize_k_fp8_fp8_residual(k[:, :t + 1].contiguous(), f8)
+            want = attn_forward_decode_fp8fp8(q, base, v[:, :t + 1].contiguous(), k_residual=res, BS=64, SBS=64, delta=8.0)
+            got = cache.decode(q, layer_idx=0, delta=8.0)
+            assert cache.get_seq_length() == t + 1
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+def test_crop_reset_and_capacity():
+    B, HKV, D = 1, 8, 128
+    q, k, v = make_decode_inputs(B, 130, 32, HKV, D, seed=3, device="cuda")
+    cache = PagedFP8Fp8Cache(B, HKV, max_seq_len=128)
+    cache.update(k[:, :100], v[:, :100], 0)
+    with pytest.raises(ValueError, match="capacity"):
+        cache.update(k[:, 100:130], v[:, 100:130], 0)
+    a = cache.decode(q, 0, delta=8.0).clone()
+    cache.update(k[:, 100:120], v[:, 100:120], 0)
+    cache.crop(100)
+    assert torch.equal(cache.decode(q, 0, delta=8.0), a)
+    cache.reset()
+    assert cache.get_seq_length() == 0
+    with pytest.raises(RuntimeError):
+        cache.decode(q, 0)
