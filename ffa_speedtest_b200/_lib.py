@@ -57,7 +57,7 @@ class FfaKprojArgs(C.Structure):
         ("B", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("HKV", C.c_int32), ("head_dim", C.c_int32),
         ("io_dtype", C.c_int32), ("rope_dtype", C.c_int32), ("fp8_format", C.c_int32), ("page_size", C.c_int32),
         ("h", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p),
-        ("slot_table", C.c_void_p), ("slot_stride", C.c_int32), ("reserved", C.c_int32),
+        ("slot_table", C.c_void_p), ("slot_stride", C.c_int32), ("slot_pos0", C.c_int32),
         ("codes", C.c_void_p), ("scale", C.c_void_p), ("zero", C.c_void_p), ("residual", C.c_void_p),
         ("k_rope_out", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),

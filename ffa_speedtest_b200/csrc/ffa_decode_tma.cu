@@ -201,12 +201,14 @@ __device__ __forceinline__ void dot_fp8(float (&out)[NT][2], const uint32_t (&qb
 }
 
 // fp16 values of channels kb..kb+3 of one token row of a 2-bit / 4-bit coarse tile
-template <int FMT>
+// FAST selects the packed-fp16 route of q2 / nvfp4 (the caller checked that it is exact enough, see
+// ScaleCtx); it is a template parameter so that the choice is one branch per page, not one per pair.
+template <int FMT, bool FAST>
 __device__ __forceinline__ void coarse_pair16(uint32_t& lo, uint32_t& hi, const uint32_t (&r)[4], int s, int kb,
                                               const ScaleCtx& sc) {
   if (FMT == FFA_K_Q2) {
     const uint32_t byte = (r[s >> 2] >> (8 * (s & 3))) & 0xffu;
-    if (sc.q2_fast) {
+    if (FAST) {
       lo = hfma2_u32(codes2_to_h2(byte & 0xfu), sc.s2[2 * s], sc.z2[2 * s]);
       hi = hfma2_u32(codes2_to_h2(byte >> 4), sc.s2[2 * s + 1], sc.z2[2 * s + 1]);
       return;
@@ -221,7 +223,7 @@ __device__ __forceinline__ void coarse_pair16(uint32_t& lo, uint32_t& hi, const 
       lo = e2m1x2_to_h2(two);
       hi = e2m1x2_to_h2(two >> 8);
     } else if (FMT == FFA_K_NVFP4) {
-      if (sc.page_fast) {
+      if (FAST) {
         lo = hmul2_u32(e2m1x2_to_h2(two), sc.page_scale_h2);
         hi = hmul2_u32(e2m1x2_to_h2(two >> 8), sc.page_scale_h2);
         return;
@@ -239,7 +241,7 @@ __device__ __forceinline__ void coarse_pair16(uint32_t& lo, uint32_t& hi, const 
 }
 
 // q . k_coarse for 2-bit / 4-bit formats: codes -> fp16 -> m16n8k16 against fp16 q (odd columns 0)
-template <int FMT, int NT>
+template <int FMT, int NT, bool FAST>
 __device__ __forceinline__ void dot_f16(float (&out)[NT][2], const uint32_t (&qh)[NT][8][2], const uint8_t* tile,
                                         const ScaleCtx& sc, int warp, int g, int t) {
   constexpr int ROW = Fmt<FMT>::kRow;
@@ -264,8 +266,8 @@ __device__ __forceinline__ void dot_f16(float (&out)[NT][2], const uint32_t (&qh
   for (int s = 0; s < 8; ++s) {
     const int kb = 32 * t + 4 * s;
     uint32_t alo, ahi, blo, bhi;
-    coarse_pair16<FMT>(alo, ahi, ra, s, kb, sc);
-    coarse_pair16<FMT>(blo, bhi, rb, s, kb, sc);
+    coarse_pair16<FMT, FAST>(alo, ahi, ra, s, kb, sc);
+    coarse_pair16<FMT, FAST>(blo, bhi, rb, s, kb, sc);
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) mma_f16(acc[nt][s & 1], alo, blo, ahi, bhi, qh[nt][s][0], qh[nt][s][1]);
   }
@@ -475,7 +477,9 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
     // unscaled coarse dots of one tile -> [nt][token g / g+8]; `slice` selects which 16 rows
     auto coarse_dots = [&](float (&out)[NT][2], const uint8_t* tile, int slice) {
       if constexpr (kFp8Coarse) dot_fp8<F8, NT>(out, qb, qinv, tile, slice, g, t);
-      else dot_f16<FMT, NT>(out, qh, tile, sc, slice, g, t);
+      else if (FMT == FFA_K_Q2 ? sc.q2_fast : (FMT == FFA_K_NVFP4 && sc.page_fast))
+        dot_f16<FMT, NT, true>(out, qh, tile, sc, slice, g, t);
+      else dot_f16<FMT, NT, false>(out, qh, tile, sc, slice, g, t);
     };
     auto to_log2 = [&](float d) -> float { return (d * p.sm_scale) * kLog2e; };
 

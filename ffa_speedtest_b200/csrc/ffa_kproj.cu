@@ -28,7 +28,7 @@ namespace ffa {
 // defined in ffa_quantize.cu
 int quantize_dispatch(int variant, const void* k, int k_dtype, int B, int T, int HKV, int fp8, int page_size,
                       uint8_t* codes, void* scale, void* zero, uint8_t* residual, void* scratch,
-                      const int32_t* slot_table, int slot_stride, cudaStream_t st);
+                      const int32_t* slot_table, int slot_stride, int slot_pos0, cudaStream_t st);
 
 namespace {
 
@@ -68,6 +68,7 @@ struct KprojParams {
   uint8_t* residual;
   const int32_t* slot_table;
   int slot_stride;
+  int slot_pos0;
 };
 
 // What the epilogue emits besides (or instead of) K: nothing, fp8 base + fp8 residual, or e2m1
@@ -76,7 +77,7 @@ enum { kQuantNone = 0, kQuantFp8E4 = 1, kQuantFp8E5 = 2, kQuantFp4E4 = 3, kQuant
 
 __device__ __forceinline__ int64_t out_row_of(const KprojParams& p, int64_t m) {
   if (!p.slot_table) return m;
-  const int64_t b = m / p.T, t = m % p.T;
+  const int64_t b = m / p.T, t = m % p.T + p.slot_pos0;
   return static_cast<int64_t>(p.slot_table[b * p.slot_stride + t / kPage]) * kPage + t % kPage;
 }
 
@@ -591,6 +592,8 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   if (a->io_dtype != FFA_F16 && a->io_dtype != FFA_BF16) return FFA_E_DTYPE;
   if (a->rope_dtype != FFA_F32 && a->rope_dtype != a->io_dtype) return FFA_E_DTYPE;
   if (!encode_fn()) return FFA_E_LAUNCH;
+  if (a->slot_table && a->slot_pos0 != 0 && a->variant != FFA_K_FP8 && a->variant != FFA_K_FP4) return FFA_E_VARIANT;
+  if (a->slot_table && a->slot_pos0 < 0) return FFA_E_SHAPE;
   const int64_t M = static_cast<int64_t>(a->B) * a->T;
   const int N = a->HKV * kHeadDim;
   if (M > 0x7fffffffLL) return FFA_E_LIMIT;
@@ -632,6 +635,7 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
     p.residual = static_cast<uint8_t*>(a->residual);
     p.slot_table = a->slot_table;
     p.slot_stride = a->slot_stride;
+    p.slot_pos0 = a->slot_table ? a->slot_pos0 : 0;
     if (!a->k_rope_out) p.k_out = nullptr;
   }
 
@@ -686,5 +690,5 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   if (!need_quant || quant != kQuantNone) return FFA_OK;
   return quantize_dispatch(a->variant, k_rope, out_dt, a->B, a->T, a->HKV, a->fp8_format, a->page_size,
                            static_cast<uint8_t*>(a->codes), a->scale, a->zero, static_cast<uint8_t*>(a->residual),
-                           ws + k_bytes, a->slot_table, a->slot_stride, st);
+                           ws + k_bytes, a->slot_table, a->slot_stride, a->slot_table ? a->slot_pos0 : 0, st);
 }

@@ -31,9 +31,10 @@ struct RowMap {
   const int32_t* table;
   int stride;
   int T;
+  int pos0;     // position in its sequence of token 0 of the input (appending to a cache)
   __device__ __forceinline__ int64_t operator()(int64_t row) const {
     if (!table) return row;
-    const int64_t b = row / T, t = row % T;
+    const int64_t b = row / T, t = row % T + pos0;
     return static_cast<int64_t>(table[b * stride + t / kPage]) * kPage + t % kPage;
   }
 };
@@ -416,9 +417,10 @@ int quantize_impl(int variant, const void* k, int dt, int B, int T, int HKV, int
 
 int quantize_dispatch(int variant, const void* k, int k_dtype, int B, int T, int HKV, int fp8, int page_size,
                       uint8_t* codes, void* scale, void* zero, uint8_t* residual, void* scratch,
-                      const int32_t* slot_table, int slot_stride, cudaStream_t st) {
+                      const int32_t* slot_table, int slot_stride, int slot_pos0, cudaStream_t st) {
+  if (slot_pos0 != 0 && (!slot_table || (variant != FFA_K_FP8 && variant != FFA_K_FP4))) return FFA_E_VARIANT;
   return quantize_impl(variant, k, k_dtype, B, T, HKV, fp8, page_size, codes, scale, zero, residual, scratch,
-                       RowMap{slot_table, slot_stride, T}, st);
+                       RowMap{slot_table, slot_stride, T, slot_pos0}, st);
 }
 
 }  // namespace ffa
@@ -433,31 +435,31 @@ extern "C" size_t ffa_quantize_scratch_bytes(int32_t B, int32_t HKV) {
 extern "C" int ffa_quantize_q2(const void* k, int32_t dt, int32_t B, int32_t T, int32_t HKV, int32_t fp8,
                                uint8_t* codes, void* scale, void* zero, uint8_t* residual, void* scratch,
                                ffa_stream_t stream) {
-  return quantize_impl(FFA_K_Q2, k, dt, B, T, HKV, fp8, 0, codes, scale, zero, residual, scratch, RowMap{nullptr, 0, T},
+  return quantize_impl(FFA_K_Q2, k, dt, B, T, HKV, fp8, 0, codes, scale, zero, residual, scratch, RowMap{nullptr, 0, T, 0},
                        reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffa_quantize_fp8fp8(const void* k, int32_t dt, int32_t B, int32_t T, int32_t HKV, int32_t fp8,
                                    uint8_t* base, uint8_t* residual, ffa_stream_t stream) {
   return quantize_impl(FFA_K_FP8, k, dt, B, T, HKV, fp8, 0, base, nullptr, nullptr, residual, nullptr,
-                       RowMap{nullptr, 0, T}, reinterpret_cast<cudaStream_t>(stream));
+                       RowMap{nullptr, 0, T, 0}, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffa_quantize_fp4(const void* k, int32_t dt, int32_t B, int32_t T, int32_t HKV, int32_t fp8,
                                 uint8_t* codes, uint8_t* residual, ffa_stream_t stream) {
   return quantize_impl(FFA_K_FP4, k, dt, B, T, HKV, fp8, 0, codes, nullptr, nullptr, residual, nullptr,
-                       RowMap{nullptr, 0, T}, reinterpret_cast<cudaStream_t>(stream));
+                       RowMap{nullptr, 0, T, 0}, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffa_quantize_nf4(const void* k, int32_t dt, int32_t B, int32_t T, int32_t HKV, int32_t fp8,
                                 uint8_t* codes, void* scale, uint8_t* residual, void* scratch, ffa_stream_t stream) {
   return quantize_impl(FFA_K_NF4, k, dt, B, T, HKV, fp8, 0, codes, scale, nullptr, residual, scratch,
-                       RowMap{nullptr, 0, T}, reinterpret_cast<cudaStream_t>(stream));
+                       RowMap{nullptr, 0, T, 0}, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffa_quantize_nvfp4(const void* k, int32_t dt, int32_t B, int32_t T, int32_t HKV, int32_t fp8,
                                   int32_t page_size, uint8_t* codes, void* scale, uint8_t* residual,
                                   ffa_stream_t stream) {
   return quantize_impl(FFA_K_NVFP4, k, dt, B, T, HKV, fp8, page_size, codes, scale, nullptr, residual, nullptr,
-                       RowMap{nullptr, 0, T}, reinterpret_cast<cudaStream_t>(stream));
+                       RowMap{nullptr, 0, T, 0}, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -20,6 +20,7 @@ import torch
 
 from ... import quantize as Q
 from ...decode import DecodeWorkspace, allocate_decode_workspace
+from ...kproj import kproj_fused
 from ..attn_kernel.attn_kernel_v1210_fused_bsz_fp8fp8 import attn_forward_decode_fp8fp8
 
 PAGE = 64
@@ -81,6 +82,25 @@ class PagedFP8Fp8Layer:
         flat(self.value)[rows] = value_states.to(self.dtype).reshape(-1, HKV, D)
         self.seq_len += T_new
 
+    def update_from_hidden(self, hidden: torch.Tensor, w_k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                           value_states: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+        """Append the tokens whose hidden states are ``hidden [B, T_new, H]``: K projection, RoPE
+        (``cos, sin [T_new, D]`` are the rows of the new positions) and quantisation run as one fused
+        kernel that writes the codes and the residual into this layer's pages; V is copied in."""
+        if not self.use_fp8_residual:
+            raise ValueError("the fused append writes base and residual; build the cache with use_fp8_residual=True")
+        B, T_new, _ = hidden.shape
+        HKV, D = self.num_kv_heads, self.head_dim
+        if B != self.batch or value_states.shape != (B, T_new, HKV, D):
+            raise ValueError(f"expected hidden [B={self.batch}, T, H] and values [B, T, {HKV}, {D}]")
+        if self.seq_len + T_new > self.max_seq_len:
+            raise ValueError(f"cache capacity {self.max_seq_len} exceeded ({self.seq_len} + {T_new})")
+        kproj_fused("fp8", hidden, w_k, cos, sin, HKV, D, bias=bias, fp8_dtype=self.fp8_dtype,
+                    block_table=self.block_table, out=(self.key_base, self.key_residual), position=self.seq_len)
+        rows = self._rows(self.seq_len, T_new)
+        self.value.view(-1, HKV, D)[rows] = value_states.to(self.dtype).reshape(-1, HKV, D)
+        self.seq_len += T_new
+
     # ---- decode ----------------------------------------------------------------------------------
     def decode(self, q: torch.Tensor, **kwargs) -> torch.Tensor:
         """Pruned decode attention of ``q [B, 1, HQ, D]`` over the cached tokens; keyword arguments
@@ -132,6 +152,10 @@ class PagedFP8Fp8Cache:
                cache_kwargs: Optional[dict[str, Any]] = None) -> None:
         self._ensure_layer(layer_idx)
         self.layers[layer_idx].update(key_states, value_states, cache_kwargs)
+
+    def update_from_hidden(self, hidden, w_k, cos, sin, value_states, layer_idx: int, bias=None) -> None:
+        self._ensure_layer(layer_idx)
+        self.layers[layer_idx].update_from_hidden(hidden, w_k, cos, sin, value_states, bias)
 
     def decode(self, q: torch.Tensor, layer_idx: int, **kwargs) -> torch.Tensor:
         return self.layers[layer_idx].decode(q, **kwargs)

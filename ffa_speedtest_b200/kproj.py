@@ -84,8 +84,12 @@ def kproj_reference(variant, h, w_k, cos, sin, num_kv_heads, head_dim, bias=None
 
 def kproj_fused(variant: Optional[str], h, w_k, cos, sin, num_kv_heads, head_dim, bias=None, fp8_dtype=None,
                 page_size: int = PAGE, *, block_table: Optional[torch.Tensor] = None, out=None,
-                return_k: bool = False):
-    """tcgen05 GEMM + bias + RoPE epilogue, then the variant's quantiser (``variant=None``: K only)."""
+                return_k: bool = False, position: int = 0):
+    """tcgen05 GEMM + bias + RoPE epilogue, then the variant's quantiser (``variant=None``: K only).
+
+    With ``block_table`` the codes and residual go straight into the pools ``out=(codes, residual)``;
+    ``position`` is where token 0 of ``h`` sits in its sequence, so new tokens can be appended to a
+    cache (fp8fp8 and fp4 only: the other formats take scales from the whole sequence or page)."""
     if not h.is_cuda:
         raise ValueError("h must be a CUDA tensor (this build has no CPU path)")
     if h.dim() != 3:
@@ -132,12 +136,15 @@ def kproj_fused(variant: Optional[str], h, w_k, cos, sin, num_kv_heads, head_dim
         if block_table is not None:
             if block_table.dtype != torch.int32 or block_table.dim() != 2 or block_table.shape[0] != B:
                 raise ValueError("block_table must be an int32 tensor of shape [B, pages_per_sequence]")
-            if block_table.shape[1] * PAGE < T:
-                raise ValueError("block_table has too few pages for T")
+            if position < 0 or block_table.shape[1] * PAGE < position + T:
+                raise ValueError("block_table has too few pages for position + T")
+            if position and variant not in ("fp8", "fp4"):
+                raise ValueError("appending at a position needs an elementwise format (fp8fp8 or fp4)")
             if out is None:
                 raise ValueError("with block_table, pass out=(codes_pool, residual_pool) to scatter into")
             codes, res = out
             a.slot_table, a.slot_stride = block_table.data_ptr(), block_table.shape[1]
+            a.slot_pos0 = position
         else:
             code_w = {"q2": 32, "fp8": 128}.get(variant, 64)
             codes = torch.empty((B, T, HKV, code_w), dtype=fp8_dtype if variant == "fp8" else torch.uint8, device=dev)

@@ -179,7 +179,9 @@ typedef struct FfaKprojArgs {
   const int32_t* slot_table; /* [B, slot_stride] page ids to scatter token rows into a paged cache, or NULL
                                 for the reference layout [B, T, HKV, .]                            */
   int32_t slot_stride;
-  int32_t reserved;
+  int32_t slot_pos0;      /* with slot_table: position in its sequence of token 0 of this call (appending
+                             new tokens to a cache); only the elementwise formats (fp8fp8, fp4) accept
+                             a non-zero value, the others derive scales from the whole sequence / page */
   void* codes;            /* outputs in the reference layouts (or pool layout with slot_table)     */
   void* scale;
   void* zero;

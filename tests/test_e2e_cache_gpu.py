@@ -42,3 +42,27 @@ def test_crop_reset_and_capacity():
     assert cache.get_seq_length() == 0
     with pytest.raises(RuntimeError):
         cache.decode(q, 0)
+
+
+def test_append_from_hidden_states_equals_append_of_projected_keys():
+    """hidden -> fused K-proj + RoPE + quantise + scatter at the cache position, against projecting
+    first (same kernel, K only) and appending the keys."""
+    from ffa_speedtest_b200.kproj import build_rope_cache, kproj_fused
+    from ffa_speedtest_b200.synth import make_kproj_inputs
+    B, HKV, D, H, T = 2, 8, 128, 512, 150
+    f8 = torch.float8_e4m3fn
+    h, w = make_kproj_inputs(T, H, HKV, D, B=B, seed=5, device="cuda")
+    cos, sin = build_rope_cache(T, D, base=500000.0, device="cuda")
+    cos, sin = cos.to(h.dtype), sin.to(h.dtype)
+    q, _, v = make_decode_inputs(B, T, 32, HKV, D, seed=6, device="cuda")
+    fused = PagedFP8Fp8Cache(B, HKV, max_seq_len=256, fp8_dtype=f8)
+    plain = PagedFP8Fp8Cache(B, HKV, max_seq_len=256, fp8_dtype=f8)
+    steps = [(0, 100), (100, 101), (101, 129), (129, 150)]          # crosses the page boundary at 128
+    for a, b in steps:
+        fused.update_from_hidden(h[:, a:b].contiguous(), w, cos[a:b].contiguous(), sin[a:b].contiguous(), v[:, a:b], 0)
+        (k,) = kproj_fused(None, h[:, a:b].contiguous(), w, cos[a:b].contiguous(), sin[a:b].contiguous(), HKV, D)
+        plain.update(k, v[:, a:b], 0)
+        for name in ("key_base", "key_residual", "value"):
+            x, y = getattr(fused.layers[0], name), getattr(plain.layers[0], name)
+            assert torch.equal(x.view(torch.uint8), y.view(torch.uint8)), (name, a, b)
+    assert torch.equal(fused.decode(q, 0, delta=8.0), plain.decode(q, 0, delta=8.0))
