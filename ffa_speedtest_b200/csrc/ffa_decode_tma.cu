@@ -36,14 +36,18 @@ namespace {
 
 constexpr int kThreads = kDecodeThreads;
 constexpr int kWarps = kDecodeWarps;
-constexpr int kPB = 3;          // coarse tiles requested ahead of the page being scored
-constexpr int kNBase = kPB + 1;
+// Coarse tiles requested ahead of the page being scored, and the slots that takes (one more).  The
+// fp8 coarse format with a refine lag of 1 keeps 3 slots so that three CTAs fit on an SM
+// (3 x 8 + 2 x 24 KiB); everything else keeps 4.
+constexpr int n_base_slots(int fmt, int lag) { return (fmt == FFA_K_FP8 && lag == 1) ? 3 : 4; }
 constexpr unsigned long long kWaitLimitNs = 200ull * 1000 * 1000;   // 0.2 s per mbarrier wait, then give up
 
 // DA = pages between scoring a page and refining it; DA + 1 residual+V slots
 template <int FMT, int DA>
 struct SmemT {
   static constexpr int kNRv = DA + 1;
+  static constexpr int kNBase = n_base_slots(FMT, DA);
+  static constexpr int kPB = kNBase - 1;
   static constexpr int kBaseSlot = kPage * Fmt<FMT>::kRow;            // 8 KiB / 2 KiB / 4 KiB
   static constexpr int kOffRv = kNBase * kBaseSlot;
   static constexpr int kOffAux = kOffRv + kNRv * kRvSlot;
@@ -297,6 +301,8 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
                                                               const __grid_constant__ CUtensorMap tm_v) {
   using L = SmemT<FMT, kDA>;
   constexpr int kNRv = L::kNRv;
+  constexpr int kNBase = L::kNBase;
+  constexpr int kPB = L::kPB;
   constexpr int ROW = Fmt<FMT>::kRow;
   constexpr bool kFp8Coarse = (FMT == FFA_K_FP8);
   extern __shared__ uint8_t smem_raw[];
@@ -376,7 +382,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       issue_tile(0, 0);
       issue_tile(1, ((p.NTB - 1) * kSample) / kPage);
     }
-    for (int j = 0; j < 2 && j < n; ++j) issue_base(j);
+    for (int j = 0; j < kNBase - 2 && j < n; ++j) issue_base(j);     // the slots the samples do not use
 
     if (L::kHasChannelScale) {
       const int64_t o = (static_cast<int64_t>(b) * p.HKV + hkv) * kHeadDim + tid;
@@ -549,7 +555,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
 
     // (the __syncthreads after the sample scoring, or after the q set-up, orders every warp's reads
     // of slots 0 and 1 before they are refilled)
-    for (int j = 2; j < kPB && j < n; ++j) issue_base(j);
+    for (int j = kNBase - 2; j < kPB && j < n; ++j) issue_base(j);
 
     float ks_next = 0.f;
     if (FMT == FFA_K_NVFP4) ks_next = load_block_scale((page_begin * kPage) / p.BS);
@@ -904,10 +910,11 @@ void decode_tma_plan(int B, int HKV, int NP, int wc_in, int ctas_per_sm, int* wc
 }
 
 int decode_tma_residency(int variant, int refine_lag) {
-  // shared memory per CTA: 4 coarse slots + (lag + 1) x 24 KiB, out of 227 KiB per SM
-  const int base = (variant == FFA_K_FP8 ? 8 : (variant == FFA_K_Q2 ? 2 : 4)) * 1024 * kNBase;
-  const int bytes = base + (refine_lag + 1) * kRvSlot + 4096;
-  const int n = (227 * 1024) / bytes;
+  // shared memory per CTA: coarse slots + (lag + 1) x 24 KiB + barriers, exchange buffers and
+  // alignment slack (under 3 KiB) + 1 KiB the system reserves, out of 228 KiB per SM
+  const int base = (variant == FFA_K_FP8 ? 8 : (variant == FFA_K_Q2 ? 2 : 4)) * 1024 * n_base_slots(variant, refine_lag);
+  const int bytes = base + (refine_lag + 1) * kRvSlot + 3 * 1024 + 1024;
+  const int n = (228 * 1024) / bytes;
   return n < 1 ? 1 : (n > 4 ? 4 : n);
 }
 
