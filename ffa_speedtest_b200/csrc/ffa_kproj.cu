@@ -485,26 +485,43 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
   if (timed_out && p.status) atomicExch(p.status, 2);
 }
 
-// Adds the k-split partial tiles in split order and applies the epilogue; one thread per 32 channels.
+// Adds the k-split partial tiles and applies the epilogue.  One warp per (token row, 32 channels):
+// lane = (split mod 4, float4 index) so that a warp has four splits of its 32 channels in flight per
+// step; the four split lanes are then folded with shuffles, the 32 sums meet in shared memory and
+// lane 0 runs the epilogue.  (Few tokens only, so the idle lanes cost nothing; what mattered was the
+// chain of dependent loads a single thread per row group used to walk: 13 us at T = 1.)
 template <int IO, int ROPE, int QUANT>
 __global__ void __launch_bounds__(128) kproj_finish_kernel(const __grid_constant__ KprojParams p) {
-  const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  __shared__ float s_sum[4][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int groups = p.N / 32;
-  if (idx >= static_cast<int64_t>(p.M) * groups) return;
-  const int64_t m = idx / groups;
-  const int n = static_cast<int>(idx % groups) * 32;
-  float acc[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-  for (int s = 0; s < p.n_split; ++s) {
-    const float4* src = reinterpret_cast<const float4*>(p.partial + (static_cast<int64_t>(s) * p.M + m) * p.N + n);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float4 x = src[i];
-      acc[4 * i] += x.x; acc[4 * i + 1] += x.y; acc[4 * i + 2] += x.z; acc[4 * i + 3] += x.w;
+  const int64_t idx = blockIdx.x * 4LL + warp;
+  const bool live = idx < static_cast<int64_t>(p.M) * groups;
+  const int64_t m = live ? idx / groups : 0;
+  const int n = live ? static_cast<int>(idx % groups) * 32 : 0;
+  const int sub = lane >> 3, v4 = lane & 7;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    for (int s = sub; s < p.n_split; s += 4) {
+      const float4 x = *reinterpret_cast<const float4*>(p.partial + (static_cast<int64_t>(s) * p.M + m) * p.N + n + 4 * v4);
+      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
     }
   }
-  rope_store_32_t<IO, ROPE, QUANT>(acc, p, m, (n / kHeadDim) * kHeadDim, n % kHeadDim);
+#pragma unroll
+  for (int off = 8; off < 32; off <<= 1) {
+    acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+    acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+    acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+    acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+  }
+  if (sub == 0) *reinterpret_cast<float4*>(&s_sum[warp][4 * v4]) = acc;
+  __syncwarp();
+  if (live && lane == 0) {
+    float sum[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) sum[i] = s_sum[warp][i];
+    rope_store_32_t<IO, ROPE, QUANT>(sum, p, m, (n / kHeadDim) * kHeadDim, n % kHeadDim);
+  }
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -641,8 +658,8 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
 
   const int64_t items = static_cast<int64_t>(p.m_tiles) * (N / bn) * p.n_split;
   const unsigned grid = static_cast<unsigned>(items < sm_count() ? items : sm_count());
-  const int64_t finish_threads = M * (N / 32);
-  const unsigned finish_grid = static_cast<unsigned>((finish_threads + 127) / 128);
+  const int64_t finish_warps = M * (N / 32);
+  const unsigned finish_grid = static_cast<unsigned>((finish_warps + 3) / 4);
   int dev = 0;
   cudaGetDevice(&dev);
   // one kernel per (tile width, activation dtype, table dtype, fused quantiser); each raises its

@@ -94,14 +94,24 @@ __global__ void __launch_bounds__(256) minmax_kernel(const void* __restrict__ k,
       float lo[8], hi[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) { lo[j] = INFINITY; hi[j] = -INFINITY; }
-      for (int t = t0 + lane; t < t1; t += lanes) {
-        float x[8];
-        load8<DT>(k, (static_cast<int64_t>(b) * T + t) * row_elems + 8 * g, x);
+      // four token rows in flight per step
+      for (int t = t0 + lane; t < t1; t += 4 * lanes) {
+        float x[4][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float v = ABS ? fabsf(x[j]) : x[j];
-          lo[j] = fminf(lo[j], v);
-          hi[j] = fmaxf(hi[j], v);
+        for (int u = 0; u < 4; ++u) {
+          const int tt = t + u * lanes;
+          if (tt < t1) load8<DT>(k, (static_cast<int64_t>(b) * T + tt) * row_elems + 8 * g, x[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (t + u * lanes < t1) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float v = ABS ? fabsf(x[u][j]) : x[u][j];
+              lo[j] = fminf(lo[j], v);
+              hi[j] = fmaxf(hi[j], v);
+            }
+          }
         }
       }
       if (lanes == 1) {
