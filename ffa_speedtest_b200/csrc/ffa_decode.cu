@@ -613,12 +613,11 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   // Refine lag (pages between scoring and refining): 1 for every format.  A lag of 2 keeps one more
   // page of residual+V in flight per CTA, but the smaller ring of lag 1 lets a third CTA live on the
   // SM, which hides more latency than the deeper ring did (fp8 coarse, B=8, T=32K: 169 us against
-  // 177 us; the 2-/4-bit formats gain 15-20 %).  reserved bits 4-5 override.
-  const int lag_override = (a->reserved >> 4) & 3;
-  p.refine_lag = lag_override == 2 ? 2 : 1;
+  // 177 us; the 2-/4-bit formats gain 15-20 %).
+  p.refine_lag = 1;
   const bool use_tma = want_tma && decode_tma_supported(p);
   if (use_tma)
-    decode_tma_plan(a->B, a->HKV, p.NP, a->pages_per_chunk, decode_tma_residency(a->variant, p.refine_lag), &p.ppc,
+    decode_tma_plan(a->B, a->HKV, p.NP, a->pages_per_chunk, decode_tma_residency(p, a->variant, a->fp8_format), &p.ppc,
                     &p.nch);
   else ffa_decode_plan(a->B, a->T, a->HKV, a->pages_per_chunk, &p.ppc, &p.nch);
 

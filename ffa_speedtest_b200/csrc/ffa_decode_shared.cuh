@@ -70,7 +70,7 @@ int launch_decode_tma(const DecodeParams& p, int variant, int f8, int64_t kv_row
 // (about one CTA per resident slot: 2 per SM), `nch` = most partials any kv-head can receive.
 void decode_tma_plan(int B, int HKV, int NP, int wc_in, int ctas_per_sm, int* wc, int* nch);
 // resident CTAs per SM of the TMA kernel for a coarse format and refine lag
-int decode_tma_residency(int variant, int refine_lag);
+int decode_tma_residency(const DecodeParams& p, int variant, int f8);   // CTAs per SM of the kernel that would run
 // true when the TMA path handles these arguments (bf16 q, driver entry point available)
 bool decode_tma_supported(const DecodeParams& p);
 

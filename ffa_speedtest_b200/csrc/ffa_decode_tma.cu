@@ -185,9 +185,11 @@ __device__ __forceinline__ void load_fp8_rows(uint32_t (&ra)[8], uint32_t (&rb)[
 
 // q . k for the warp's 16 tokens from raw fp8 K bytes and the e4m3 pieces of q.
 // out[nt][0] : token g, head 4nt+t;  out[nt][1] : token g+8, head 4nt+t   (unscaled dot products)
-template <int F8, int NT>
-__device__ __forceinline__ void dot_fp8(float (&out)[NT][2], const uint32_t (&qb)[NT][4][2], const float (&qinv)[NT],
-                                        const uint8_t* tile, int warp, int g, int t) {
+// QP = 2 (bf16 q): one n-tile per four heads, columns 2t / 2t+1 = pieces hi / lo x16.
+// QP = 3 (fp16 q): a second n-tile per four heads whose column 2t is the third piece (x256).
+template <int F8, int NT, int QP>
+__device__ __forceinline__ void dot_fp8(float (&out)[NT][2], const uint32_t (&qb)[NT * (QP - 1)][4][2],
+                                        const float (&qinv)[NT], const uint8_t* tile, int warp, int g, int t) {
   uint32_t ra[8], rb[8];
   load_fp8_rows(ra, rb, tile, warp, g, t);
 #pragma unroll
@@ -198,9 +200,21 @@ __device__ __forceinline__ void dot_fp8(float (&out)[NT][2], const uint32_t (&qb
       if (s & 1) mma_fp8<F8>(acc1, ra[2 * s], rb[2 * s], ra[2 * s + 1], rb[2 * s + 1], qb[nt][s][0], qb[nt][s][1]);
       else       mma_fp8<F8>(acc0, ra[2 * s], rb[2 * s], ra[2 * s + 1], rb[2 * s + 1], qb[nt][s][0], qb[nt][s][1]);
     }
-    // columns 2t / 2t+1 hold the hi / lo piece of head 4nt+t; lo was stored times 16
-    out[nt][0] = ((acc0[0] + acc1[0]) + (acc0[1] + acc1[1]) * 0.0625f) * qinv[nt];
-    out[nt][1] = ((acc0[2] + acc1[2]) + (acc0[3] + acc1[3]) * 0.0625f) * qinv[nt];
+    float d0 = (acc0[0] + acc1[0]) + (acc0[1] + acc1[1]) * 0.0625f;
+    float d1 = (acc0[2] + acc1[2]) + (acc0[3] + acc1[3]) * 0.0625f;
+    if (QP == 3) {
+      float acc2[4] = {0.f, 0.f, 0.f, 0.f}, acc3[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const uint32_t b0 = qb[(QP - 2) * NT + nt][s][0], b1 = qb[(QP - 2) * NT + nt][s][1];
+        if (s & 1) mma_fp8<F8>(acc3, ra[2 * s], rb[2 * s], ra[2 * s + 1], rb[2 * s + 1], b0, b1);
+        else       mma_fp8<F8>(acc2, ra[2 * s], rb[2 * s], ra[2 * s + 1], rb[2 * s + 1], b0, b1);
+      }
+      d0 += (acc2[0] + acc3[0]) * 0.00390625f;
+      d1 += (acc2[2] + acc3[2]) * 0.00390625f;
+    }
+    out[nt][0] = d0 * qinv[nt];
+    out[nt][1] = d1 * qinv[nt];
   }
 }
 
@@ -294,8 +308,10 @@ __device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t x) {
 
 // One CTA walks a contiguous range of the flattened (batch x kv-head, page) space, `wc` pages
 // long; the part of the range inside one (b, kv-head) is a "segment" and produces one partial.
-template <int FMT, int F8, int NT, bool VBF, int kDA>
-__global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_constant__ DecodeParams p,
+// QP: e4m3 pieces per q value (2 for bf16 q, 3 for fp16 q: 4 + 4 + 3 significant bits).
+// Three CTAs per SM for up to four q heads per kv head (at most 168 registers), two beyond that.
+template <int FMT, int F8, int NT, bool VBF, int kDA, int QP>
+__global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(const __grid_constant__ DecodeParams p,
                                                               const __grid_constant__ CUtensorMap tm_c,
                                                               const __grid_constant__ CUtensorMap tm_r,
                                                               const __grid_constant__ CUtensorMap tm_v) {
@@ -417,16 +433,23 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
     };
     auto set_block_scale = [&](int blk) { apply_block_scale(load_block_scale(blk)); };
 
-    // ---- q operands (q is bf16 on this path) -------------------------------------------------------
-    // B-fragment column n = g of n-tile nt is head 4nt + g/2, piece g&1 (hi / lo x16) for the fp8
-    // MMAs, and (q as fp16 / zero) for the fp16 MMA of the 2-bit / 4-bit coarse formats.
-    uint32_t qb[NT][4][2];
+    // ---- q operands ------------------------------------------------------------------------------
+    // q . 2^e = hi + mid / 16 (+ lo / 256 for fp16 q), every piece an e4m3 number: exact for bf16's 8
+    // and fp16's 11 significant bits as long as the value stays above e4m3's underflow.
+    // B-fragment column n = g of n-tile nt is head 4nt + g/2, piece g&1 (hi / mid); with three pieces
+    // n-tile NT + nt holds (lo / zero) in the same columns.  The fp16 MMA of the 2-bit / 4-bit coarse
+    // formats takes (q as fp16 / zero).
+    uint32_t qb[NT * (QP - 1)][4][2];
     uint32_t qh[kFp8Coarse ? 1 : NT][kFp8Coarse ? 1 : 8][2];
+    auto q_pair = [&](uint32_t w) -> float2 {               // two consecutive q values as floats
+      if (QP == 2) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+      return unpack_h2(w);
+    };
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int hc = 4 * nt + (g >> 1);
-      const bool lo_piece = (g & 1) != 0;
-      uint32_t raw[16];                                       // 32 bf16 channels 32t .. 32t+31
+      const bool second = (g & 1) != 0;                        // column of the mid piece / of zeros
+      uint32_t raw[16];                                       // 32 16-bit channels 32t .. 32t+31
       if (hc < G) {
         const uint4* src = reinterpret_cast<const uint4*>(
             p.q + ((static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G + hc) * kHeadDim + 32 * t) * 2);
@@ -442,8 +465,8 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       float amax = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        amax = fmaxf(amax, fabsf(__uint_as_float(raw[i] << 16)));
-        amax = fmaxf(amax, fabsf(__uint_as_float(raw[i] & 0xffff0000u)));
+        const float2 f = q_pair(raw[i]);
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
       }
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
@@ -452,26 +475,29 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
       if (amax > 0.f && amax < INFINITY) e = 134 - static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);
       e = max(-100, min(100, e));
       const float up = __int_as_float((127 + e) << 23), down = __int_as_float((127 - e) << 23);
-      if (warp == 0 && t == 0 && !lo_piece) sQinv[hc] = down;
+      if (warp == 0 && t == 0 && !second) sQinv[hc] = down;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        const float x0 = __uint_as_float(raw[2 * r] << 16) * up, x1 = __uint_as_float(raw[2 * r] & 0xffff0000u) * up;
-        const float x2 = __uint_as_float(raw[2 * r + 1] << 16) * up, x3 = __uint_as_float(raw[2 * r + 1] & 0xffff0000u) * up;
+        const float2 fa = q_pair(raw[2 * r]), fb = q_pair(raw[2 * r + 1]);
+        const float x0 = fa.x * up, x1 = fa.y * up, x2 = fb.x * up, x3 = fb.y * up;
         const uint32_t h01 = f32x2_to_e4m3x2(x0, x1), h23 = f32x2_to_e4m3x2(x2, x3);
-        uint32_t w = h01 | (h23 << 16);
-        if (lo_piece) {
-          const float2 d01 = e4m3x2_to_f32x2(h01), d23 = e4m3x2_to_f32x2(h23);
-          w = f32x2_to_e4m3x2((x0 - d01.x) * 16.f, (x1 - d01.y) * 16.f) |
-              (f32x2_to_e4m3x2((x2 - d23.x) * 16.f, (x3 - d23.y) * 16.f) << 16);
+        const float2 d01 = e4m3x2_to_f32x2(h01), d23 = e4m3x2_to_f32x2(h23);
+        const float r0 = (x0 - d01.x) * 16.f, r1 = (x1 - d01.y) * 16.f, r2 = (x2 - d23.x) * 16.f, r3 = (x3 - d23.y) * 16.f;
+        const uint32_t m01 = f32x2_to_e4m3x2(r0, r1), m23 = f32x2_to_e4m3x2(r2, r3);
+        qb[nt][r >> 1][r & 1] = second ? (m01 | (m23 << 16)) : (h01 | (h23 << 16));   // register r: channels 32t+4r .. +3
+        if (QP == 3) {
+          const float2 e01 = e4m3x2_to_f32x2(m01), e23 = e4m3x2_to_f32x2(m23);
+          const uint32_t l01 = f32x2_to_e4m3x2((r0 - e01.x) * 16.f, (r1 - e01.y) * 16.f);
+          const uint32_t l23 = f32x2_to_e4m3x2((r2 - e23.x) * 16.f, (r3 - e23.y) * 16.f);
+          qb[(QP - 2) * NT + nt][r >> 1][r & 1] = second ? 0u : (l01 | (l23 << 16));
         }
-        qb[nt][r >> 1][r & 1] = w;                            // register r: channels 32t+4r .. +3
       }
       if (!kFp8Coarse) {
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
-          // bf16 -> fp16 like the reference's q.to(float16)
-          qh[kFp8Coarse ? 0 : nt][kFp8Coarse ? 0 : s][0] = lo_piece ? 0u : bf16x2_to_h2(raw[2 * s]);
-          qh[kFp8Coarse ? 0 : nt][kFp8Coarse ? 0 : s][1] = lo_piece ? 0u : bf16x2_to_h2(raw[2 * s + 1]);
+          // the reference's q.to(float16)
+          qh[kFp8Coarse ? 0 : nt][kFp8Coarse ? 0 : s][0] = second ? 0u : (QP == 2 ? bf16x2_to_h2(raw[2 * s]) : raw[2 * s]);
+          qh[kFp8Coarse ? 0 : nt][kFp8Coarse ? 0 : s][1] = second ? 0u : (QP == 2 ? bf16x2_to_h2(raw[2 * s + 1]) : raw[2 * s + 1]);
         }
       }
     }
@@ -482,7 +508,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
 
     // unscaled coarse dots of one tile -> [nt][token g / g+8]; `slice` selects which 16 rows
     auto coarse_dots = [&](float (&out)[NT][2], const uint8_t* tile, int slice) {
-      if constexpr (kFp8Coarse) dot_fp8<F8, NT>(out, qb, qinv, tile, slice, g, t);
+      if constexpr (kFp8Coarse) dot_fp8<F8, NT, QP>(out, qb, qinv, tile, slice, g, t);
       else if (FMT == FFA_K_Q2 ? sc.q2_fast : (FMT == FFA_K_NVFP4 && sc.page_fast))
         dot_f16<FMT, NT, true>(out, qh, tile, sc, slice, g, t);
       else dot_f16<FMT, NT, false>(out, qh, tile, sc, slice, g, t);
@@ -595,7 +621,7 @@ __global__ void __launch_bounds__(kThreads) decode_tma_kernel(const __grid_const
         float dr[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) dr[nt][0] = dr[nt][1] = 0.f;
-        if (use_res) dot_fp8<F8, NT>(dr, qb, qinv, slot, warp, g, t);
+        if (use_res) dot_fp8<F8, NT, QP>(dr, qb, qinv, slot, warp, g, t);
         const int tok = page * kPage + 16 * warp + g;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -844,18 +870,30 @@ bool make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t row_bytes_
                            static_cast<CUtensorMapL2promotion>(promo), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int FMT, int F8, int NT, bool VBF, int DA>
+// Launches the kernel, or (stream == kQueryResidency) returns how many of its CTAs fit on an SM.
+const cudaStream_t kQueryResidency = reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(-16));
+
+template <int FMT, int F8, int NT, bool VBF, int DA, int QP>
 int launch_one(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
                cudaStream_t stream) {
   using L = SmemT<FMT, DA>;
-  auto kern = decode_tma_kernel<FMT, F8, NT, VBF, DA>;
+  auto kern = decode_tma_kernel<FMT, F8, NT, VBF, DA, QP>;
   static bool configured[64] = {};
+  static int resident[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
+  const bool slot = dev >= 0 && dev < 64;
+  if (!slot || !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
     if (e != cudaSuccess) return note_cuda_error(e, "cudaFuncSetAttribute(decode_tma)");
-    configured[dev] = true;
+    if (slot) configured[dev] = true;
+  }
+  if (stream == kQueryResidency) {
+    if (slot && resident[dev] > 0) return resident[dev];
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, L::kBytes) != cudaSuccess || n < 1) n = 1;
+    if (slot) resident[dev] = n;
+    return n;
   }
   const int64_t total_pages = static_cast<int64_t>(p.B) * p.HKV * p.NP;
   const unsigned grid = static_cast<unsigned>((total_pages + p.ppc - 1) / p.ppc);
@@ -864,24 +902,23 @@ int launch_one(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& 
   return e == cudaSuccess ? FFA_OK : note_cuda_error(e, "decode_tma launch");
 }
 
-template <int FMT, int F8, int DA>
-int launch_nt(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
-              cudaStream_t stream) {
-  if (p.G <= 4)
-    return p.v_bf16 ? launch_one<FMT, F8, 1, true, DA>(p, mc, mr, mv, stream)
-                    : launch_one<FMT, F8, 1, false, DA>(p, mc, mr, mv, stream);
-  return p.v_bf16 ? launch_one<FMT, F8, 2, true, DA>(p, mc, mr, mv, stream)
-                  : launch_one<FMT, F8, 2, false, DA>(p, mc, mr, mv, stream);
+// bf16 q goes with either V type; fp16 q with fp16 V (decode_tma_supported admits nothing else)
+template <int FMT, int F8, int NT>
+int launch_types(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
+                 cudaStream_t stream) {
+  if (p.q_dtype == FFA_F16) return launch_one<FMT, F8, NT, false, 1, 3>(p, mc, mr, mv, stream);
+  return p.v_bf16 ? launch_one<FMT, F8, NT, true, 1, 2>(p, mc, mr, mv, stream)
+                  : launch_one<FMT, F8, NT, false, 1, 2>(p, mc, mr, mv, stream);
 }
 
 template <int FMT>
 int launch_fmt(const DecodeParams& p, int f8, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
                cudaStream_t stream) {
-  if (p.refine_lag == 1)
-    return f8 == FFA_E4M3 ? launch_nt<FMT, FFA_E4M3, 1>(p, mc, mr, mv, stream)
-                          : launch_nt<FMT, FFA_E5M2, 1>(p, mc, mr, mv, stream);
-  return f8 == FFA_E4M3 ? launch_nt<FMT, FFA_E4M3, 2>(p, mc, mr, mv, stream)
-                        : launch_nt<FMT, FFA_E5M2, 2>(p, mc, mr, mv, stream);
+  if (p.G <= 4)
+    return f8 == FFA_E4M3 ? launch_types<FMT, FFA_E4M3, 1>(p, mc, mr, mv, stream)
+                          : launch_types<FMT, FFA_E5M2, 1>(p, mc, mr, mv, stream);
+  return f8 == FFA_E4M3 ? launch_types<FMT, FFA_E4M3, 2>(p, mc, mr, mv, stream)
+                        : launch_types<FMT, FFA_E5M2, 2>(p, mc, mr, mv, stream);
 }
 
 }  // namespace
@@ -909,18 +946,27 @@ void decode_tma_plan(int B, int HKV, int NP, int wc_in, int ctas_per_sm, int* wc
   *nch_out = static_cast<int>((NP + wc - 1) / wc) + 1;
 }
 
-int decode_tma_residency(int variant, int refine_lag) {
-  // shared memory per CTA: coarse slots + (lag + 1) x 24 KiB + barriers, exchange buffers and
-  // alignment slack (under 3 KiB) + 1 KiB the system reserves, out of 228 KiB per SM
-  const int base = (variant == FFA_K_FP8 ? 8 : (variant == FFA_K_Q2 ? 2 : 4)) * 1024 * n_base_slots(variant, refine_lag);
-  const int bytes = base + (refine_lag + 1) * kRvSlot + 3 * 1024 + 1024;
-  const int n = (228 * 1024) / bytes;
+int decode_tma_residency(const DecodeParams& p, int variant, int f8) {
+  // ask the runtime how many CTAs of the kernel that would run fit on an SM (shared memory and
+  // registers both count); the page ranges are cut so that the grid is exactly one such wave
+  CUtensorMap none{};
+  int n;
+  switch (variant) {
+    case FFA_K_FP8:   n = launch_fmt<FFA_K_FP8>(p, f8, none, none, none, kQueryResidency); break;
+    case FFA_K_Q2:    n = launch_fmt<FFA_K_Q2>(p, f8, none, none, none, kQueryResidency); break;
+    case FFA_K_FP4:   n = launch_fmt<FFA_K_FP4>(p, f8, none, none, none, kQueryResidency); break;
+    case FFA_K_NF4:   n = launch_fmt<FFA_K_NF4>(p, f8, none, none, none, kQueryResidency); break;
+    case FFA_K_NVFP4: n = launch_fmt<FFA_K_NVFP4>(p, f8, none, none, none, kQueryResidency); break;
+    default: n = 1;
+  }
   return n < 1 ? 1 : (n > 4 ? 4 : n);
 }
 
 bool decode_tma_supported(const DecodeParams& p) {
-  // two exact e4m3 pieces need a bf16 query; row indices are 32-bit TMA coordinates
-  return p.q_dtype == FFA_BF16 && encode_tiled_fn() != nullptr;
+  // the query is split into exact e4m3 pieces: two for bf16, three for fp16 (fp16 q comes with
+  // fp16 V in practice; the mixed case is left to the fp16 tensor-core kernel)
+  const bool types_ok = p.q_dtype == FFA_BF16 || (p.q_dtype == FFA_F16 && !p.v_bf16);
+  return types_ok && encode_tiled_fn() != nullptr;
 }
 
 int launch_decode_tma(const DecodeParams& p, int variant, int f8, int64_t kv_rows, cudaStream_t stream) {

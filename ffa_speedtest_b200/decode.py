@@ -22,7 +22,6 @@ import torch
 from . import _lib
 
 PAGE = 64
-_TUNE: dict = {}     # experiment knobs (e.g. {"refine_lag": 1}); empty in normal use
 
 
 class DecodeWorkspace:
@@ -194,7 +193,7 @@ def decode_call(
     a.workspace = workspace.scratch.data_ptr()
     a.workspace_bytes = workspace.scratch.numel()
     a.pages_per_chunk = pages_per_chunk
-    a.reserved = (1 if kernel == "fp16" else 0) | (_TUNE.get("refine_lag", 0) << 4)
+    a.reserved = 1 if kernel == "fp16" else 0
     a.kv_rows = k_codes.shape[0] * k_codes.shape[1]
     _lib.check(_lib.lib().ffa_decode(a, _lib.current_stream(q.device)), "ffa_decode")
 
