@@ -46,6 +46,9 @@ WORKLOADS = {
     "fp4fp8_b16_t64k": dict(kind="fp4", B=16, T=65536, delta=8.0, fp8="e4m3"),
     "nf4fp8_b16_t64k": dict(kind="nf4", B=16, T=65536, delta=8.0, fp8="e4m3"),
     "nvfp4fp8_b16_t64k": dict(kind="nvfp4", B=16, T=65536, delta=8.0, fp8="e4m3"),
+    # sequence split over the ranks (strong scaling): every rank owns a page range of every sequence,
+    # one all-gather of (O, LSE) partials and a merge kernel finish the step
+    "q2fp8_b4_t512k_seqsplit": dict(kind="q2", B=4, T=524288, delta=8.0, fp8="e4m3", seqsplit=True),
     # fused K-projection + RoPE + quantise into a paged cache (hidden 4096 -> 8 kv heads x 128)
     "kproj_q2fp8_t8192": dict(kproj="q2", T=8192, fp8="e4m3"),
     "kproj_q2fp8_t64": dict(kproj="q2", T=64, fp8="e4m3"),
@@ -283,7 +286,9 @@ def run_kproj(args, wl_name: str, wl: dict) -> dict:
                 "note": "few-token projection: streaming the 8 MiB weight from HBM is the floor; launch latency dominates"}
         metric, unit, value = "kproj_rope_quantize_TBps", "TB/s", byt / per_step_s / 1e12
         e2e_value = byt / s_e2e / 1e12
-    n_quant = {"q2": 4, "fp8": 0}[variant]            # fp8fp8 is quantised inside the GEMM epilogue
+    # fp8fp8 is quantised inside the GEMM epilogue; q2 reduces min/max there and then runs three small
+    # kernels (reset of the min/max scratch, scale finalisation, encode)
+    n_quant = {"q2": 4, "fp8": 0}[variant]
     n_gemm = 1 if T >= 4096 else 2                     # few-token shapes add the split-k finish kernel
     return {
         "metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": steps, "warmup": W,
@@ -300,6 +305,121 @@ def run_kproj(args, wl_name: str, wl: dict) -> dict:
         "gpu_launches": steps * (n_gemm + n_quant),
         "clocks": clocks,
     }
+
+
+def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank: int):
+    """Sequence-split decode: rank r holds pages [lo, hi) of every sequence (contiguous layout), all
+    ranks hold the same thresholds (computed from the replicated 32 sample rows), each step is the
+    local decode into a [B, HQ, 129] partial, one all-gather and the merge kernel."""
+    import torch.distributed as dist
+    from ffa_speedtest_b200 import quantize as Q, sharded
+    from ffa_speedtest_b200.decode import allocate_decode_workspace, decode_call
+    from ffa_speedtest_b200.synth import make_decode_inputs
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("nccl", device_id=dev) if world > 1 else None
+    kind, B, T, delta = wl["kind"], wl["B"], wl["T"], wl["delta"]
+    f8 = {"e5m2": torch.float8_e5m2, "e4m3": torch.float8_e4m3fn}[wl["fp8"]]
+    NP = T // PAGE
+    W = max(args.warmup, 3)
+    lo, hi = sharded.page_slice(NP, rank, world)
+    # the same sequence on every rank (same seed); the scales of q2 span the whole sequence, so K is
+    # quantised whole and then cut to this rank's pages
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, D, seed=1, device=dev)
+    codes, scale, zero, res = Q.quantize_k_2bit_fp8_residual(k, f8)
+    del k
+    r0, r1 = sharded.sample_token_rows(T, PAGE)
+    sample = torch.cat([codes[:, r0.start:r0.stop], codes[:, r1.start:r1.stop]], dim=1).contiguous()
+    th = sharded.global_threshold(kind, q, sample, delta=delta, k_scale=scale, k_zero=zero)
+    ck, rk, vk = (x[:, lo * PAGE:hi * PAGE].contiguous() for x in (codes, res, v))
+    del codes, res, v
+    torch.cuda.empty_cache()
+    ws = allocate_decode_workspace(q, vk, BS=PAGE, SBS=PAGE)
+    q_dev = q.clone()
+
+    def local(partial_out=None, out=None):
+        return decode_call(kind, q_dev, ck, vk, k_scale=scale, k_zero=zero, k_residual=rk, BS=PAGE, SBS=PAGE,
+                           delta=delta, precomputed_threshold=th, workspace=ws, partial_out=partial_out, out=out)
+
+    if world > 1:
+        runner = sharded.SequenceShardedDecode(dist.group.WORLD, B, HQ, dev, q.dtype)
+        step = lambda: runner.step(local)
+    else:
+        step = lambda: local()
+    o = step()
+    torch.cuda.synchronize()
+    kept_local = float(ws.mask.float().mean())
+    step_bytes = algorithmic_bytes(kind, B, (hi - lo) * PAGE, kept_local, paged=False)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+
+    q_host = q.cpu().pin_memory()
+    o_host = torch.empty((B, HQ, D), dtype=q.dtype).pin_memory()
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        o_host.copy_(step(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(W):
+        e2e_step()
+    barrier()
+    n_e2e = max(10, min(args.steps, 100))
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    barrier()
+    s_e2e = (time.perf_counter() - t0) / n_e2e
+    if ws.status() != 0:
+        raise SystemExit("a bounded wait inside the decode kernel gave up (status word set): results are invalid")
+    t = torch.tensor([ms, s_e2e, step_bytes, kept_local], dtype=torch.float64, device=dev)
+    tmax, tsum = t.clone(), t.clone()
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+    out = None
+    if rank == 0:
+        per_step_s = float(tmax[0]) / 1e3 / args.steps
+        job_bytes = float(tsum[2])
+        peak, peak_kind = peaks()
+        out = {
+            "metric": METRIC, "value": job_bytes / per_step_s / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": W, "ms_per_step": per_step_s * 1e3, "us_per_step": per_step_s * 1e6, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32 (2-bit/fp8/bf16 storage)", "data": "synthetic",
+            "config": {"workload": wl_name, "variant": kind + "fp8", "batch": B, "context": T, "q_heads": HQ,
+                       "kv_heads": HKV, "head_dim": D, "page": PAGE, "delta": delta, "fp8": wl["fp8"],
+                       "kept_fraction": float(tsum[3]) / world, "pages_per_rank": hi - lo,
+                       "algorithmic_bytes_per_step": job_bytes, "cuda_graph": False,
+                       "l2": "inputs_larger_than_l2 (no flush)",
+                       "sharding": "sequence split: page range per rank, all-gather of [B,HQ,129] partials + merge"},
+            "roofline": {"bound": "hbm", "achieved": job_bytes / world / per_step_s / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": job_bytes / world / per_step_s / 1e9 / peak, "peak_source": peak_kind, "traffic": None,
+                         "note": "per-GPU rate of the whole step (local decode + all-gather + merge)"},
+            "e2e": {"value": job_bytes / float(tmax[1]) / 1e12, "unit": UNIT, "h2d_bytes_per_step": q_host.numel() * 2,
+                    "d2h_bytes_per_step": o_host.numel() * 2, "us_per_step": float(tmax[1]) * 1e6, "steps": n_e2e},
+            "gpu_launches": args.steps * (1 if world == 1 else 2),     # decode (+ merge); the all-gather is NCCL's
+            "clocks": clocks,
+        }
+    if world > 1:
+        dist.destroy_process_group()
+    return out
 
 
 def main():
@@ -334,6 +454,11 @@ def main():
     if "kproj" in wl:
         if rank == 0:
             print(json.dumps(run_kproj(args, args.workload, wl)), flush=True)
+        return
+    if wl.get("seqsplit"):
+        out = run_seqsplit(args, args.workload, wl, rank, world, local_rank)
+        if rank == 0:
+            print(json.dumps(out), flush=True)
         return
     import torch.distributed as dist
     from ffa_speedtest_b200 import quantize as Q

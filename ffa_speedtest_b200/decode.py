@@ -110,8 +110,8 @@ def decode_call(
 ):
     """Shape bookkeeping shared by the five entry points; tensors are already type-checked.
 
-    ``kernel``: "auto" picks the TMA / fp8 tensor-core kernel when q is bfloat16 and the fp16
-    tensor-core kernel otherwise; "fp16" forces the latter (it follows the reference's fp16
+    ``kernel``: "auto" picks the TMA / fp8 tensor-core kernel when q is bfloat16, or float16 with
+    float16 V, and the fp16 tensor-core kernel otherwise; "fp16" forces the latter (it follows the reference's fp16
     rounding of the refined K tile to the letter)."""
     if kernel not in ("auto", "fp16"):
         raise ValueError(f"kernel must be 'auto' or 'fp16', got {kernel!r}")

@@ -55,6 +55,43 @@ def merge_partials(parts: torch.Tensor, out_dtype: torch.dtype, out: Optional[to
     return out
 
 
+def sample_token_rows(T: int, BS: int) -> Tuple[range, range]:
+    """The two 16-token blocks the prune thresholds are computed from: tokens ``[0, 16)`` and
+    ``[(NTB-1)*16, +16)`` with ``NTB = ceil(T / BS)`` (reference ...q2fp8.py:55-82)."""
+    ntb = -(-T // BS)
+    if ntb * 16 > T:
+        raise ValueError(f"T={T} is shorter than the sample blocks of {ntb} x 16 tokens")
+    return range(0, 16), range((ntb - 1) * 16, (ntb - 1) * 16 + 16)
+
+
+def global_threshold(variant: str, q: torch.Tensor, k_codes: torch.Tensor, *, delta: float,
+                     k_scale: Optional[torch.Tensor] = None, k_zero: Optional[torch.Tensor] = None,
+                     scale: Optional[float] = None) -> torch.Tensor:
+    """Prune thresholds ``[B, HQ]`` of a sequence from its two sample blocks alone.
+
+    The thresholds depend on the coarse codes of the token rows ``sample_token_rows(T, BS)`` only, so
+    a rank that owns other pages can compute them from a replicated copy of those 32 rows: ``k_codes``
+    is ``[B, 32, HKV, code_bytes]`` (first block, then second block).  The two blocks are placed in a five-page stand-in sequence at
+    the positions the kernel samples and one decode call over it writes the thresholds.  nvfp4 is
+    excluded: its page scales sit at other indices in the stand-in."""
+    from .decode import DecodeWorkspace, decode_call
+    if variant == "nvfp4":
+        raise ValueError("global_threshold does not cover nvfp4 (page scales)")
+    if k_codes.dim() != 4 or k_codes.shape[1] != 32:
+        raise ValueError("k_codes must be [B, 32, HKV, code_bytes]: the two 16-token sample blocks")
+    B, _, HKV, W = k_codes.shape
+    HQ = q.shape[2]
+    T_s = 5 * 64                                          # ceil(320 / 64) = 5 pages; second sample at (5-1)*16 = 64
+    mini = torch.zeros((B, T_s, HKV, W), dtype=k_codes.dtype, device=k_codes.device)
+    mini.view(torch.uint8)[:, 0:16] = k_codes.view(torch.uint8)[:, 0:16]
+    mini.view(torch.uint8)[:, 64:80] = k_codes.view(torch.uint8)[:, 16:32]
+    v = torch.zeros((B, T_s, HKV, 128), dtype=q.dtype if q.dtype != torch.float32 else torch.float16, device=q.device)
+    ws = DecodeWorkspace(B, T_s, HQ, HKV, 128, BS=64, SBS=64, device=q.device, dtype=q.dtype)
+    decode_call(variant, q, mini, v, k_scale=k_scale, k_zero=k_zero, k_residual=None, scale=scale, BS=64, SBS=64,
+                delta=delta, use_fp8_residual=False, workspace=ws)
+    return ws.threshold.clone()
+
+
 class SequenceShardedDecode:
     """Sequence-split decode step for one rank.
 

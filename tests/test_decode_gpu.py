@@ -242,3 +242,61 @@ def test_validation_errors_match_reference():
         f(q, *args[1:], k_residual=res.to(d))          # CPU q
     with pytest.raises(ValueError, match="integer"):
         f(args[0], v.to(d)[..., :32].contiguous(), *args[2:], k_residual=res.to(d))
+
+
+@pytest.mark.parametrize("kind", ["q2", "fp8", "fp4", "nf4"])
+def test_global_threshold_from_replicated_sample_rows(kind):
+    """Thresholds computed from the 32 sample rows alone equal those of a decode over the sequence."""
+    from ffa_speedtest_b200 import sharded
+    from ffa_speedtest_b200.decode import allocate_decode_workspace
+    B, T, HQ, HKV, BS = 2, 64 * 37 + 5, 8, 2, 128
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, 128, seed=77, n_heavy=3)
+    coarse, res = fo.make_coarse(kind, k, torch.float8_e4m3fn, BS)
+    ws = allocate_decode_workspace(q.cuda(), v.cuda(), BS=BS, SBS=64)
+    call(kind, q, coarse, v, res, BS=BS, SBS=64, delta=5.0, workspace=ws)
+    r0, r1 = sharded.sample_token_rows(T, BS)
+    codes = coarse.codes.cuda()
+    sample = torch.cat([codes[:, r0.start:r0.stop], codes[:, r1.start:r1.stop]], dim=1).contiguous()
+    scale = None if coarse.scale is None else coarse.scale.cuda()
+    zero = None if getattr(coarse, "zero", None) is None else coarse.zero.cuda()
+    th = sharded.global_threshold(kind, q.cuda(), sample, delta=5.0, k_scale=scale, k_zero=zero)
+    assert torch.equal(th, ws.threshold)
+
+
+@pytest.mark.parametrize("kind,B,T", [("fp8", 8, 32768), ("q2", 4, 131072)])
+def test_full_size_properties(kind, B, T):
+    """BASELINE-sized caches (config 1; config 4 cut to 4 sequences), checked through properties that
+    need no CPU pass over the data: (i) with V = 1 everywhere every output is exactly 1 (softmax
+    weights of the kept pages sum to one), (ii) the two sequence halves, run separately with the
+    global thresholds, merge to the unsplit result, (iii) the kept fraction is that of the mask."""
+    from ffa_speedtest_b200 import quantize as Q
+    from ffa_speedtest_b200.decode import allocate_decode_workspace, decode_call
+    from ffa_speedtest_b200.sharded import merge_partials
+    f8 = torch.float8_e4m3fn
+    q, k, v = make_decode_inputs(B, T, 32, 8, 128, seed=1, device="cuda")
+    scale = zero = None
+    if kind == "fp8":
+        codes, res = Q.quantize_k_fp8_fp8_residual(k, f8)
+    else:
+        codes, scale, zero, res = Q.quantize_k_2bit_fp8_residual(k, f8)
+    del k
+    kw = dict(k_scale=scale, k_zero=zero, BS=64, SBS=64, delta=8.0)
+    ws = allocate_decode_workspace(q, v, BS=64)
+    o, skip = decode_call(kind, q, codes, v, k_residual=res, workspace=ws, return_skip_ratio=True, **kw)
+    o = o.clone()
+    assert ws.status() == 0 and torch.isfinite(o.float()).all()
+    assert abs(skip - (1.0 - float(ws.mask.float().mean()))) < 1e-6 and 0.02 < skip < 0.5
+    th = ws.threshold.clone()
+
+    ones = torch.ones_like(v)
+    o1 = decode_call(kind, q, codes, ones, k_residual=res, workspace=ws, **kw)
+    assert bool((o1.float() == 1.0).all())
+    del ones
+
+    half = T // 2
+    parts = torch.empty((2, B, 32, 129), dtype=torch.float32, device="cuda")
+    for i, (a, b) in enumerate(((0, half), (half, T))):
+        decode_call(kind, q, codes[:, a:b].contiguous(), v[:, a:b].contiguous(), k_residual=res[:, a:b].contiguous(),
+                    precomputed_threshold=th, partial_out=parts[i], **kw)
+    merged = merge_partials(parts, torch.bfloat16)
+    assert (merged.float() - o.float()).abs().max().item() <= 2.0 ** -7 * max(1.0, o.float().abs().max().item())

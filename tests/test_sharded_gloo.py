@@ -146,3 +146,15 @@ def test_missing_rank_surfaces_as_error_not_hang():
     ret = mp.Manager().dict()
     mp.spawn(_failing_rank_worker, args=(2, port, ret), nprocs=2, join=True)
     assert ret[1] == "left" and str(ret[0]).startswith("error"), dict(ret)
+
+
+def test_sample_token_rows_match_the_oracle_sampling():
+    """The rows a rank replicates for the global threshold are the ones the oracle samples."""
+    from ffa_speedtest_b200.sharded import sample_token_rows
+    for T, BS in ((4096, 64), (2373, 128), (524288, 64), (64, 64)):
+        ntb = -(-T // BS)
+        r0, r1 = sample_token_rows(T, BS)
+        assert list(r0) == list(range(16))
+        assert list(r1) == [(ntb - 1) * fo.THRESHOLD_SAMPLE + i for i in range(fo.THRESHOLD_SAMPLE)]
+    with pytest.raises(ValueError):
+        sample_token_rows(10, 64)
