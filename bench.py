@@ -359,8 +359,10 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
 
     for _ in range(W):
         step()
-    barrier()
+    # the sampler takes a moment to start: start it before the barrier, or the other ranks would
+    # spend the first steps of their timed loop waiting for this one in the all-gather
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -537,8 +539,8 @@ def main():
     # ---- device-timed region: K steps, cache resident in HBM (inputs >> L2, no flush needed) ------
     for _ in range(W):
         run()
+    sampler = ClockSampler(local_rank) if rank == 0 else None     # started before the barrier that aligns the ranks
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
