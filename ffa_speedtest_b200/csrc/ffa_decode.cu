@@ -541,6 +541,37 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace ffa
 
+namespace ffa {
+namespace {
+// Prune granularity above one page: one thread per (b, kv-head, group of m pages).  The group is
+// pruned only if every head's maximum coarse score over all its pages is strictly below that head's
+// threshold (reference ...q2fp8.py:85-113 with SBS = 64 m); the flag is copied to each page.
+__global__ void group_keep_kernel(const float* __restrict__ page_max, const float* __restrict__ th, int B, int HKV,
+                                  int G, int NP, int m, int n_groups, int NTBS, int8_t* __restrict__ page_keep,
+                                  int8_t* __restrict__ mask) {
+  // NTBS counts whole BS blocks, so it can exceed the groups that hold tokens: those read "not kept"
+  const int per_unit = max(n_groups, NTBS);
+  const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (idx >= static_cast<int64_t>(B) * HKV * per_unit) return;
+  const int grp = static_cast<int>(idx % per_unit);
+  const int64_t unit = idx / per_unit;                         // b * HKV + hkv
+  if (grp >= n_groups) {
+    if (mask) mask[unit * NTBS + grp] = 0;
+    return;
+  }
+  const int p0 = grp * m, p1 = min(NP, p0 + m);
+  bool keep = false;
+  for (int h = 0; h < G && !keep; ++h) {
+    const int64_t row = unit * G + h;                          // (b * HQ + hkv * G + h)
+    const float t = th[row];
+    for (int pg = p0; pg < p1; ++pg) keep = keep || !(page_max[row * NP + pg] < t);
+  }
+  for (int pg = p0; pg < p1; ++pg) page_keep[unit * NP + pg] = keep ? 1 : 0;
+  if (mask && grp < NTBS) mask[unit * NTBS + grp] = keep ? 1 : 0;
+}
+}  // namespace
+}  // namespace ffa
+
 using namespace ffa;
 
 extern "C" int ffa_decode_plan(int32_t B, int32_t T, int32_t HKV, int32_t ppc_in, int32_t* ppc_out,
@@ -568,8 +599,11 @@ extern "C" size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, i
   decode_tma_plan(B, HKV, (T + kPage - 1) / kPage, ppc_in, 4, &wc, &nch_tma);   // 4 CTAs per SM at most
   if (nch_tma > nch) nch = nch_tma;            // either kernel may run: size for the larger plan
   const size_t rows = static_cast<size_t>(B) * HQ;
+  // + per-page maxima, per-page keep flags and thresholds of the two-launch path (SBS above 64)
+  const size_t NP = static_cast<size_t>((T + kPage - 1) / kPage);
   return kArrivalBytes + align_up(rows * nch * sizeof(float), 256) * 2 +
-         align_up(rows * nch * kHeadDim * sizeof(float), 256) + 256;
+         align_up(rows * nch * kHeadDim * sizeof(float), 256) + 256 + align_up(rows * NP * sizeof(float), 256) +
+         align_up(static_cast<size_t>(B) * HKV * NP, 256) + align_up(rows * sizeof(float), 256);
 }
 
 extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
@@ -578,7 +612,7 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   if (a->B <= 0 || a->T <= 0 || a->HKV <= 0 || a->HQ <= 0 || a->HQ % a->HKV != 0) return FFA_E_SHAPE;
   const int G = a->HQ / a->HKV;
   if (G > 8 || a->head_dim != kHeadDim) return FFA_E_SHAPE;
-  if (a->SBS != kPage || a->BS < kPage || a->BS % kPage != 0) return FFA_E_SHAPE;
+  if (a->SBS < kPage || a->SBS % kPage != 0 || a->BS < a->SBS || a->BS % a->SBS != 0) return FFA_E_SHAPE;
   if (a->q_dtype < FFA_F16 || a->q_dtype > FFA_F32) return FFA_E_DTYPE;
   if (a->v_dtype != FFA_F16 && a->v_dtype != FFA_BF16) return FFA_E_DTYPE;
   if (a->fp8_format != FFA_E5M2 && a->fp8_format != FFA_E4M3) return FFA_E_DTYPE;
@@ -637,8 +671,31 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   p.partial_out = a->partial_out;
 
   int rc;
+  const int m = a->SBS / kPage;                 // pages per prune group
+  if (m > 1 && !use_tma) return FFA_E_SHAPE;    // the fp16 tensor-core kernel prunes page by page only
   if (use_tma) {
     const int64_t kv_rows = a->kv_rows > 0 ? a->kv_rows : static_cast<int64_t>(a->B) * a->T;
+    if (m > 1) {
+      // score all pages, decide per group of m pages, then run the step with the decisions given
+      const size_t pm_bytes = align_up(rows * p.NP * sizeof(float), 256);
+      const size_t pk_bytes = align_up(static_cast<size_t>(a->B) * a->HKV * p.NP, 256);
+      const size_t th_bytes = align_up(rows * sizeof(float), 256);
+      if (a->workspace_bytes < need + pm_bytes + pk_bytes + th_bytes) return FFA_E_WORKSPACE;
+      float* page_max = reinterpret_cast<float*>(ws + need);
+      int8_t* page_keep = reinterpret_cast<int8_t*>(ws + need + pm_bytes);
+      float* th = a->threshold_out ? a->threshold_out : reinterpret_cast<float*>(ws + need + pm_bytes + pk_bytes);
+      DecodeParams ps = p;
+      ps.mode = 1; ps.page_max = page_max; ps.mask = nullptr; ps.th_out = th;
+      rc = launch_decode_tma(ps, a->variant, a->fp8_format, kv_rows, stream);
+      if (rc != FFA_OK) return rc;
+      const int n_groups = (p.NP + m - 1) / m;
+      const int64_t threads = static_cast<int64_t>(a->B) * a->HKV * (n_groups > p.NTBS ? n_groups : p.NTBS);
+      group_keep_kernel<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, stream>>>(
+          page_max, th, a->B, a->HKV, G, p.NP, m, n_groups, p.NTBS, page_keep, a->kept_mask);
+      cudaError_t ge = cudaGetLastError();
+      if (ge != cudaSuccess) return note_cuda_error(ge, "group_keep launch");
+      p.mode = 2; p.page_keep = page_keep; p.mask = nullptr; p.th_in = th; p.th_out = nullptr;
+    }
     rc = launch_decode_tma(p, a->variant, a->fp8_format, kv_rows, stream);
   } else
   switch (a->variant) {

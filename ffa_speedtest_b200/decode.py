@@ -139,9 +139,12 @@ def decode_call(
         scale = 1.0 / math.sqrt(K)
     if SBS is None:
         SBS = BS
-    if SBS != PAGE or BS % PAGE != 0:
-        raise ValueError(f"this build prunes at page granularity: SBS must be 64 and BS a multiple of 64 "
-                         f"(got BS={BS}, SBS={SBS})")
+    if SBS % PAGE != 0 or SBS < PAGE or BS % SBS != 0:
+        raise ValueError(f"this build prunes in units of 64-token pages: SBS must be a multiple of 64 and BS a "
+                         f"multiple of SBS (got BS={BS}, SBS={SBS})")
+    if SBS != PAGE and (kernel == "fp16" or not (q.dtype == torch.bfloat16 or
+                                                   (q.dtype == torch.float16 and v.dtype == torch.float16))):
+        raise ValueError("SBS above 64 needs the TMA kernel: bfloat16 q, or float16 q with float16 v")
     NTB = -(-T // BS)
     NTBS = NTB * (BS // SBS)
 

@@ -59,8 +59,9 @@ typedef struct FfaDecodeArgs {
   int32_t variant;          /* FFA_K_*                                                          */
   int32_t B, T, HQ, HKV;    /* batch, context length, query heads, kv heads (G = HQ/HKV <= 8)   */
   int32_t head_dim;         /* K = V = 128                                                      */
-  int32_t BS, SBS;          /* reference block sizes; SBS (prune granularity) must be 64,
-                               BS a multiple of 64                                              */
+  int32_t BS, SBS;          /* reference block sizes: SBS (prune granularity) a multiple of 64,
+                               BS a multiple of SBS.  SBS = 64 is one launch; a larger SBS runs a
+                               scoring pass, a group decision and the step (bf16 / fp16 q only)  */
   float sm_scale;           /* softmax scale, reference default 1/sqrt(K)                       */
   float delta;              /* threshold offset in log2 units                                   */
   int32_t q_dtype;          /* FFA_F16 | FFA_BF16 | FFA_F32; the output has the same type       */

