@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 A "step" is one decode-attention call over one batch of synthetic K/V cache (one pass of the hot
-path).  The default workload is BASELINE config 1: fp8 K + fp8 residual ("fp8fp8"), batch 8,
+path).  The default workload is the reference's headline configuration: fp8 K + fp8 residual ("fp8fp8"), batch 8,
 32 query / 8 kv heads, head_dim 128, context 32768, page 64, delta 8, bf16 V as in the reference.
 With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank owns its own batch
 of the same size - the (batch x kv-head) units are sharded with no data-path collective - so the
@@ -62,12 +62,13 @@ HQ, HKV, D, PAGE = 32, 8, 128, 64
 CODE_BYTES = {"fp8": 128, "q2": 32, "fp4": 64, "nf4": 64, "nvfp4": 64}
 # dram__bytes_read+write / algorithmic bytes of the stage-1 kernel, from the committed ncu capture
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.02
-METRIC = "decode_attn_achieved_hbm_TBps"   # BASELINE metric: decode-attn us/step and achieved HBM TB/s
+METRIC = "decode_attn_achieved_hbm_TBps"   # the headline metric: decode-attn us/step and achieved HBM TB/s
 UNIT = "TB/s"
 
 
 def algorithmic_bytes(kind: str, B: int, T: int, kept_fraction: float, paged: bool) -> float:
-    """Bytes one decode step has to touch."""
+    """Bytes one decode step has to touch: coarse codes of every page, residual + V of the kept
+    pages, block table, scales, q and o."""
     n_pages = -(-T // PAGE)
     coarse = B * HKV * T * CODE_BYTES[kind]
     refine = kept_fraction * B * HKV * T * (128 + 256)           # fp8 residual + bf16 V

@@ -85,7 +85,7 @@ def test_against_reference_goldens(kind, name, kernel):
 @pytest.mark.parametrize("kernel", ["auto", "fp16"])
 @pytest.mark.parametrize("fp8", ["e5m2", "e4m3"])
 def test_config0_q2fp8(fp8, kernel):
-    """BASELINE config 0: B=1, 32 q / 8 kv heads, T=4096, page 64, delta 8."""
+    """benchmark config 0: B=1, 32 q / 8 kv heads, T=4096, page 64, delta 8."""
     from ffa_speedtest_b200.decode import allocate_decode_workspace
     z = np.load(GOLDEN / f"decode_q2_config0_{fp8}.npz")
     q, k, v = make_decode_inputs(1, 4096, 32, 8, 128, seed=0, dtype=torch.bfloat16)
@@ -267,7 +267,7 @@ def test_global_threshold_from_replicated_sample_rows(kind):
 
 @pytest.mark.parametrize("kind,B,T", [("fp8", 8, 32768), ("q2", 4, 131072)])
 def test_full_size_properties(kind, B, T):
-    """BASELINE-sized caches (config 1; config 4 cut to 4 sequences), checked through properties that
+    """benchmark-sized caches (config 1; config 4 cut to 4 sequences), checked through properties that
     need no CPU pass over the data: (i) with V = 1 everywhere every output is exactly 1 (softmax
     weights of the kept pages sum to one), (ii) the two sequence halves, run separately with the
     global thresholds, merge to the unsplit result, (iii) the kept fraction is that of the mask."""

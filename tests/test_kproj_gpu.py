@@ -113,7 +113,7 @@ def test_scatter_into_paged_cache():
 
 
 def test_large_tile_count_against_cublas():
-    """T = 8192 (BASELINE config 3): 512 output tiles; cuBLAS + eager RoPE on the same GPU as a
+    """T = 8192 (benchmark config 3): 512 output tiles; cuBLAS + eager RoPE on the same GPU as a
     second opinion (not the oracle: its accumulation order is its own)."""
     T, H, HKV = 8192, 4096, 8
     h, w = make_kproj_inputs(T, H, HKV, 128, B=1, seed=3, device="cuda")

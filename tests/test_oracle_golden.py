@@ -42,7 +42,7 @@ def test_decode_matches_reference_kernels(kind, name):
 
 @pytest.mark.parametrize("fp8", ["e5m2", "e4m3"])
 def test_config0_q2fp8(fp8):
-    """BASELINE config 0 (B=1, 32/8 heads, T=4096, page 64, delta 8): oracle vs reference."""
+    """benchmark config 0 (B=1, 32/8 heads, T=4096, page 64, delta 8): oracle vs reference."""
     z = np.load(GOLDEN / f"decode_q2_config0_{fp8}.npz")
     q, k, v = make_decode_inputs(1, 4096, 32, 8, 128, seed=0, dtype=torch.bfloat16)
     coarse, res = fo.make_coarse("q2", k, FP8[fp8], 64)
