@@ -245,12 +245,17 @@ def decode_attention(
     use_fp8_residual: bool = True,
     out_dtype: Optional[torch.dtype] = None,
     return_parts: bool = False,
+    mean_v: Optional[torch.Tensor] = None,                  # [B, HKV, V]: the mean-V variant
 ):
     """Stage 1 + stage 2 of the reference decode path on CPU.
 
     Returns ``o [B,HQ,V]`` (and, with ``return_parts``, a dict holding the kept mask
     ``[B,HKV,NTBS]`` int8, the thresholds ``[B,HQ]`` and the per-block coarse maxima
-    ``[B,HQ,NTBS]``)."""
+    ``[B,HQ,NTBS]``).
+
+    With ``mean_v`` the pruned sub-blocks are not dropped: each contributes its coarse softmax mass
+    times the mean of V (ffa-q2fp8-meanv/attn_kernel/attn_kernel_v1210_meanv_bsz_q2fp8.py:107-119
+    for the per-block (m, l), :169-200 for the separate scalar recurrence and the final fold)."""
     if q.dim() == 4:
         q = q[:, 0]
     B, HQ, K = q.shape
@@ -277,6 +282,8 @@ def decode_attention(
     run_m = torch.full((B, HKV, G), float("-inf"))
     run_l = torch.zeros(B, HKV, G)
     run_o = torch.zeros(B, HKV, G, V)
+    apx_m = torch.full((B, HKV, G), float("-inf"))          # mean-V: running max / mass of pruned blocks
+    apx_l = torch.zeros(B, HKV, G)
 
     for tb in range(NTB):
         for sb in range(NSB):
@@ -293,6 +300,13 @@ def decode_attention(
             blk_max[..., idx] = m_c
             keep = ~((m_c < th).all(dim=-1))             # strict <, all heads of the group
             mask[..., idx] = keep.to(torch.int8)
+            if mean_v is not None and not bool(keep.all()):
+                p_c = torch.where(live, torch.exp2(s_c - m_c.unsqueeze(-1)), torch.tensor(0.0))
+                l_c = p_c.sum(dim=-1)
+                new_m = torch.maximum(apx_m, m_c)
+                pr = ~keep.unsqueeze(-1)                                 # pruned (b, kv-head)s
+                apx_l = torch.where(pr, apx_l * torch.exp2(apx_m - new_m) + l_c * torch.exp2(m_c - new_m), apx_l)
+                apx_m = torch.where(pr, new_m, apx_m)
             if not bool(keep.any()):
                 continue
             if use_res:
@@ -315,7 +329,16 @@ def decode_attention(
             run_o = torch.where(kp.unsqueeze(-1), run_o * r_prev.unsqueeze(-1) + o_b * r_blk.unsqueeze(-1), run_o)
             run_m = torch.where(kp, new_m, run_m)
 
-    out = torch.where((run_l == 0).unsqueeze(-1), torch.zeros_like(run_o), run_o / run_l.unsqueeze(-1))
+    if mean_v is None:
+        out = torch.where((run_l == 0).unsqueeze(-1), torch.zeros_like(run_o), run_o / run_l.unsqueeze(-1))
+    else:
+        have_any = (run_l > 0) | (apx_l > 0)
+        new_m = torch.where(have_any, torch.maximum(run_m, apx_m), torch.zeros_like(run_m))
+        r_b, r_p = torch.exp2(run_m - new_m), torch.exp2(apx_m - new_m)
+        acc = run_l * r_b + apx_l * r_p
+        mv = mean_v.to(torch.float32).unsqueeze(2)                       # [B,HKV,1,V]
+        o_t = run_o * r_b.unsqueeze(-1) + mv * (apx_l * r_p).unsqueeze(-1)
+        out = torch.where(have_any.unsqueeze(-1), o_t / acc.unsqueeze(-1), torch.zeros_like(o_t))
     out = out.reshape(B, HQ, V).to(out_dtype or q.dtype)
     if return_parts:
         return out, {

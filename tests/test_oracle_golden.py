@@ -111,3 +111,23 @@ def test_kproj_reference_goldens(kind, T):
         got = t.view(torch.uint8).numpy() if t.dtype == torch.float8_e4m3fn else (
             t.view(torch.int16).numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.numpy())
         assert np.array_equal(got, ref), f"output {i} differs"
+
+
+@pytest.mark.parametrize("name", ["meanv_ragged", "meanv_fp16"])
+def test_mean_v_variant_matches_the_reference(name):
+    """Pruned blocks folded in as coarse mass x mean(V): oracle against the reference's mean-V kernels."""
+    z = np.load(GOLDEN / f"decode_q2_{name}.npz")
+    B, T, HQ, HKV, D, BS, SBS, seed, n_heavy = (int(x) for x in z["meta"])
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16}[str(z["dtype"])]
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, D, seed=seed, dtype=dt, n_heavy=n_heavy)
+    assert digest(q, k, v) == str(z["sha_inputs"])
+    coarse, res = fo.make_coarse("q2", k, FP8[str(z["fp8"])], BS)
+    mean_v = v.mean(dim=1, dtype=torch.float32).to(v.dtype)
+    o, parts = fo.decode_attention(q, coarse, v, res, BS=BS, SBS=SBS, delta=float(z["delta"]), mean_v=mean_v,
+                                   out_dtype=torch.float32, return_parts=True)
+    approx = torch.from_numpy(z["approx"])
+    # a block is approximated exactly when it holds tokens and was pruned
+    n_sub = -(-T // SBS)
+    has_tokens = (torch.arange(approx.shape[-1]) < n_sub).view(1, 1, -1)
+    assert torch.equal((parts["mask"] == 0) & has_tokens, approx.bool())
+    torch.testing.assert_close(o, torch.from_numpy(z["o"]), rtol=0, atol=1e-4)
