@@ -48,6 +48,7 @@ class FfaDecodeArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("pages_per_chunk", C.c_int32), ("reserved", C.c_int32),
         ("kv_rows", C.c_int64),
+        ("v_mean", C.c_void_p),
     ]
 
 

@@ -601,7 +601,7 @@ extern "C" size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, i
   const size_t rows = static_cast<size_t>(B) * HQ;
   // + per-page maxima, per-page keep flags and thresholds of the two-launch path (SBS above 64)
   const size_t NP = static_cast<size_t>((T + kPage - 1) / kPage);
-  return kArrivalBytes + align_up(rows * nch * sizeof(float), 256) * 2 +
+  return kArrivalBytes + align_up(rows * nch * sizeof(float), 256) * 4 +
          align_up(rows * nch * kHeadDim * sizeof(float), 256) + 256 + align_up(rows * NP * sizeof(float), 256) +
          align_up(static_cast<size_t>(B) * HKV * NP, 256) + align_up(rows * sizeof(float), 256);
 }
@@ -658,7 +658,7 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   const size_t rows = static_cast<size_t>(a->B) * a->HQ;
   const size_t ml = align_up(rows * p.nch * sizeof(float), 256);
   const size_t po = align_up(rows * p.nch * kHeadDim * sizeof(float), 256);
-  const size_t need = kArrivalBytes + ml * 2 + po + 256;
+  const size_t need = kArrivalBytes + ml * 4 + po + 256;          // m, l, mean-V (m, l), o, legacy status
   if (a->workspace_bytes < need) return FFA_E_WORKSPACE;
   if (static_cast<size_t>(a->B) * a->HKV * sizeof(int) > kArrivalBytes - 256) return FFA_E_LIMIT;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
@@ -669,6 +669,13 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   p.status = reinterpret_cast<int*>(ws + kArrivalBytes - 256);      // fixed place: end of the counter block
   p.out = a->out;
   p.partial_out = a->partial_out;
+  p.part_pm = reinterpret_cast<float*>(ws + kArrivalBytes + 2 * ml + po + 256);
+  p.part_pl = reinterpret_cast<float*>(ws + kArrivalBytes + 3 * ml + po + 256);
+  p.v_mean = a->v_mean;
+  if (a->v_mean) {
+    // mean-V: 2-bit format on the TMA kernel, final output only (a partial would need the mass too)
+    if (a->variant != FFA_K_Q2 || !use_tma || a->partial_out) return FFA_E_SHAPE;
+  }
 
   int rc;
   const int m = a->SBS / kPage;                 // pages per prune group

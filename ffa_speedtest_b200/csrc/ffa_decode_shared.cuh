@@ -67,6 +67,11 @@ struct DecodeParams {
   int mode;
   float* page_max;           // mode 1: [B*HQ, NP]
   const int8_t* page_keep;   // mode 2: [B*HKV, NP]
+  // mean-V variant (q2 only): pruned pages contribute their coarse softmax mass times the mean of V.
+  // Every segment adds the running maximum and mass of its pruned pages to its partial.
+  const void* v_mean;        // [B*HKV, 128] in V's dtype, or null
+  float* part_pm;            // [B*HQ, nch]
+  float* part_pl;            // [B*HQ, nch]
 };
 
 

@@ -310,7 +310,8 @@ __device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t x) {
 // long; the part of the range inside one (b, kv-head) is a "segment" and produces one partial.
 // QP: e4m3 pieces per q value (2 for bf16 q, 3 for fp16 q: 4 + 4 + 3 significant bits).
 // Three CTAs per SM for up to four q heads per kv head (at most 168 registers), two beyond that.
-template <int FMT, int F8, int NT, bool VBF, int kDA, int QP>
+// MV: the mean-V variant (pruned pages keep their coarse softmax mass; see DecodeParams::v_mean).
+template <int FMT, int F8, int NT, bool VBF, int kDA, int QP, bool MV>
 __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(const __grid_constant__ DecodeParams p,
                                                               const __grid_constant__ CUtensorMap tm_c,
                                                               const __grid_constant__ CUtensorMap tm_r,
@@ -578,6 +579,9 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
       for (int d = 0; d < kDA; ++d) hist[d][nt][0] = hist[d][nt][1] = 0.f;
     }
     uint32_t keepq = 0;
+    float apx_m[NT], apx_l[NT], cs[NT][2];       // mean-V: running max / mass of the pruned pages, page scores
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { apx_m[nt] = -INFINITY; apx_l[nt] = 0.f; cs[nt][0] = cs[nt][1] = -INFINITY; }
 
     // (the __syncthreads after the sample scoring, or after the q set-up, orders every warp's reads
     // of slots 0 and 1 before they are refilled)
@@ -608,6 +612,7 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
         for (int nt = 0; nt < NT; ++nt) {
           const float s0 = tok < T ? to_log2(dc[nt][0]) : -INFINITY;
           const float s1 = tok + 8 < T ? to_log2(dc[nt][1]) : -INFINITY;
+          if (MV) { cs[nt][0] = s0; cs[nt][1] = s1; }
           float mm = fmaxf(s0, s1);
 #pragma unroll
           for (int off = 4; off < 32; off <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
@@ -675,6 +680,21 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
           keep = p.page_keep[(static_cast<int64_t>(b) * p.HKV + hkv) * p.NP + page_begin + j] != 0;
         } else
         keep = !__all_sync(0xffffffffu, below);     // pruned only if every head is strictly below
+        if (MV && !keep && p.mode != 1) {
+          // pruned page: its coarse scores relative to the page maximum join the running mass
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const float mc = cm[nt];
+            if (mc != -INFINITY) {
+              const float pp = (cs[nt][0] == -INFINITY ? 0.f : ex2_approx(cs[nt][0] - mc)) +
+                               (cs[nt][1] == -INFINITY ? 0.f : ex2_approx(cs[nt][1] - mc));
+              const float nm = fmaxf(apx_m[nt], mc);
+              const float rp = apx_m[nt] == -INFINITY ? 0.f : ex2_approx(apx_m[nt] - nm);
+              apx_l[nt] = apx_l[nt] * rp + pp * ex2_approx(mc - nm);
+              apx_m[nt] = nm;
+            }
+          }
+        }
         if (keep) fills ^= 1u << (kNBase + j % kNRv);
         if (tid == 0) {
           if (keep) issue_rv(j);
@@ -758,6 +778,14 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
       const int h = 4 * nt + t;
       if (g == 0) lred[warp * 8 + h] = l;
       if (warp == 0 && g == 0) mred[h] = run_m[nt];
+      if (MV) {
+        // every thread folded the same page maxima, so only the masses need adding up
+        float al = apx_l[nt];
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) al += __shfl_xor_sync(0xffffffffu, al, off);
+        if (g == 0) mred[16 + warp * 8 + h] = al;
+        if (warp == 0 && g == 0) mred[48 + h] = apx_m[nt];
+      }
       float* w = red + warp * 1024 + h * 128;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -775,6 +803,10 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
     if (tid < G) {
       p.part_m[(row0 + tid) * p.nch + part] = mred[tid];
       p.part_l[(row0 + tid) * p.nch + part] = lred[tid] + lred[8 + tid] + lred[16 + tid] + lred[24 + tid];
+      if (MV) {
+        p.part_pm[(row0 + tid) * p.nch + part] = mred[48 + tid];
+        p.part_pl[(row0 + tid) * p.nch + part] = mred[16 + tid] + mred[24 + tid] + mred[32 + tid] + mred[40 + tid];
+      }
     }
     if (p.mask && page_begin + n == p.NP) {
       for (int i = p.NP + tid; i < p.NTBS; i += kThreads)
@@ -785,7 +817,7 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
     // Every segment publishes its partial, then bumps the unit's arrival counter; whoever sees all the
     // others already there merges the partials in page order and resets the counter for the next launch.
     const int n_seg = static_cast<int>((unit0 + p.NP - 1) / p.ppc - unit0 / p.ppc) + 1;
-    int* s_flag = reinterpret_cast<int*>(mred + 8);
+    int* s_flag = reinterpret_cast<int*>(mred + 8);       // mred + 16 .. + 56 belong to the mean-V sums
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -805,6 +837,10 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
         const int h = idx / per_head, i = idx % per_head;
         sm_m[h * 64 + i] = __ldcg(p.part_m + (row0 + h) * p.nch + i);
         sm_l[h * 64 + i] = __ldcg(p.part_l + (row0 + h) * p.nch + i);
+        if (MV) {
+          sm_l[8 * 64 + h * 64 + i] = __ldcg(p.part_pm + (row0 + h) * p.nch + i);
+          sm_l[16 * 64 + h * 64 + i] = __ldcg(p.part_pl + (row0 + h) * p.nch + i);
+        }
       }
       __syncthreads();
       for (int h = warp; h < G; h += kWarps) {
@@ -830,6 +866,27 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
             const int i = i0 + j;
             if (i < per_head) acc += sm_l[h * 64 + i] * w[j];
             o.x += v[j].x * w[j]; o.y += v[j].y * w[j]; o.z += v[j].z * w[j]; o.w += v[j].w * w[j];
+          }
+        }
+        if (MV) {
+          // fold the pruned pages in: mass x mean of V (...meanv_bsz_q2fp8.py:188-200)
+          const float* sm_pm = sm_l + 8 * 64;
+          const float* sm_pl = sm_l + 16 * 64;
+          float p_top = -INFINITY, p_acc = 0.f;
+          for (int i = 0; i < per_head; ++i)
+            if (sm_pl[h * 64 + i] != 0.f) p_top = fmaxf(p_top, sm_pm[h * 64 + i]);
+          for (int i = 0; i < per_head; ++i)
+            if (sm_pl[h * 64 + i] != 0.f) p_acc += sm_pl[h * 64 + i] * exp2f(sm_pm[h * 64 + i] - p_top);
+          if (acc > 0.f || p_acc > 0.f) {
+            const float nm = fmaxf(top, p_top);
+            const float rb = acc > 0.f ? exp2f(top - nm) : 0.f, rp = p_acc > 0.f ? exp2f(p_top - nm) : 0.f;
+            const int64_t ve = (static_cast<int64_t>(b) * p.HKV + hkv) * kHeadDim + 4 * lane;
+            const float wv = p_acc * rp;
+            o.x = o.x * rb + load_as_float(p.v_mean, ve, p.v_bf16 ? FFA_BF16 : FFA_F16) * wv;
+            o.y = o.y * rb + load_as_float(p.v_mean, ve + 1, p.v_bf16 ? FFA_BF16 : FFA_F16) * wv;
+            o.z = o.z * rb + load_as_float(p.v_mean, ve + 2, p.v_bf16 ? FFA_BF16 : FFA_F16) * wv;
+            o.w = o.w * rb + load_as_float(p.v_mean, ve + 3, p.v_bf16 ? FFA_BF16 : FFA_F16) * wv;
+            acc = acc * rb + wv;
           }
         }
         const float inv = acc == 0.f ? 0.f : 1.f / acc;
@@ -888,11 +945,11 @@ bool make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t row_bytes_
 // Launches the kernel, or (stream == kQueryResidency) returns how many of its CTAs fit on an SM.
 const cudaStream_t kQueryResidency = reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(-16));
 
-template <int FMT, int F8, int NT, bool VBF, int DA, int QP>
+template <int FMT, int F8, int NT, bool VBF, int DA, int QP, bool MV = false>
 int launch_one(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
                cudaStream_t stream) {
   using L = SmemT<FMT, DA>;
-  auto kern = decode_tma_kernel<FMT, F8, NT, VBF, DA, QP>;
+  auto kern = decode_tma_kernel<FMT, F8, NT, VBF, DA, QP, MV>;
   static bool configured[64] = {};
   static int resident[64] = {};
   int dev = 0;
@@ -921,6 +978,13 @@ int launch_one(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& 
 template <int FMT, int F8, int NT>
 int launch_types(const DecodeParams& p, const CUtensorMap& mc, const CUtensorMap& mr, const CUtensorMap& mv,
                  cudaStream_t stream) {
+  if constexpr (FMT == FFA_K_Q2) {
+    if (p.v_mean) {                                  // mean-V variant: 2-bit format only, like the reference
+      if (p.q_dtype == FFA_F16) return launch_one<FMT, F8, NT, false, 1, 3, true>(p, mc, mr, mv, stream);
+      return p.v_bf16 ? launch_one<FMT, F8, NT, true, 1, 2, true>(p, mc, mr, mv, stream)
+                      : launch_one<FMT, F8, NT, false, 1, 2, true>(p, mc, mr, mv, stream);
+    }
+  }
   if (p.q_dtype == FFA_F16) return launch_one<FMT, F8, NT, false, 1, 3>(p, mc, mr, mv, stream);
   return p.v_bf16 ? launch_one<FMT, F8, NT, true, 1, 2>(p, mc, mr, mv, stream)
                   : launch_one<FMT, F8, NT, false, 1, 2>(p, mc, mr, mv, stream);

@@ -107,8 +107,12 @@ def decode_call(
     partial_out: Optional[torch.Tensor] = None,
     pages_per_chunk: int = 0,
     kernel: str = "auto",
+    mean_v: Optional[torch.Tensor] = None,
 ):
     """Shape bookkeeping shared by the five entry points; tensors are already type-checked.
+
+    ``mean_v [B, HKV, 128]`` (V's dtype) selects the mean-V variant of the 2-bit format: pruned pages
+    are not dropped but contribute their coarse softmax mass times this vector.
 
     ``kernel``: "auto" picks the TMA / fp8 tensor-core kernel when q is bfloat16, or float16 with
     float16 V, and the fp16 tensor-core kernel otherwise; "fp16" forces the latter (it follows the reference's fp16
@@ -193,6 +197,15 @@ def decode_call(
     a.kept_mask = workspace.mask.data_ptr()
     a.threshold_out = workspace.threshold.data_ptr()
     a.partial_out = _lib.ptr(partial_out)
+    if mean_v is not None:
+        if variant != "q2":
+            raise ValueError("the mean-V variant exists for the 2-bit format only")
+        if mean_v.shape != (B, HKV, V) or mean_v.dtype != v.dtype or not mean_v.is_cuda:
+            raise ValueError(f"mean_v must be a CUDA tensor [B, HKV, V] = [{B}, {HKV}, {V}] of v's dtype")
+        if partial_out is not None or kernel == "fp16":
+            raise ValueError("the mean-V variant has no partial output and runs on the TMA kernel only")
+        mean_v = mean_v.contiguous()
+    a.v_mean = _lib.ptr(mean_v)
     a.workspace = workspace.scratch.data_ptr()
     a.workspace_bytes = workspace.scratch.numel()
     a.pages_per_chunk = pages_per_chunk

@@ -50,6 +50,7 @@ def attn_forward_decode_quantized(
     partial_out: torch.Tensor | None = None,
     pages_per_chunk: int = 0,
     kernel: str = "auto",
+    mean_v: torch.Tensor | None = None,
     **kwargs,
 ):
     check_common(q, k_q, v, k_residual, "attn_forward_decode_quantized")
@@ -76,4 +77,4 @@ def attn_forward_decode_quantized(
         "q2", q, k_q, v, k_scale=k_scale, k_zero=k_zero, k_residual=k_residual, scale=scale, BS=BS, SBS=SBS,
         delta=delta, return_skip_ratio=return_skip_ratio, precomputed_threshold=precomputed_threshold,
         use_fp8_residual=use_fp8_residual, block_table=block_table, seq_len=seq_len, workspace=workspace, out=out,
-        partial_out=partial_out, pages_per_chunk=pages_per_chunk, kernel=kernel)
+        partial_out=partial_out, pages_per_chunk=pages_per_chunk, kernel=kernel, mean_v=mean_v)

@@ -93,6 +93,10 @@ typedef struct FfaDecodeArgs {
   int32_t reserved;         /* bit 0: use the fp16 tensor-core kernel even when the TMA/fp8 kernel
                                applies (bf16 q); 0 otherwise                                    */
   int64_t kv_rows;          /* token rows in the K/V tensors: pages*64 of a pool, 0 = B*T       */
+  const void* v_mean;       /* optional [B, HKV, 128] in V's type: the mean-V variant
+                               (ffa-q2fp8-meanv/attn_kernel/attn_kernel_v1210_meanv_bsz_q2fp8.py): pruned
+                               pages contribute their coarse softmax mass times this vector.  2-bit
+                               format, bf16 / fp16 q, no partial_out.  NULL = pruned pages are dropped */
 } FfaDecodeArgs;
 
 /* Replaces attn_forward_decode_quantized / _fp8fp8 / _fp4 / _nf4 / _nvfp4fp8 after validation:

@@ -302,3 +302,27 @@ def test_full_size_properties(kind, B, T):
                     precomputed_threshold=th, partial_out=parts[i], **kw)
     merged = merge_partials(parts, torch.bfloat16)
     assert (merged.float() - o.float()).abs().max().item() <= 2.0 ** -7 * max(1.0, o.float().abs().max().item())
+
+
+@pytest.mark.parametrize("name", ["meanv_ragged", "meanv_fp16"])
+def test_mean_v_variant_against_reference_goldens(name):
+    """Pruned pages contribute coarse mass x mean(V): the CUDA path against the reference's mean-V output."""
+    from ffa_speedtest_b200.q2fp8_meanv.attn_kernel.attn_kernel_v1210_meanv_bsz_q2fp8 import attn_forward_decode_quantized
+    z = np.load(GOLDEN / f"decode_q2_{name}.npz")
+    B, T, HQ, HKV, D, BS, SBS, seed, n_heavy = (int(x) for x in z["meta"])
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16}[str(z["dtype"])]
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, D, seed=seed, dtype=dt, n_heavy=n_heavy)
+    coarse, res = fo.make_coarse("q2", k, FP8[str(z["fp8"])], BS)
+    dev = "cuda"
+    o, skip = attn_forward_decode_quantized(q.to(dev), coarse.codes.to(dev), coarse.scale.to(dev), coarse.zero.to(dev),
+                                            v.to(dev), k_residual=res.to(dev), BS=BS, SBS=SBS, delta=float(z["delta"]),
+                                            return_skip_ratio=True)
+    o_ref = torch.from_numpy(z["o"])
+    err = check_output(o, o_ref)
+    assert err <= 6e-3 * max(1.0, o_ref.abs().max().item())
+    assert abs(skip - float(z["approx"].mean())) <= 2.0 / z["approx"].size + 1e-6
+    # and the plain variant differs: the pruned mass matters in these cases
+    from ffa_speedtest_b200.q2fp8.attn_kernel.attn_kernel_v1210_fused_bsz_q2fp8 import attn_forward_decode_quantized as plain
+    o_plain = plain(q.to(dev), coarse.codes.to(dev), coarse.scale.to(dev), coarse.zero.to(dev), v.to(dev),
+                    k_residual=res.to(dev), BS=BS, SBS=SBS, delta=float(z["delta"]))
+    assert (o_plain.float().cpu() - o_ref).abs().max().item() > 2 * err
