@@ -304,7 +304,7 @@ def test_full_size_properties(kind, B, T):
     assert (merged.float() - o.float()).abs().max().item() <= 2.0 ** -7 * max(1.0, o.float().abs().max().item())
 
 
-@pytest.mark.parametrize("name", ["meanv_ragged", "meanv_fp16"])
+@pytest.mark.parametrize("name", ["meanv_ragged", "meanv_fp16", "meanv_sbs128"])
 def test_mean_v_variant_against_reference_goldens(name):
     """Pruned pages contribute coarse mass x mean(V): the CUDA path against the reference's mean-V output."""
     from ffa_speedtest_b200.q2fp8_meanv.attn_kernel.attn_kernel_v1210_meanv_bsz_q2fp8 import attn_forward_decode_quantized

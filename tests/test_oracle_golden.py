@@ -113,7 +113,7 @@ def test_kproj_reference_goldens(kind, T):
         assert np.array_equal(got, ref), f"output {i} differs"
 
 
-@pytest.mark.parametrize("name", ["meanv_ragged", "meanv_fp16"])
+@pytest.mark.parametrize("name", ["meanv_ragged", "meanv_fp16", "meanv_sbs128"])
 def test_mean_v_variant_matches_the_reference(name):
     """Pruned blocks folded in as coarse mass x mean(V): oracle against the reference's mean-V kernels."""
     z = np.load(GOLDEN / f"decode_q2_{name}.npz")
