@@ -201,7 +201,7 @@ size_t ffa_kproj_workspace_bytes(int32_t B, int32_t T, int32_t HKV, int32_t rope
 
 /* Text of the last CUDA runtime error seen by this library on the calling thread ("" if none). */
 const char* ffa_last_cuda_error(void);
-/* Library version, bumped when the ABI changes. */
+/* Library version, bumped when the ABI changes (2: FfaDecodeArgs ends in v_mean; FfaKprojArgs.slot_pos0). */
 int ffa_abi_version(void);
 
 #ifdef __cplusplus
