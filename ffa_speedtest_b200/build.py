@@ -14,7 +14,9 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT = PKG / "libffa_b200.so"
-SOURCES = ["ffa_lib.cu", "ffa_decode.cu", "ffa_decode_tma.cu", "ffa_quantize.cu", "ffa_kproj.cu", "ffa_static.cu"]
+SOURCES = ["ffa_lib.cu", "ffa_decode.cu", "ffa_decode_tma.cu", "ffa_decode_ws.cu", "ffa_decode_ws_fp8.cu",
+           "ffa_decode_ws_q2.cu", "ffa_decode_ws_fp4.cu", "ffa_decode_ws_nf4.cu", "ffa_decode_ws_nvfp4.cu",
+           "ffa_quantize.cu", "ffa_kproj.cu", "ffa_static.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--use_fast_math=false",
@@ -50,7 +52,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     bdir.mkdir(exist_ok=True)
     for src in sources():
         obj = bdir / (src.stem + ".o")
-        cmd = [_nvcc(), *[f for f in NVCC_FLAGS if f != "--use_fast_math=false"], "-c", str(src), "-o", str(obj)]
+        cmd = [_nvcc(), *[f for f in NVCC_FLAGS if f != "--use_fast_math=false"], *os.environ.get("FFA_NVCC_EXTRA", "").split(),
+               "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

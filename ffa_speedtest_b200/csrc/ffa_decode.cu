@@ -541,37 +541,6 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace ffa
 
-namespace ffa {
-namespace {
-// Prune granularity above one page: one thread per (b, kv-head, group of m pages).  The group is
-// pruned only if every head's maximum coarse score over all its pages is strictly below that head's
-// threshold (reference ...q2fp8.py:85-113 with SBS = 64 m); the flag is copied to each page.
-__global__ void group_keep_kernel(const float* __restrict__ page_max, const float* __restrict__ th, int B, int HKV,
-                                  int G, int NP, int m, int n_groups, int NTBS, int8_t* __restrict__ page_keep,
-                                  int8_t* __restrict__ mask) {
-  // NTBS counts whole BS blocks, so it can exceed the groups that hold tokens: those read "not kept"
-  const int per_unit = max(n_groups, NTBS);
-  const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-  if (idx >= static_cast<int64_t>(B) * HKV * per_unit) return;
-  const int grp = static_cast<int>(idx % per_unit);
-  const int64_t unit = idx / per_unit;                         // b * HKV + hkv
-  if (grp >= n_groups) {
-    if (mask) mask[unit * NTBS + grp] = 0;
-    return;
-  }
-  const int p0 = grp * m, p1 = min(NP, p0 + m);
-  bool keep = false;
-  for (int h = 0; h < G && !keep; ++h) {
-    const int64_t row = unit * G + h;                          // (b * HQ + hkv * G + h)
-    const float t = th[row];
-    for (int pg = p0; pg < p1; ++pg) keep = keep || !(page_max[row * NP + pg] < t);
-  }
-  for (int pg = p0; pg < p1; ++pg) page_keep[unit * NP + pg] = keep ? 1 : 0;
-  if (mask && grp < NTBS) mask[unit * NTBS + grp] = keep ? 1 : 0;
-}
-}  // namespace
-}  // namespace ffa
-
 using namespace ffa;
 
 extern "C" int ffa_decode_plan(int32_t B, int32_t T, int32_t HKV, int32_t ppc_in, int32_t* ppc_out,
@@ -594,16 +563,13 @@ extern "C" int ffa_decode_plan(int32_t B, int32_t T, int32_t HKV, int32_t ppc_in
 }
 
 extern "C" size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, int32_t HKV, int32_t ppc_in) {
-  int ppc = 0, nch = 0, wc = 0, nch_tma = 0;
-  if (ffa_decode_plan(B, T, HKV, ppc_in, &ppc, &nch) != FFA_OK) return 0;
-  decode_tma_plan(B, HKV, (T + kPage - 1) / kPage, ppc_in, 4, &wc, &nch_tma);   // 4 CTAs per SM at most
-  if (nch_tma > nch) nch = nch_tma;            // either kernel may run: size for the larger plan
+  if (B <= 0 || T <= 0 || HKV <= 0 || HQ <= 0) return 0;
+  // sized for the most partials either kernel can produce per (b, kv-head); the bound does not
+  // shrink when T grows, so a workspace made for a maximum length serves every shorter one
+  const int nch = decode_nch_bound(B, HKV, (T + kPage - 1) / kPage, ppc_in);
   const size_t rows = static_cast<size_t>(B) * HQ;
-  // + per-page maxima, per-page keep flags and thresholds of the two-launch path (SBS above 64)
-  const size_t NP = static_cast<size_t>((T + kPage - 1) / kPage);
   return kArrivalBytes + align_up(rows * nch * sizeof(float), 256) * 4 +
-         align_up(rows * nch * kHeadDim * sizeof(float), 256) + 256 + align_up(rows * NP * sizeof(float), 256) +
-         align_up(static_cast<size_t>(B) * HKV * NP, 256) + align_up(rows * sizeof(float), 256);
+         align_up(rows * nch * kHeadDim * sizeof(float), 256) + 256;
 }
 
 extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
@@ -643,22 +609,27 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   p.q_dtype = a->q_dtype; p.scale_dtype = a->scale_dtype;
   p.use_res = a->use_residual ? 1 : 0;
   p.v_bf16 = a->v_dtype == FFA_BF16 ? 1 : 0;
-  const bool want_tma = (a->reserved & 1) == 0;          // reserved bit 0: force the fp16 path
-  // Refine lag (pages between scoring and refining): 1 for every format.  A lag of 2 keeps one more
-  // page of residual+V in flight per CTA, but the smaller ring of lag 1 lets a third CTA live on the
-  // SM, which hides more latency than the deeper ring did (fp8 coarse, B=8, T=32K: 169 us against
-  // 177 us; the 2-/4-bit formats gain 15-20 %).
+  // reserved bit 0 forces the fp16 tensor-core kernel; bit 1 selects the earlier TMA kernel (one page
+  // per CTA barrier, three CTAs per SM), kept for side-by-side measurements
+  const int m = a->SBS / kPage;                 // pages per prune group
+  const bool want_fp16 = (a->reserved & 1) != 0;
+  const bool want_v1 = (a->reserved & 2) != 0;
   p.refine_lag = 1;
-  const bool use_tma = want_tma && decode_tma_supported(p);
-  if (use_tma)
+  p.group = m;
+  const bool use_ws = !want_fp16 && !want_v1 && decode_ws_supported(p, m);
+  const bool use_tma = !want_fp16 && !use_ws && decode_tma_supported(p);
+  if (use_ws) decode_ws_plan(a->B, a->HKV, p.NP, m, a->pages_per_chunk, &p.NPp, &p.ppc);
+  else if (use_tma)
     decode_tma_plan(a->B, a->HKV, p.NP, a->pages_per_chunk, decode_tma_residency(p, a->variant, a->fp8_format), &p.ppc,
                     &p.nch);
   else ffa_decode_plan(a->B, a->T, a->HKV, a->pages_per_chunk, &p.ppc, &p.nch);
+  // the in-kernel merges address the partials with this stride; it bounds every plan's count
+  if (use_ws) p.nch = decode_nch_bound(a->B, a->HKV, p.NP, a->pages_per_chunk);
 
   const size_t rows = static_cast<size_t>(a->B) * a->HQ;
   const size_t ml = align_up(rows * p.nch * sizeof(float), 256);
   const size_t po = align_up(rows * p.nch * kHeadDim * sizeof(float), 256);
-  const size_t need = kArrivalBytes + ml * 4 + po + 256;          // m, l, mean-V (m, l), o, legacy status
+  const size_t need = kArrivalBytes + ml * 4 + po + 256;          // m, l, mean-V (m, l), o
   if (a->workspace_bytes < need) return FFA_E_WORKSPACE;
   if (static_cast<size_t>(a->B) * a->HKV * sizeof(int) > kArrivalBytes - 256) return FFA_E_LIMIT;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
@@ -673,38 +644,16 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   p.part_pl = reinterpret_cast<float*>(ws + kArrivalBytes + 3 * ml + po + 256);
   p.v_mean = a->v_mean;
   if (a->v_mean) {
-    // mean-V: 2-bit format on the TMA kernel, final output only (a partial would need the mass too)
-    if (a->variant != FFA_K_Q2 || !use_tma || a->partial_out) return FFA_E_SHAPE;
+    // mean-V: 2-bit format, final output only (a partial would need the mass too)
+    if (a->variant != FFA_K_Q2 || !(use_ws || use_tma) || a->partial_out) return FFA_E_SHAPE;
   }
+  if (m > 1 && !use_ws) return FFA_E_SHAPE;     // the other kernels prune page by page only
 
   int rc;
-  const int m = a->SBS / kPage;                 // pages per prune group
-  if (m > 1 && !use_tma) return FFA_E_SHAPE;    // the fp16 tensor-core kernel prunes page by page only
-  if (use_tma) {
-    const int64_t kv_rows = a->kv_rows > 0 ? a->kv_rows : static_cast<int64_t>(a->B) * a->T;
-    if (m > 1) {
-      // score all pages, decide per group of m pages, then run the step with the decisions given
-      const size_t pm_bytes = align_up(rows * p.NP * sizeof(float), 256);
-      const size_t pk_bytes = align_up(static_cast<size_t>(a->B) * a->HKV * p.NP, 256);
-      const size_t th_bytes = align_up(rows * sizeof(float), 256);
-      if (a->workspace_bytes < need + pm_bytes + pk_bytes + th_bytes) return FFA_E_WORKSPACE;
-      float* page_max = reinterpret_cast<float*>(ws + need);
-      int8_t* page_keep = reinterpret_cast<int8_t*>(ws + need + pm_bytes);
-      float* th = a->threshold_out ? a->threshold_out : reinterpret_cast<float*>(ws + need + pm_bytes + pk_bytes);
-      DecodeParams ps = p;
-      ps.mode = 1; ps.page_max = page_max; ps.mask = nullptr; ps.th_out = th;
-      rc = launch_decode_tma(ps, a->variant, a->fp8_format, kv_rows, stream);
-      if (rc != FFA_OK) return rc;
-      const int n_groups = (p.NP + m - 1) / m;
-      const int64_t threads = static_cast<int64_t>(a->B) * a->HKV * (n_groups > p.NTBS ? n_groups : p.NTBS);
-      group_keep_kernel<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, stream>>>(
-          page_max, th, a->B, a->HKV, G, p.NP, m, n_groups, p.NTBS, page_keep, a->kept_mask);
-      cudaError_t ge = cudaGetLastError();
-      if (ge != cudaSuccess) return note_cuda_error(ge, "group_keep launch");
-      p.mode = 2; p.page_keep = page_keep; p.mask = nullptr; p.th_in = th; p.th_out = nullptr;
-    }
-    rc = launch_decode_tma(p, a->variant, a->fp8_format, kv_rows, stream);
-  } else
+  const int64_t kv_rows = a->kv_rows > 0 ? a->kv_rows : static_cast<int64_t>(a->B) * a->T;
+  if (use_ws) rc = launch_decode_ws(p, a->variant, a->fp8_format, kv_rows, stream);
+  else if (use_tma) rc = launch_decode_tma(p, a->variant, a->fp8_format, kv_rows, stream);
+  else
   switch (a->variant) {
     case FFA_K_FP8:   rc = launch_stage1_fmt<FFA_K_FP8>(p, a->fp8_format, stream); break;
     case FFA_K_Q2:    rc = launch_stage1_fmt<FFA_K_Q2>(p, a->fp8_format, stream); break;
@@ -714,7 +663,7 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
     default: return FFA_E_VARIANT;
   }
   if (rc != FFA_OK) return rc;
-  if (use_tma) return FFA_OK;          // the last segment of every (b, kv-head) merged in-kernel
+  if (use_ws || use_tma) return FFA_OK;          // the last segment of every (b, kv-head) merged in-kernel
   decode_merge_kernel<<<static_cast<unsigned>(rows), kHeadDim, 0, stream>>>(
       p.part_m, p.part_l, p.part_o, p.nch, 0, p.NP, G, a->out, a->q_dtype, a->partial_out);
   cudaError_t e = cudaGetLastError();

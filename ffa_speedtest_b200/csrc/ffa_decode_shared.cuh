@@ -9,6 +9,7 @@ namespace ffa {
 constexpr int kDecodeThreads = 128;
 constexpr int kDecodeWarps = 4;   // each warp owns 16 tokens of every page
 constexpr int kSample = 16;       // threshold sample width (T_BS in the reference)
+constexpr int kMaxPruneGroup = 8; // largest prune group of the warp-specialised kernel, in pages (SBS <= 512)
 constexpr int kResRow = 128;      // fp8 residual bytes per token per head
 constexpr int kVRow = 256;        // V bytes per token per head (fp16 / bf16)
 constexpr int kRvSlot = kPage * (kResRow + kVRow);
@@ -70,10 +71,23 @@ struct DecodeParams {
   // mean-V variant (q2 only): pruned pages contribute their coarse softmax mass times the mean of V.
   // Every segment adds the running maximum and mass of its pruned pages to its partial.
   const void* v_mean;        // [B*HKV, 128] in V's dtype, or null
+  // warp-specialised kernel: pages per prune group (SBS / 64) and pages per (b, kv-head) rounded up
+  // to whole groups; page ranges are cut in that padded space so that no group straddles two CTAs
+  int group;
+  int NPp;
   float* part_pm;            // [B*HQ, nch]
   float* part_pl;            // [B*HQ, nch]
 };
 
+
+// ffa_decode_ws.cu (warp-specialised kernel: bf16 / fp16 / fp32 q, prune groups of up to 8 pages):
+// plan and launch.  `wc` pages per CTA over the flattened, group-padded (b, kv-head, page) space.
+void decode_ws_plan(int B, int HKV, int NP, int group, int wc_in, int* NPp, int* wc);
+bool decode_ws_supported(const DecodeParams& p, int group);
+int launch_decode_ws(const DecodeParams& p, int variant, int f8, int64_t kv_rows, cudaStream_t stream);
+// Upper bound, monotonic in NP, of the partials any (b, kv-head) receives under either kernel's plan:
+// the stride of the partial arrays and what the workspace is sized for.
+int decode_nch_bound(int B, int HKV, int NP, int wc_in);
 
 // ffa_decode_tma.cu: returns FFA_OK after enqueueing stage 1, or a negative FFA_E_* code.
 // `kv_rows` is the number of token rows in the K/V tensors (B*T, or pages*64 for a pool).

@@ -39,8 +39,8 @@ class GraphDecodeRunner:
         self._static = {n: (tensors[n] if in_place else tensors[n].clone()) for n in self._names}
         BS = self._settings.get("BS", 128)
         SBS = self._settings.get("SBS") or BS
-        self._ws = DecodeWorkspace(q.shape[0], v.shape[1], q.shape[2], v.shape[2], v.shape[3], BS=BS, SBS=SBS,
-                                   device=self._device, dtype=q.dtype)
+        self._ws = DecodeWorkspace.for_shape(q.shape[0], v.shape[1], q.shape[2], v.shape[2], v.shape[3], BS=BS, SBS=SBS,
+                                             device=self._device, dtype=q.dtype)
         for _ in range(max(1, warmup)):
             self._call()
         torch.cuda.synchronize(self._device)

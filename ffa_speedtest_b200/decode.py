@@ -24,48 +24,102 @@ from . import _lib
 PAGE = 64
 
 
+MAX_SBS = 512      # largest prune granularity of this build (eight 64-token pages)
+
+
 class DecodeWorkspace:
-    """Reusable scratch for one decode shape (the analogue of ``Q2FP8DecodeWorkspace`` in
-    ffa-q2fp8-h100/attn_kernel/attn_kernel_v1210_fused_bsz_q2fp8.py:232-277)."""
+    """Reusable output, mask, threshold and scratch buffers of the decode call.
 
-    def __init__(self, B: int, T: int, HQ: int, HKV: int, V: int, *, BS: int, SBS: int, device, dtype,
-                 pages_per_chunk: int = 0):
-        self.key = (B, T, HQ, HKV, V, BS, SBS, torch.device(device), dtype, pages_per_chunk)
-        nbytes = _lib.lib().ffa_decode_workspace_bytes(B, T, HQ, HKV, pages_per_chunk)
-        ntbs = -(-T // BS) * (BS // SBS)
-        self.scratch = torch.empty(max(nbytes, 65536), dtype=torch.uint8, device=device)
+    Same constructor, attributes ``o`` / ``mask_buf`` / ``threshold_buf`` and ``matches`` as
+    ``Q2FP8DecodeWorkspace`` of the reference
+    (ffa-q2fp8-h100/attn_kernel/attn_kernel_v1210_fused_bsz_q2fp8.py:232-258), for all five
+    variants.  The reference's ``m_buf`` / ``l_buf`` / ``o_buf`` (one partial per block) have no
+    counterpart: partial results live in ``scratch``, one per page range of a CTA.
+
+    ``NTBS`` is the number of prune blocks per sequence, ``ceil(T/BS) * (BS/SBS)``.  The scratch is
+    sized for the longest sequence that many blocks can hold, so one workspace serves a cache
+    that grows up to ``NTBS`` blocks (``fits``)."""
+
+    def __init__(self, B: int, HQ: int, HKV: int, V: int, NTBS: int, device, dtype, *, pages_per_chunk: int = 0):
+        self.B, self.HQ, self.HKV, self.V, self.NTBS = int(B), int(HQ), int(HKV), int(V), int(NTBS)
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.pages_per_chunk = int(pages_per_chunk)
+        nbytes = _lib.lib().ffa_decode_workspace_bytes(self.B, self.NTBS * MAX_SBS, self.HQ, self.HKV,
+                                                       self.pages_per_chunk)
+        self.scratch = torch.empty(max(nbytes, 65536), dtype=torch.uint8, device=self.device)
         self.scratch[:65536].zero_()     # arrival counters + status word: zero before first use
-        self.o = torch.empty((B, HQ, V), dtype=dtype, device=device)
-        self.mask = torch.empty((B, HKV, ntbs), dtype=torch.int8, device=device)
-        self.threshold = torch.empty((B, HQ), dtype=torch.float32, device=device)
-        self.pages_per_chunk = pages_per_chunk
+        self.o = torch.empty((self.B, self.HQ, self.V), dtype=dtype, device=self.device)
+        self.mask_buf = torch.empty((self.B, self.HKV, self.NTBS), dtype=torch.int8, device=self.device)
+        self.threshold_buf = torch.empty((self.B, self.HQ), dtype=torch.float32, device=self.device)
 
-    def fits(self, B: int, T: int, HQ: int, HKV: int, V: int, BS: int, SBS: int, device, dtype,
-             pages_per_chunk: int) -> bool:
+    @classmethod
+    def for_shape(cls, B: int, T: int, HQ: int, HKV: int, V: int, *, BS: int, SBS: int, device, dtype,
+                  pages_per_chunk: int = 0) -> "DecodeWorkspace":
+        """Workspace for sequences of up to T tokens pruned in SBS-token blocks of BS-token blocks."""
+        return cls(B, HQ, HKV, V, -(-T // BS) * (BS // SBS), device, dtype, pages_per_chunk=pages_per_chunk)
+
+    # the names used before the reference's were adopted
+    @property
+    def mask(self) -> torch.Tensor:
+        return self.mask_buf
+
+    @property
+    def threshold(self) -> torch.Tensor:
+        return self.threshold_buf
+
+    def matches(self, B: int, HQ: int, HKV: int, V: int, NTBS: int, device, dtype) -> bool:
+        """Exactly the shape, device and dtype the workspace was made for (reference :248-258)."""
+        return (self.B == int(B) and self.HQ == int(HQ) and self.HKV == int(HKV) and self.V == int(V)
+                and self.NTBS == int(NTBS) and self.device == torch.device(device) and self.dtype == dtype)
+
+    def fits(self, B: int, HQ: int, HKV: int, V: int, NTBS: int, device, dtype, pages_per_chunk: int = 0) -> bool:
         """True for the shape the workspace was made for and for shorter sequences of the same batch
         (a cache that grows towards the allocated length)."""
-        kB, kT, kHQ, kHKV, kV, kBS, kSBS, kdev, kdt, kppc = self.key
-        if (B, HQ, HKV, V, BS, SBS, torch.device(device), dtype, pages_per_chunk) != \
-                (kB, kHQ, kHKV, kV, kBS, kSBS, kdev, kdt, kppc) or T > kT:
-            return False
-        return _lib.lib().ffa_decode_workspace_bytes(B, T, HQ, HKV, pages_per_chunk) <= self.scratch.numel()
+        return (self.matches(B, HQ, HKV, V, self.NTBS, device, dtype) and int(NTBS) <= self.NTBS
+                and int(pages_per_chunk) == self.pages_per_chunk)
 
     def mask_view(self, B: int, HKV: int, ntbs: int) -> torch.Tensor:
-        """The kept-page mask of a call over ``ntbs`` pages per sequence (the buffer is sized for the
+        """The kept-page mask of a call over ``ntbs`` blocks per sequence (the buffer is sized for the
         longest sequence; a call writes the first B*HKV*ntbs entries)."""
-        return self.mask.view(-1)[:B * HKV * ntbs].view(B, HKV, ntbs)
+        return self.mask_buf.view(-1)[:B * HKV * ntbs].view(B, HKV, ntbs)
 
     def status(self) -> int:
-        """Device status word (synchronises): 0 = ok, 1 = a bounded wait inside a kernel gave up."""
+        """Device status word (synchronises): 0 = ok, 1 = a bounded wait inside a kernel gave up (the
+        affected outputs are NaN)."""
         return int(self.scratch[65280:65284].view(torch.int32).item())
 
 
-def allocate_decode_workspace(q, v, *, BS: int = 128, SBS: Optional[int] = None, seq_len: Optional[int] = None,
+def allocate_decode_workspace(q, *kv, BS: int = 128, SBS: Optional[int] = None, seq_len: Optional[int] = None,
                               pages_per_chunk: int = 0) -> DecodeWorkspace:
-    B, _, HQ, _ = q.shape
-    T = seq_len if seq_len is not None else v.shape[1]
-    return DecodeWorkspace(B, T, HQ, v.shape[2], v.shape[3], BS=BS, SBS=SBS or BS, device=q.device, dtype=q.dtype,
-                           pages_per_chunk=pages_per_chunk)
+    """``allocate_q2fp8_decode_workspace(q, k_q, v, BS=128, SBS=None)`` of the reference
+    (ffa-q2fp8-h100/attn_kernel/attn_kernel_v1210_fused_bsz_q2fp8.py:261-277), for every variant.
+    ``(q, v)`` without the K tensor is accepted too; BS and SBS may also be given positionally after
+    the tensors as in the reference.  ``seq_len`` sizes a workspace for paged pools
+    ``[n_pages, 64, HKV, D]``, whose second dimension is the page size and not the sequence length."""
+    tensors = [t for t in kv if isinstance(t, torch.Tensor)]
+    rest = [t for t in kv if not isinstance(t, torch.Tensor)]
+    if len(tensors) not in (1, 2) or len(rest) > 2:
+        raise TypeError("allocate_decode_workspace(q, [k,] v, BS=128, SBS=None)")
+    if len(rest) >= 1:
+        BS = rest[0]
+    if len(rest) == 2:
+        SBS = rest[1]
+    v = tensors[-1]
+    B, Tq, HQ, _ = q.shape
+    Bv, Tv, HKV, V = v.shape
+    if seq_len is None:
+        if len(tensors) == 2:
+            Bk, Tk, HKVk, _ = tensors[0].shape
+            if B != Bk or Tk != Tv or HKVk != HKV:
+                raise ValueError("K/V layouts must be [B, T, HKV, D]")
+        if B != Bv or Tq != 1:
+            raise ValueError("K/V layouts must be [B, T, HKV, D]")
+    T = seq_len if seq_len is not None else Tv
+    if SBS is None:
+        SBS = BS
+    return DecodeWorkspace.for_shape(B, T, HQ, HKV, V, BS=BS, SBS=SBS, device=q.device, dtype=q.dtype,
+                                     pages_per_chunk=pages_per_chunk)
 
 
 def _fp8_format(*tensors) -> int:
@@ -114,11 +168,12 @@ def decode_call(
     ``mean_v [B, HKV, 128]`` (V's dtype) selects the mean-V variant of the 2-bit format: pruned pages
     are not dropped but contribute their coarse softmax mass times this vector.
 
-    ``kernel``: "auto" picks the TMA / fp8 tensor-core kernel when q is bfloat16, or float16 with
-    float16 V, and the fp16 tensor-core kernel otherwise; "fp16" forces the latter (it follows the reference's fp16
-    rounding of the refined K tile to the letter)."""
-    if kernel not in ("auto", "fp16"):
-        raise ValueError(f"kernel must be 'auto' or 'fp16', got {kernel!r}")
+    ``kernel``: "auto" is the warp-specialised TMA kernel (any q dtype, either V dtype, prune groups of
+    up to eight pages); "fp16" forces the fp16 tensor-core kernel, which follows the reference's fp16
+    rounding of the refined K tile to the letter and prunes page by page only; "tma_v1" is the earlier
+    TMA kernel (one CTA barrier per page), kept for side-by-side timing."""
+    if kernel not in ("auto", "fp16", "tma_v1"):
+        raise ValueError(f"kernel must be 'auto', 'fp16' or 'tma_v1', got {kernel!r}")
     B, Tq, HQ, K = q.shape
     HKV, V = v.shape[2], v.shape[3]
     if block_table is None:
@@ -146,9 +201,10 @@ def decode_call(
     if SBS % PAGE != 0 or SBS < PAGE or BS % SBS != 0:
         raise ValueError(f"this build prunes in units of 64-token pages: SBS must be a multiple of 64 and BS a "
                          f"multiple of SBS (got BS={BS}, SBS={SBS})")
-    if SBS != PAGE and (kernel == "fp16" or not (q.dtype == torch.bfloat16 or
-                                                   (q.dtype == torch.float16 and v.dtype == torch.float16))):
-        raise ValueError("SBS above 64 needs the TMA kernel: bfloat16 q, or float16 q with float16 v")
+    if SBS > MAX_SBS or (SBS // PAGE) & (SBS // PAGE - 1):
+        raise ValueError(f"this build prunes groups of 1, 2, 4 or 8 pages: SBS must be 64, 128, 256 or 512 (got {SBS})")
+    if SBS != PAGE and kernel != "auto":
+        raise ValueError("SBS above 64 needs kernel='auto': the other kernels prune page by page only")
     NTB = -(-T // BS)
     NTBS = NTB * (BS // SBS)
 
@@ -164,10 +220,11 @@ def decode_call(
         th_in = None
 
     if workspace is None:
-        workspace = DecodeWorkspace(B, T, HQ, HKV, V, BS=BS, SBS=SBS, device=q.device, dtype=q.dtype,
-                                    pages_per_chunk=pages_per_chunk)
-    elif not workspace.fits(B, T, HQ, HKV, V, BS, SBS, q.device, q.dtype, pages_per_chunk):
-        raise ValueError("workspace was allocated for a different decode shape")
+        workspace = DecodeWorkspace(B, HQ, HKV, V, NTBS, q.device, q.dtype, pages_per_chunk=pages_per_chunk)
+    elif not isinstance(workspace, DecodeWorkspace):
+        raise TypeError("workspace must be a Q2FP8DecodeWorkspace")
+    elif not workspace.fits(B, HQ, HKV, V, NTBS, q.device, q.dtype, pages_per_chunk):
+        raise ValueError("workspace shape/device/dtype mismatch")
     o = workspace.o if out is None else out
     if o.shape != (B, HQ, V) or o.dtype != q.dtype or not o.is_contiguous():
         raise ValueError("out must be a contiguous [B, HQ, V] tensor of q's dtype")
@@ -209,7 +266,7 @@ def decode_call(
     a.workspace = workspace.scratch.data_ptr()
     a.workspace_bytes = workspace.scratch.numel()
     a.pages_per_chunk = pages_per_chunk
-    a.reserved = 1 if kernel == "fp16" else 0
+    a.reserved = {"auto": 0, "fp16": 1, "tma_v1": 2}[kernel]
     a.kv_rows = k_codes.shape[0] * k_codes.shape[1]
     _lib.check(_lib.lib().ffa_decode(a, _lib.current_stream(q.device)), "ffa_decode")
 

@@ -86,7 +86,7 @@ def global_threshold(variant: str, q: torch.Tensor, k_codes: torch.Tensor, *, de
     mini.view(torch.uint8)[:, 0:16] = k_codes.view(torch.uint8)[:, 0:16]
     mini.view(torch.uint8)[:, 64:80] = k_codes.view(torch.uint8)[:, 16:32]
     v = torch.zeros((B, T_s, HKV, 128), dtype=q.dtype if q.dtype != torch.float32 else torch.float16, device=q.device)
-    ws = DecodeWorkspace(B, T_s, HQ, HKV, 128, BS=64, SBS=64, device=q.device, dtype=q.dtype)
+    ws = DecodeWorkspace.for_shape(B, T_s, HQ, HKV, 128, BS=64, SBS=64, device=q.device, dtype=q.dtype)
     decode_call(variant, q, mini, v, k_scale=k_scale, k_zero=k_zero, k_residual=None, scale=scale, BS=64, SBS=64,
                 delta=delta, use_fp8_residual=False, workspace=ws)
     return ws.threshold.clone()
