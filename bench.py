@@ -60,7 +60,8 @@ WORKLOADS = {
 HIDDEN = 4096
 HQ, HKV, D, PAGE = 32, 8, 128, 64
 CODE_BYTES = {"fp8": 128, "q2": 32, "fp4": 64, "nf4": 64, "nvfp4": 64}
-# dram__bytes_read+write / algorithmic bytes of the stage-1 kernel, from the committed ncu capture
+# dram__bytes_read + dram__bytes_write of the decode kernel divided by its algorithmic bytes, from an ncu
+# capture of a B=2, T=32K case of the default workload (traffic grows in proportion to the pages read)
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.02
 METRIC = "decode_attn_achieved_hbm_TBps"   # the headline metric: decode-attn us/step and achieved HBM TB/s
 UNIT = "TB/s"
@@ -308,10 +309,12 @@ def run_kproj(args, wl_name: str, wl: dict) -> dict:
     }
 
 
-def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank: int):
+def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank: int, own_group: bool = True):
     """Sequence-split decode: rank r holds pages [lo, hi) of every sequence (contiguous layout), all
     ranks hold the same thresholds (computed from the replicated 32 sample rows), each step is the
-    local decode into a [B, HQ, 129] partial, one all-gather and the merge kernel."""
+    local decode into this rank's slot of the gathered [world, B, HQ, 129] buffer, one in-place
+    all-gather and the merge kernel.  Before the sequence is cut every rank runs the unsplit step once
+    on the whole sequence, which is what the split result is compared with."""
     import torch.distributed as dist
     from ffa_speedtest_b200 import quantize as Q, sharded
     from ffa_speedtest_b200.decode import allocate_decode_workspace, decode_call
@@ -319,11 +322,13 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    dist.init_process_group("nccl", device_id=dev) if world > 1 else None
+    if world > 1 and own_group:
+        dist.init_process_group("nccl", device_id=dev)
     kind, B, T, delta = wl["kind"], wl["B"], wl["T"], wl["delta"]
     f8 = {"e5m2": torch.float8_e5m2, "e4m3": torch.float8_e4m3fn}[wl["fp8"]]
     NP = T // PAGE
     W = max(args.warmup, 3)
+    steps = max(1, min(args.steps, 200))
     lo, hi = sharded.page_slice(NP, rank, world)
     # the same sequence on every rank (same seed); the scales of q2 span the whole sequence, so K is
     # quantised whole and then cut to this rank's pages
@@ -333,6 +338,27 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     r0, r1 = sharded.sample_token_rows(T, PAGE)
     sample = torch.cat([codes[:, r0.start:r0.stop], codes[:, r1.start:r1.stop]], dim=1).contiguous()
     th = sharded.global_threshold(kind, q, sample, delta=delta, k_scale=scale, k_zero=zero)
+    # the unsplit step on the whole sequence: reference result and single-GPU time
+    ws_full = allocate_decode_workspace(q, v, BS=PAGE, SBS=PAGE)
+
+    def full_step():
+        return decode_call(kind, q, codes, v, k_scale=scale, k_zero=zero, k_residual=res, BS=PAGE, SBS=PAGE,
+                           delta=delta, workspace=ws_full)
+
+    for _ in range(3):
+        o_full = full_step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        o_full = full_step()
+    e1.record()
+    torch.cuda.synchronize()
+    us_unsplit = e0.elapsed_time(e1) * 1e3 / 10
+    o_full = o_full.float().clone()
+    th_full = ws_full.threshold.clone()
+    kept_full = float(ws_full.mask.float().mean())
+    del ws_full
     ck, rk, vk = (x[:, lo * PAGE:hi * PAGE].contiguous() for x in (codes, res, v))
     del codes, res, v
     torch.cuda.empty_cache()
@@ -343,6 +369,7 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
         return decode_call(kind, q_dev, ck, vk, k_scale=scale, k_zero=zero, k_residual=rk, BS=PAGE, SBS=PAGE,
                            delta=delta, precomputed_threshold=th, workspace=ws, partial_out=partial_out, out=out)
 
+    runner = None
     if world > 1:
         runner = sharded.SequenceShardedDecode(dist.group.WORLD, B, HQ, dev, q.dtype)
         step = lambda: runner.step(local)
@@ -350,6 +377,8 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
         step = lambda: local()
     o = step()
     torch.cuda.synchronize()
+    err_vs_unsplit = float((o.float() - o_full).abs().max())
+    th_err = float((th - th_full).abs().max())
     kept_local = float(ws.mask.float().mean())
     step_bytes = algorithmic_bytes(kind, B, (hi - lo) * PAGE, kept_local, paged=False)
 
@@ -358,20 +387,27 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
             dist.barrier()
         torch.cuda.synchronize()
 
+    def timed(fn, n):
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(n):
+            fn()
+        a1.record()
+        barrier()
+        return a0.elapsed_time(a1)
+
     for _ in range(W):
         step()
     # the sampler takes a moment to start: start it before the barrier, or the other ranks would
     # spend the first steps of their timed loop waiting for this one in the all-gather
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
+    sampler = ClockSampler(local_rank) if rank == 0 and own_group else None
+    ms = timed(step, steps)
     clocks = sampler.stop() if sampler else None
+    # the parts of a step, each timed alone
+    ms_local = timed(lambda: local(partial_out=runner.local) if runner else local(), steps)
+    ms_gather = timed(runner.gather, steps) if runner else 0.0
+    ms_merge = timed(runner.merge, steps) if runner else 0.0
 
     q_host = q.cpu().pin_memory()
     o_host = torch.empty((B, HQ, D), dtype=q.dtype).pin_memory()
@@ -384,7 +420,7 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     for _ in range(W):
         e2e_step()
     barrier()
-    n_e2e = max(10, min(args.steps, 100))
+    n_e2e = max(10, min(steps, 100))
     t0 = time.perf_counter()
     for _ in range(n_e2e):
         e2e_step()
@@ -392,18 +428,19 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     s_e2e = (time.perf_counter() - t0) / n_e2e
     if ws.status() != 0:
         raise SystemExit("a bounded wait inside the decode kernel gave up (status word set): results are invalid")
-    t = torch.tensor([ms, s_e2e, step_bytes, kept_local], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms, s_e2e, step_bytes, kept_local, ms_local, ms_gather, ms_merge, err_vs_unsplit, us_unsplit],
+                     dtype=torch.float64, device=dev)
     tmax, tsum = t.clone(), t.clone()
     if world > 1:
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
     out = None
     if rank == 0:
-        per_step_s = float(tmax[0]) / 1e3 / args.steps
+        per_step_s = float(tmax[0]) / 1e3 / steps
         job_bytes = float(tsum[2])
         peak, peak_kind = peaks()
         out = {
-            "metric": METRIC, "value": job_bytes / per_step_s / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": METRIC, "value": job_bytes / per_step_s / 1e12, "unit": UNIT, "n_gpus": world, "steps": steps,
             "warmup": W, "ms_per_step": per_step_s * 1e3, "us_per_step": per_step_s * 1e6, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32 (2-bit/fp8/bf16 storage)", "data": "synthetic",
             "config": {"workload": wl_name, "variant": kind + "fp8", "batch": B, "context": T, "q_heads": HQ,
@@ -415,14 +452,112 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
             "roofline": {"bound": "hbm", "achieved": job_bytes / world / per_step_s / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": job_bytes / world / per_step_s / 1e9 / peak, "peak_source": peak_kind, "traffic": None,
                          "note": "per-GPU rate of the whole step (local decode + all-gather + merge)"},
+            "seqsplit": {"us_per_step": per_step_s * 1e6, "value": job_bytes / per_step_s / 1e12,
+                         "unsplit_us_per_step_on_one_gpu": float(tmax[8]),
+                         "speedup_vs_unsplit": float(tmax[8]) / (per_step_s * 1e6),
+                         "max_abs_err_vs_unsplit": float(tmax[7]), "threshold_max_abs_diff": th_err,
+                         "local_decode_us": float(tmax[4]) * 1e3 / steps, "allgather_us": float(tmax[5]) * 1e3 / steps,
+                         "merge_us": float(tmax[6]) * 1e3 / steps, "kept_fraction_unsplit": kept_full},
             "e2e": {"value": job_bytes / float(tmax[1]) / 1e12, "unit": UNIT, "h2d_bytes_per_step": q_host.numel() * 2,
                     "d2h_bytes_per_step": o_host.numel() * 2, "us_per_step": float(tmax[1]) * 1e6, "steps": n_e2e},
-            "gpu_launches": args.steps * (1 if world == 1 else 2),     # decode (+ merge); the all-gather is NCCL's
+            "gpu_launches": steps * (1 if world == 1 else 2),     # decode (+ merge); the all-gather is NCCL's
             "clocks": clocks,
         }
-    if world > 1:
+    if world > 1 and own_group:
         dist.destroy_process_group()
     return out
+
+
+def triton_baseline(kind: str, q, codes, scale, zero, res, v, delta: float, steps: int) -> dict:
+    """The reference's own Triton kernels, JIT-compiled on this GPU, on the same (contiguous) tensors:
+    its CUDA-graph runner's replay_only(), which is what its cudagraph bench times
+    (ffa-q2fp8/run_attn_bench_q2_cudagraph.py:51-56, 462-464), with the reference's timing protocol
+    (utils/bench.py:7-20).  The files come from baseline/_ref (baseline/install_reference.py)."""
+    import importlib.util
+    variant = {"fp8": "fp8fp8", "q2": "q2fp8", "fp4": "fp4fp8", "nf4": "nf4fp8", "nvfp4": "nvfp4fp8"}[kind]
+    cls = {"fp8": "CUDAGraphDecodeRunnerFP8FP8", "q2": "CUDAGraphDecodeRunnerQ2FP8", "fp4": "CUDAGraphDecodeRunnerFP4FP8",
+           "nf4": "CUDAGraphDecodeRunnerNF4FP8", "nvfp4": "CUDAGraphDecodeRunnerNVFP4FP8"}[kind]
+    fn = {"fp8": "attn_forward_decode_fp8fp8", "q2": "attn_forward_decode_quantized", "fp4": "attn_forward_decode_fp4",
+          "nf4": "attn_forward_decode_nf4", "nvfp4": "attn_forward_decode_nvfp4fp8"}[kind]
+    try:
+        spec = importlib.util.spec_from_file_location("ffa_baseline_install", ROOT / "baseline" / "install_reference.py")
+        inst = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(inst)
+        mod = inst.load(f"ffa_{variant}", f"attn_kernel_v1210_fused_bsz_{variant}")
+        cg = inst.load(f"ffa_{variant}", f"attn_kernel_v1210_fused_bsz_{variant}_cudagraph")
+        kt = [codes, scale, zero] if kind == "q2" else ([codes, scale] if kind in ("nf4", "nvfp4") else [codes])
+        kw = dict(k_residual=res, BS=PAGE, SBS=PAGE, delta=delta)
+        o_ref, skip = getattr(mod, fn)(q, *kt, v, return_skip_ratio=True, **kw)
+        runner = getattr(cg, cls)(q, *kt, v, use_fp8_residual=True, warmup=2, **kw)
+        for _ in range(5):
+            runner.replay_only()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            runner.replay_only()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / steps
+        kept = 1.0 - float(skip)
+        byt = algorithmic_bytes(kind, q.shape[0], v.shape[1], kept, paged=False)
+        return {"us_per_step": us, "value": byt / us / 1e6, "unit": UNIT, "kept_fraction": kept, "steps": steps,
+                "output": o_ref.float(),
+                "how": f"{cls}.replay_only() of the unmodified reference kernels (Triton JIT), contiguous layout, same tensors"}
+    except Exception as e:                     # no copy of the reference, no Triton, or it does not compile here
+        return {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+
+
+def target_128k(args) -> dict:
+    """The long-context target shape on one GPU: q2fp8, batch 32, 128K tokens, page 64, delta 8."""
+    from ffa_speedtest_b200 import quantize as Q
+    from ffa_speedtest_b200.decode import allocate_decode_workspace, decode_call
+    from ffa_speedtest_b200.synth import make_block_table, make_decode_inputs
+    dev = torch.device("cuda", 0)
+    kind, B, T, delta = "q2", 32, 131072, 8.0
+    NP = T // PAGE
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, D, seed=1, device=dev)
+    codes, scale, zero, res = Q.quantize_k_2bit_fp8_residual(k, torch.float8_e4m3fn)
+    del k
+    bt = make_block_table(B, NP, seed=7).to(dev)
+
+    def to_pool(x):
+        xp = x.reshape(B * NP, PAGE, *x.shape[2:])
+        pool = torch.empty_like(xp)
+        view = torch.uint8 if x.dtype.itemsize == 1 else torch.int16
+        pool.view(view)[bt.reshape(-1).long()] = xp.view(view)
+        return pool
+
+    codes_p = to_pool(codes); del codes
+    res_p = to_pool(res); del res
+    v_p = to_pool(v); del v
+    torch.cuda.empty_cache()
+    ws = allocate_decode_workspace(q, v_p, BS=PAGE, SBS=PAGE, seq_len=T)
+
+    def step():
+        return decode_call(kind, q, codes_p, v_p, k_scale=scale, k_zero=zero, k_residual=res_p, BS=PAGE, SBS=PAGE,
+                           delta=delta, block_table=bt, seq_len=T, workspace=ws)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    kept = float(ws.mask.float().mean())
+    n = max(10, min(args.steps, 50))
+    sampler = ClockSampler(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    us = e0.elapsed_time(e1) * 1e3 / n
+    byt = algorithmic_bytes(kind, B, T, kept, paged=True)
+    peak, _ = peaks()
+    if ws.status() != 0:
+        return {"unavailable": "a bounded wait inside the decode kernel gave up"}
+    return {"us_per_step": us, "value": byt / us / 1e6, "unit": UNIT, "frac": byt / us / 1e3 / peak,
+            "frac_of_nominal_8TBps": byt / us / 1e3 / 8000.0, "kept_fraction": kept, "steps": n, "clocks": clocks}
 
 
 def main():
@@ -434,6 +569,9 @@ def main():
     ap.add_argument("--workload", default="fp8fp8_b8_t32k", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-triton-baseline", action="store_true", help="skip the reference's Triton kernels column")
+    ap.add_argument("--no-targets", action="store_true", help="skip the 128K target shape (one GPU)")
+    ap.add_argument("--no-seqsplit", action="store_true", help="skip the sequence-split leg (several GPUs)")
     ap.add_argument("--identity-table", action="store_true", help="identity block table instead of a permutation")
     ap.add_argument("--pages-per-chunk", type=int, default=0)
     args = ap.parse_args()
@@ -463,6 +601,7 @@ def main():
         if rank == 0:
             print(json.dumps(out), flush=True)
         return
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     import torch.distributed as dist
     from ffa_speedtest_b200 import quantize as Q
     from ffa_speedtest_b200.decode import allocate_decode_workspace, decode_call
@@ -503,7 +642,9 @@ def main():
         return pool
 
     codes_p, res_p, v_p = to_pool(codes), to_pool(res), to_pool(v)
-    del codes, res, v
+    want_triton = world == 1 and not args.no_triton_baseline
+    if not want_triton:
+        del codes, res, v
     torch.cuda.empty_cache()
 
     ws = allocate_decode_workspace(q, v_p, BS=PAGE, SBS=PAGE, seq_len=T, pages_per_chunk=args.pages_per_chunk)
@@ -587,6 +728,7 @@ def main():
     else:
         job_bytes = step_bytes
 
+    out = None
     if rank == 0:
         per_step_s = ms / 1e3 / args.steps
         value = job_bytes / per_step_s / 1e12
@@ -611,14 +753,21 @@ def main():
                 "traffic_unit": "bytes per launch",
                 "frac_of_nominal_8TBps": per_gpu_gbs / 8000.0,
                 "note": "achieved = algorithmic bytes / step (one kernel: score, prune, refine, merge); traffic = "
-                        "dram read+write of an ncu capture at B=2 scaled by the bytes processed "
-                        "(profiles/decode_tma_fp8fp8_b2_t32k.md)",
+                        "dram read+write of an ncu capture of a B=2 case of this workload, scaled by the bytes processed",
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": q_host.numel() * 2,
                     "d2h_bytes_per_step": o_host.numel() * 2, "us_per_step": ms_e2e * 1e3 / n_e2e, "steps": n_e2e},
             "gpu_launches": args.steps,        # one decode kernel per step (the merge runs inside it)
             "clocks": clocks,
         }
+        if want_triton:
+            # the reference's own kernels on the same box, same tensors (contiguous layout: it has no block table)
+            tb = triton_baseline(kind, q, codes, scale, zero, res, v, delta, max(10, min(args.steps, 200)))
+            if "output" in tb:
+                tb["max_abs_diff_vs_ours"] = float((tb.pop("output") - ws.o.float()).abs().max())
+                tb["speedup_ours_over_triton"] = tb["us_per_step"] / (per_step_s * 1e6)
+            out["triton_baseline"] = tb
+            del codes, res, v
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
@@ -633,6 +782,18 @@ def main():
             out["cpu_baseline"] = {"value": cb / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
                                    "sample": f"B=1 of {B} sequences, T={min(T, 32768)}, {n_c} timed steps",
                                    "us_per_step": dt * 1e6}
+    # ---- second legs: the 128K target shape (one GPU), the sequence split (several GPUs) -----------
+    del codes_p, res_p, v_p, ws, graph
+    torch.cuda.empty_cache()
+    if world == 1 and not args.no_targets and args.workload == "fp8fp8_b8_t32k":
+        out["targets"] = {"q2fp8_b32_t128k": target_128k(args)}
+    if world > 1 and not args.no_seqsplit and args.workload == "fp8fp8_b8_t32k":
+        name = "q2fp8_b4_t512k_seqsplit"
+        ss = run_seqsplit(args, name, WORKLOADS[name], rank, world, local_rank, own_group=False)
+        if rank == 0:
+            out["seqsplit"] = dict(ss["seqsplit"], workload=name, kept_fraction=ss["config"]["kept_fraction"],
+                                   pages_per_rank=ss["config"]["pages_per_rank"])
+    if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()

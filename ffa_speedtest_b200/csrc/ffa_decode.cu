@@ -618,22 +618,22 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   p.group = m;
   const bool use_ws = !want_fp16 && !want_v1 && decode_ws_supported(p, m);
   const bool use_tma = !want_fp16 && !use_ws && decode_tma_supported(p);
-  if (use_ws) decode_ws_plan(a->B, a->HKV, p.NP, m, a->pages_per_chunk, &p.NPp, &p.ppc);
+  if (use_ws) decode_ws_plan(a->B, a->HKV, p.NP, m, a->pages_per_chunk, &p.NPp, &p.ppc, &p.nseg, &p.grid);
   else if (use_tma)
     decode_tma_plan(a->B, a->HKV, p.NP, a->pages_per_chunk, decode_tma_residency(p, a->variant, a->fp8_format), &p.ppc,
                     &p.nch);
   else ffa_decode_plan(a->B, a->T, a->HKV, a->pages_per_chunk, &p.ppc, &p.nch);
-  // the in-kernel merges address the partials with this stride; it bounds every plan's count
-  if (use_ws) p.nch = decode_nch_bound(a->B, a->HKV, p.NP, a->pages_per_chunk);
+  if (use_ws) p.nch = p.nseg;                              // one partial per chunk
 
   const size_t rows = static_cast<size_t>(a->B) * a->HQ;
   const size_t ml = align_up(rows * p.nch * sizeof(float), 256);
   const size_t po = align_up(rows * p.nch * kHeadDim * sizeof(float), 256);
   const size_t need = kArrivalBytes + ml * 4 + po + 256;          // m, l, mean-V (m, l), o
   if (a->workspace_bytes < need) return FFA_E_WORKSPACE;
-  if (static_cast<size_t>(a->B) * a->HKV * sizeof(int) > kArrivalBytes - 256) return FFA_E_LIMIT;
+  if (static_cast<size_t>(a->B) * a->HKV > static_cast<size_t>(kWorkCounterIndex)) return FFA_E_LIMIT;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   p.arrivals = reinterpret_cast<int*>(ws);
+  p.work = p.arrivals + kWorkCounterIndex;
   p.part_m = reinterpret_cast<float*>(ws + kArrivalBytes);
   p.part_l = reinterpret_cast<float*>(ws + kArrivalBytes + ml);
   p.part_o = reinterpret_cast<float*>(ws + kArrivalBytes + 2 * ml);

@@ -10,6 +10,11 @@ constexpr int kDecodeThreads = 128;
 constexpr int kDecodeWarps = 4;   // each warp owns 16 tokens of every page
 constexpr int kSample = 16;       // threshold sample width (T_BS in the reference)
 constexpr int kMaxPruneGroup = 8; // largest prune group of the warp-specialised kernel, in pages (SBS <= 512)
+constexpr int kWsRefineWarps = 4; // refine warps of the warp-specialised kernel
+constexpr int kWsMaxParts = 32;   // partials (one per chunk) per q head that its merge handles
+// ints of the arrival-counter block that the warp-specialised kernel uses as its work counter (next
+// chunk to hand out) and as the count of CTAs that have left; both are zero between launches
+constexpr int kWorkCounterIndex = 16000;
 constexpr int kResRow = 128;      // fp8 residual bytes per token per head
 constexpr int kVRow = 256;        // V bytes per token per head (fp16 / bf16)
 constexpr int kRvSlot = kPage * (kResRow + kVRow);
@@ -75,14 +80,18 @@ struct DecodeParams {
   // to whole groups; page ranges are cut in that padded space so that no group straddles two CTAs
   int group;
   int NPp;
+  int nseg;          // chunks per (b, kv-head); `ppc` is the pages of a chunk
+  int grid;          // CTAs to launch
+  int* work;         // [0] next chunk to hand out, [1] CTAs that have left
   float* part_pm;            // [B*HQ, nch]
   float* part_pl;            // [B*HQ, nch]
 };
 
 
 // ffa_decode_ws.cu (warp-specialised kernel: bf16 / fp16 / fp32 q, prune groups of up to 8 pages):
-// plan and launch.  `wc` pages per CTA over the flattened, group-padded (b, kv-head, page) space.
-void decode_ws_plan(int B, int HKV, int NP, int group, int wc_in, int* NPp, int* wc);
+// plan and launch.  Every (b, kv-head) is cut into `nseg` chunks of `chunk` pages (whole prune groups,
+// the last one shorter); CTAs take chunks from a counter until none is left.
+void decode_ws_plan(int B, int HKV, int NP, int group, int chunk_in, int* NPp, int* chunk, int* nseg, int* grid);
 bool decode_ws_supported(const DecodeParams& p, int group);
 int launch_decode_ws(const DecodeParams& p, int variant, int f8, int64_t kv_rows, cudaStream_t stream);
 // Upper bound, monotonic in NP, of the partials any (b, kv-head) receives under either kernel's plan:

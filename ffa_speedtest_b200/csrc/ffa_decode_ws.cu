@@ -66,37 +66,41 @@ thread_local MapCache g_maps;
 
 }  // namespace
 
-void decode_ws_plan(int B, int HKV, int NP, int group, int wc_in, int* NPp_out, int* wc_out) {
+void decode_ws_plan(int B, int HKV, int NP, int group, int chunk_in, int* NPp_out, int* chunk_out, int* nseg_out,
+                    int* grid_out) {
   const int m = group < 1 ? 1 : group;
   const long long NPp = (static_cast<long long>(NP) + m - 1) / m * m;
-  const long long total = static_cast<long long>(B) * HKV * NPp;
-  long long wc = wc_in;
-  if (wc <= 0) {
-    const long long slots = sm_count();              // one persistent CTA per SM
-    wc = (total + slots - 1) / slots;
-    if (wc < 4) wc = 4;                              // a CTA's set-up is worth a few pages
+  const long long units = static_cast<long long>(B) * HKV;
+  const long long total = units * NPp;
+  const long long sms = sm_count();
+  long long ch = chunk_in;
+  if (ch <= 0) {
+    // about six chunks per SM when there is that much work (fine enough for the SMs to even out
+    // their different kept fractions, coarse enough that a chunk's set-up - q operands, thresholds,
+    // one partial per refine warp - stays small beside its pages); never less than four pages
+    const long long per_cta = (total + sms - 1) / sms;
+    ch = per_cta >= 96 ? (per_cta + 5) / 6 : (per_cta >= 16 ? 16 : (per_cta > 4 ? per_cta : 4));
   }
-  if (wc < (NPp + 62) / 63) wc = (NPp + 62) / 63;    // the in-kernel merge holds at most 64 partials per q head
-  wc = (wc + m - 1) / m * m;                         // no prune group straddles two CTAs
-  if (wc > total) wc = total;
-  if (wc < 1) wc = 1;
+  // the merge of a (b, kv-head) holds at most kWsMaxParts partials per q head, one per chunk
+  const long long max_seg = kWsMaxParts;
+  if (ch < (NPp + max_seg - 1) / max_seg) ch = (NPp + max_seg - 1) / max_seg;
+  ch = (ch + m - 1) / m * m;                         // whole prune groups
+  if (ch > NPp) ch = NPp;
+  const long long nseg = (NPp + ch - 1) / ch;
+  const long long chunks = units * nseg;
   *NPp_out = static_cast<int>(NPp);
-  *wc_out = static_cast<int>(wc);
+  *chunk_out = static_cast<int>(ch);
+  *nseg_out = static_cast<int>(nseg);
+  *grid_out = static_cast<int>(chunks < sms ? chunks : sms);
 }
 
 int decode_nch_bound(int B, int HKV, int NP, int wc_in) {
   const long long units = static_cast<long long>(B) * HKV;
   const long long NPp = static_cast<long long>(NP) + kMaxPruneGroup - 1;     // whatever the prune group
-  // warp-specialised kernel: ceil(NPp / wc) + 1 with wc >= max(4 or wc_in, total / SMs, NPp / 63)
-  long long ws;
-  if (wc_in > 0) ws = (NPp + wc_in - 1) / wc_in;
-  else {
-    ws = (NPp + 3) / 4;
-    const long long per_unit = (sm_count() + units - 1) / units;
-    if (ws > per_unit) ws = per_unit;
-  }
-  if (ws > 63) ws = 63;
-  ws += 1;
+  // warp-specialised kernel: one partial per chunk; chunks of at least 4 pages (or the caller's size)
+  // and at most kWsMaxParts partials per q head
+  long long ws = (NPp + (wc_in > 0 ? wc_in : 4) - 1) / (wc_in > 0 ? wc_in : 4);
+  if (ws > kWsMaxParts) ws = kWsMaxParts;
   // fp16 kernel (ffa_decode_plan): ceil(NP / ppc) with ppc >= max(4, NP / want)
   long long f16;
   if (wc_in > 0) f16 = (static_cast<long long>(NP) + wc_in - 1) / wc_in;

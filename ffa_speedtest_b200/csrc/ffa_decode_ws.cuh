@@ -5,27 +5,27 @@
 // attn_kernel_v1210_fused_bsz_q2fp8.py:30-171), organised so that a pruned page costs only its
 // coarse bytes and its share of the scoring arithmetic:
 //
-//   warp 0        coarse producer: streams the coarse K tile of every page of the CTA's range into a
-//                 ring of shared-memory slots with TMA, as far ahead as the ring allows.
+//   warp 0        coarse producer: claims chunks of work (a run of pages of one (batch, kv-head)) from
+//                 a global counter, publishes them to the other warps and streams the coarse K tile of
+//                 every page into a ring of shared-memory slots with TMA, as far ahead as the ring
+//                 allows - across chunk boundaries, so the pipeline never drains between chunks.
 //   warps 2..5    scoring: each takes whole pages (64 tokens = four m16 tiles) round robin, computes
 //                 the coarse q.k of every token against all heads of the group on the tensor cores
 //                 and publishes the page's per-head maximum plus the raw dots.  No CTA barrier, no
 //                 exchange between warps: a page's statistic is complete inside one warp.
-//   warp 1        dispatcher: walks the published pages in order, applies the prune rule (a group of
-//                 SBS/64 pages is dropped only if every head's maximum over the group is strictly
-//                 below that head's threshold), writes the kept mask and, for kept pages, requests
-//                 residual + V with TMA into the next free slot of a second ring.
+//   warp 1        dispatcher: walks the published pages in order, eight per trip, applies the prune
+//                 rule (a group of SBS/64 pages is dropped only if every head's maximum over the group
+//                 is strictly below that head's threshold), writes the kept mask and, for kept pages,
+//                 requests residual + V with TMA into the next free slot of a second ring.
 //   warps 6..9    refine: kept page number k goes to refine warp k mod 4, which adds the residual
 //                 dot to the coarse dots, does the page's softmax and accumulates P.V for all 64
-//                 tokens.  Again nothing leaves the warp until the segment ends.
+//                 tokens.  At the end of a chunk each refine warp writes its own partial
+//                 (m, l, o[128]) per q head; whichever warp arrives last for a (batch, kv-head) merges
+//                 all its partials (stage 2, ...q2fp8.py:142-171) while the others carry on.
 //
-// Scoring runs ahead of refining by the depth of the rings, so the residual + V of several kept
-// pages are in flight while earlier pages are refined and later ones are scored; when most pages
-// are pruned the step moves at the speed of the scoring warps instead of paying a per-page barrier.
-//
-// A CTA walks a contiguous range of the flattened (batch x kv-head, page) space; the part inside
-// one (batch, kv-head) is a segment and ends in one partial (m, l, o[128]) per q head; the segment
-// that arrives last for a (batch, kv-head) merges its partials (stage 2, ...q2fp8.py:142-171).
+// Chunks are handed out dynamically, so an SM whose pages are mostly pruned simply takes more of
+// them; the kept fraction differs a lot between (batch, kv-head)s, and equal page ranges per SM left
+// the slowest SM 40 % behind the average.
 //
 // Numerics are those of the TMA kernel this replaces: q split into exact e4m3 pieces against raw
 // fp8 K bytes (fp8 coarse and the residual), fp16 q against dequantised codes (2-/4-bit coarse),
@@ -33,8 +33,8 @@
 // q.k_coarse + q.k_residual (the reference rounds k_coarse + k_residual to fp16 first).
 //
 // Every wait is bounded in wall-clock time.  A wait that gives up raises a CTA-wide flag; every role
-// then leaves its loop, the CTA publishes NaN partials for its remaining segments (so the merged
-// output of the affected heads is NaN, not a plausible number) and sets the status word.
+// then leaves its loops, the refine warps publish NaN partials for the chunk they were on (so the
+// merged output of the affected heads is NaN, not a plausible number) and the status word is set.
 #pragma once
 
 #include "ffa_decode_prims.cuh"
@@ -44,12 +44,15 @@ namespace ffa {
 namespace {
 
 constexpr int kNS = 4;                     // scoring warps
-constexpr int kNR = 4;                     // refine warps (the first four also run the segment epilogue)
+constexpr int kNR = kWsRefineWarps;        // refine warps, working in pairs: a kept page is refined by two warps, 32 tokens each
+constexpr int kNP = kNR / 2;               // (a page is out of its shared-memory slot twice as fast as with one warp,
+                                           // which leaves more of the ring for loads in flight)
 constexpr int kWsWarps = 2 + kNS + kNR;
 constexpr int kWsThreads = 32 * kWsWarps;
 constexpr int kBatch = kMaxPruneGroup;     // pages the dispatcher decides per trip; a whole prune group must fit (SBS <= 512)
 constexpr int kND = 2 * kBatch;            // published-page ring: scoring runs a trip ahead of the pages still being refined
 constexpr int kSampleRows = kSample;       // rows of a threshold sample tile
+constexpr int kNSeg = 4;                   // published chunks the consumers may lag behind the producer
 
 template <int FMT, int NT>
 struct WsSmem {
@@ -57,37 +60,40 @@ struct WsSmem {
   static constexpr int kCoarseSlot = kPage * kRow;                                  // 8 / 2 / 4 KiB
   // coarse ring: each scoring warp should find its next tile already landed, i.e. more than one slot
   // per warp in flight; the residual + V ring takes what is left of the 227 KiB
-  static constexpr int kNC = FMT == FFA_K_FP8 ? (NT == 2 ? 5 : 7) : (FMT == FFA_K_Q2 ? 16 : 8);
-  static constexpr int kNRV = (NT == 2 || FMT == FFA_K_FP8) ? 6 : 7;                // residual + V slots
+  static constexpr int kNC = FMT == FFA_K_FP8 ? 5 : (FMT == FFA_K_Q2 ? 16 : 8);
+  static constexpr int kNRV = NT == 2 ? 5 : 6;                                      // residual + V slots (24 KiB each)
   static constexpr int kSampleSlot = kSampleRows * kRow < 1024 ? 1024 : kSampleRows * kRow;
   static constexpr int kHist = NT * 1024;                                           // raw dots of one page
   static constexpr bool kHasChannelScale = (FMT == FFA_K_Q2 || FMT == FFA_K_NF4);
   static constexpr int kOffRv = 0;
   static constexpr int kOffCoarse = kOffRv + kNRV * kRvSlot;
-  static constexpr int kOffSample = kOffCoarse + kNC * kCoarseSlot;
-  static constexpr int kOffDHist = kOffSample + 2 * kSampleSlot;
+  static constexpr int kOffSample = kOffCoarse + kNC * kCoarseSlot;                 // 2 chunks x 2 tiles
+  static constexpr int kOffDHist = kOffSample + 4 * kSampleSlot;
   static constexpr int kOffDMax = kOffDHist + kND * kHist;      // [kND][8] page maxima
   static constexpr int kOffDPl = kOffDMax + kND * 32;           // [kND][8] mean-V: mass relative to the maximum
   static constexpr int kOffBars = kOffDPl + kND * 32;
-  static constexpr int kNBars = 2 * kNC + 2 + 2 * kND + 2 * kNRV + 1;
+  // barriers: chunk full/empty | coarse full/empty | sample full/empty | threshold full/empty |
+  //           page full/empty | residual+V full/empty
+  //           | three chunk-end meeting points of the refine warps | one meeting point per refine pair
+  static constexpr int kNBars = 2 * kNSeg + 2 * kNC + 8 + 4 + 2 * kND + 2 * kNRV + 3 + kNP;
   static constexpr int kOffMisc = kOffBars + ((kNBars * 8 + 63) / 64) * 64;
-  // misc: sTh[16] | sApx[16] | kq_page[8] | kq_ds[8] | abort, flag, pad[6] | sS[128] | sZ[128] | book[16]
+  // misc: sTh[2][16] | seg[kNSeg][4] | kq_page[8] | kq_ds[8] | abort, last, pad[6] | book[16] | per scoring warp sS[128], sZ[128]
   static constexpr int kOffTh = kOffMisc;
-  static constexpr int kOffApx = kOffTh + 64;
-  static constexpr int kOffKq = kOffApx + 64;
+  static constexpr int kOffSeg = kOffTh + 128;
+  static constexpr int kOffKq = kOffSeg + kNSeg * 16;
   static constexpr int kOffFlags = kOffKq + 64;
-  static constexpr int kOffS = kOffFlags + 32;
-  static constexpr int kOffZ = kOffS + 512;
-  static constexpr int kOffBook = kOffZ + 512;
-  static constexpr int kOffProf = kOffBook + 64;
-  static constexpr int kBytes = kOffProf + 1024;                // + alignment slack
-  // the epilogue's reduction buffers reuse the coarse ring (idle once a segment's pages are scored)
-  static constexpr int kRedBytes = kNR * 8 * 128 * 4 + 2 * kNR * 8 * 4 + 64;
-  static_assert(kRedBytes <= kNC * kCoarseSlot, "epilogue buffers must fit the coarse ring");
+  static constexpr int kOffBook = kOffFlags + 32;
+  static constexpr int kOffS = kOffBook + 64;
+  // chunk end: every refine warp's (o[heads][128], m, l), added up before one partial is written
+  static constexpr int kRedWarp = NT * 4 * 128 * 4;
+  static constexpr int kOffRed = kOffS + (kHasChannelScale ? kNS * 1024 : 0);
+  static constexpr int kOffRedML = kOffRed + kNR * kRedWarp;                          // [kNR][2][8] f32
+  static constexpr int kOffPairMax = kOffRedML + kNR * 64;                            // [kNP][2 pages][2 warps][8] f32
+  static constexpr int kBytes = kOffPairMax + kNP * 128 + 1024;                       // + alignment slack
   static_assert(kBytes <= 232448, "shared memory of one CTA");
   static_assert(kNRV >= 4, "the dispatcher issues up to four requests per round");
   // a ring shared by several consumer warps stays phase-safe only if it has at least as many slots
-  static_assert(kNC >= kNS && kNRV >= kNR, "rings must not be smaller than the number of their consumers");
+  static_assert(kNC >= kNS && kNRV >= kNP, "rings must not be smaller than the number of their consumers");
 };
 
 // Profiling builds (-DFFA_WS_PROFILE) time, per warp and in SM cycles, the waits of each role and a few
@@ -107,8 +113,8 @@ struct WsSmem {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void bar_sync(int id, int count) {
-  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(count) : "memory");
+__device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
 }
 
 // Bounded wait of one lane that also ends when another role has given up (abort flag).  Returns
@@ -140,17 +146,13 @@ __device__ __forceinline__ bool ws_wait_lane(uint32_t bar, uint32_t parity, int*
 // The whole (converged) warp waits, every lane on its own; the answer is made the same in every lane
 // so that the loops around the waits stay warp-uniform even when one lane runs out of time a moment
 // before the others.  (Polling with one lane and broadcasting measured slower.)
-__device__ __forceinline__ bool ws_wait_warp(uint32_t bar, uint32_t parity, int* abort_flag, int site) {
-  return __all_sync(0xffffffffu, ws_wait_lane(bar, parity, abort_flag, site)) != 0;
-}
-
 __device__ __forceinline__ bool ws_wait(uint32_t bar, uint32_t parity, int* abort_flag, int site) {
-  return ws_wait_warp(bar, parity, abort_flag, site);
+  return __all_sync(0xffffffffu, ws_wait_lane(bar, parity, abort_flag, site)) != 0;
 }
 #ifdef FFA_WS_PROFILE
 __device__ __forceinline__ bool ws_wait_timed(uint32_t bar, uint32_t parity, int* abort_flag, int site, uint32_t& acc) {
   const uint32_t t0 = static_cast<uint32_t>(clock());
-  const bool r = ws_wait_warp(bar, parity, abort_flag, site);
+  const bool r = ws_wait(bar, parity, abort_flag, site);
   acc += static_cast<uint32_t>(clock()) - t0;
   return r;
 }
@@ -236,6 +238,100 @@ __device__ __forceinline__ void prep_q(const DecodeParams& p, int b, int hkv, in
   }
 }
 
+// Stage 2 for the q heads h0, h0 + hstep, ... of one (batch, kv-head), by one warp: merges the n_seg
+// partials each of them has received, one per chunk (reference ...q2fp8.py:142-171; the mean-V fold
+// ...meanv_bsz_q2fp8.py:188-200) and writes the output rows.  Run by the warps of the CTA whose chunk
+// completed the (batch, kv-head).
+template <bool MV>
+__device__ __forceinline__ void ws_merge_unit(const DecodeParams& p, int b, int hkv, int n_seg, int h0, int hstep, int lane) {
+  constexpr uint32_t kFull = 0xffffffffu;
+  const int G = p.G;
+  const int64_t row0 = static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G;
+  for (int h = h0; h < G; h += hstep) {
+    const int64_t row = row0 + h;
+    // lane i holds (m, l) of partial i (n_seg <= kWsMaxParts = 32)
+    const float pm = lane < n_seg ? __ldcg(p.part_m + row * p.nch + lane) : -INFINITY;
+    const float pl = lane < n_seg ? __ldcg(p.part_l + row * p.nch + lane) : 0.f;
+    float top = pl != 0.f ? pm : -INFINITY;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, off));
+    const bool live_l = pl != 0.f && pm != -INFINITY;
+    const float wl = live_l ? exp2f(pm - top) : 0.f;
+    float acc = pl != 0.f ? pl * wl : 0.f;                   // a NaN mass (a chunk whose waits gave up) stays NaN
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(kFull, acc, off);
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i0 = 0; i0 < n_seg; i0 += 8) {
+      float4 v[8];
+      float w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = i0 + j;
+        w[j] = __shfl_sync(kFull, wl, i & 31);
+        const bool live = i < n_seg && w[j] != 0.f;
+        if (!live) w[j] = 0.f;
+        v[j] = live ? __ldcg(reinterpret_cast<const float4*>(p.part_o + (row * p.nch + i) * kHeadDim) + lane)
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { o.x += v[j].x * w[j]; o.y += v[j].y * w[j]; o.z += v[j].z * w[j]; o.w += v[j].w * w[j]; }
+    }
+    if (MV) {
+      // fold the pruned pages in: mass x mean of V; one (maximum, mass) pair per chunk
+      const float qm = lane < n_seg ? __ldcg(p.part_pm + row * p.nch + lane) : -INFINITY;
+      const float ql = lane < n_seg ? __ldcg(p.part_pl + row * p.nch + lane) : 0.f;
+      float p_top = ql != 0.f ? qm : -INFINITY;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) p_top = fmaxf(p_top, __shfl_xor_sync(kFull, p_top, off));
+      float p_acc = ql != 0.f ? ql * exp2f(qm - p_top) : 0.f;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) p_acc += __shfl_xor_sync(kFull, p_acc, off);
+      if (acc > 0.f || p_acc > 0.f) {
+        const float nm = fmaxf(top, p_top);
+        const float rb = acc > 0.f ? exp2f(top - nm) : 0.f, rp = p_acc > 0.f ? exp2f(p_top - nm) : 0.f;
+        const int64_t ve = (static_cast<int64_t>(b) * p.HKV + hkv) * kHeadDim + 4 * lane;
+        const float wv = p_acc * rp;
+        const int vd = p.v_bf16 ? FFA_BF16 : FFA_F16;
+        o.x = o.x * rb + load_as_float(p.v_mean, ve, vd) * wv;
+        o.y = o.y * rb + load_as_float(p.v_mean, ve + 1, vd) * wv;
+        o.z = o.z * rb + load_as_float(p.v_mean, ve + 2, vd) * wv;
+        o.w = o.w * rb + load_as_float(p.v_mean, ve + 3, vd) * wv;
+        acc = acc * rb + wv;
+      }
+    }
+    const float inv = acc == 0.f ? 0.f : 1.f / acc;
+    const float r0 = o.x * inv, r1 = o.y * inv, r2 = o.z * inv, r3 = o.w * inv;
+    const int64_t e = row * kHeadDim + 4 * lane;
+    if (p.out) {
+      store_from_float(p.out, e, p.q_dtype, r0);
+      store_from_float(p.out, e + 1, p.q_dtype, r1);
+      store_from_float(p.out, e + 2, p.q_dtype, r2);
+      store_from_float(p.out, e + 3, p.q_dtype, r3);
+    }
+    if (p.partial_out) {
+      float* po = p.partial_out + row * (kHeadDim + 1);
+      po[4 * lane] = r0; po[4 * lane + 1] = r1; po[4 * lane + 2] = r2; po[4 * lane + 3] = r3;
+      if (lane == 0) po[kHeadDim] = acc == 0.f ? -INFINITY : top + log2f(acc);
+    }
+  }
+}
+
+// One arrival for a (batch, kv-head): the caller has published its partial.  Returns true in every
+// lane of the warp that completes the count (and has reset the counter for the next launch).
+__device__ __forceinline__ bool ws_arrive_unit(const DecodeParams& p, int unit, int target, int lane) {
+  __threadfence();
+  __syncwarp();
+  int last = 0;
+  if (lane == 0) {
+    const int prev = atomicAdd(p.arrivals + unit, 1);
+    last = prev == target - 1;
+    if (last) p.arrivals[unit] = 0;
+  }
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (last) __threadfence();
+  return last != 0;
+}
+
 // FMT: coarse format; F8: fp8 encoding of the residual (and of the fp8 coarse base); NT: n-tiles of
 // four q heads (1: group <= 4, 2: group <= 8); VBF: V is bf16 (else fp16); QP: e4m3 pieces per q value;
 // MV: mean-V variant (pruned pages keep their coarse softmax mass; DecodeParams::v_mean).
@@ -258,33 +354,47 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int G = p.G, T = p.T;
   const int m_grp = p.group;                       // pages per prune group (SBS / 64)
+  const int CH = p.ppc;                            // pages per chunk (whole prune groups)
+  const int n_seg = p.nseg;                        // chunks per (batch, kv-head)
+  const int total_chunks = p.B * p.HKV * n_seg;
+  const int arrive_target = n_seg * (MV ? 2 : 1);           // arrivals that complete a (batch, kv-head): one per chunk
+                                                            // (mean-V: one more per chunk, by the dispatcher)
 
   const uint32_t bars = smem_u32(smem + L::kOffBars);
-  auto cfull = [&](int i) { return bars + 8u * i; };
-  auto cempty = [&](int i) { return bars + 8u * (kNC + i); };
-  auto sfull = [&](int i) { return bars + 8u * (2 * kNC + i); };
-  auto dfull = [&](int i) { return bars + 8u * (2 * kNC + 2 + i); };
-  auto dempty = [&](int i) { return bars + 8u * (2 * kNC + 2 + kND + i); };
-  auto rvfull = [&](int i) { return bars + 8u * (2 * kNC + 2 + 2 * kND + i); };
-  auto rvempty = [&](int i) { return bars + 8u * (2 * kNC + 2 + 2 * kND + kNRV + i); };
-  const uint32_t thfull = bars + 8u * (2 * kNC + 2 + 2 * kND + 2 * kNRV);
+  auto segfull = [&](int i) { return bars + 8u * i; };
+  auto segempty = [&](int i) { return bars + 8u * (kNSeg + i); };
+  constexpr int kB0 = 2 * kNSeg;
+  auto cfull = [&](int i) { return bars + 8u * (kB0 + i); };
+  auto cempty = [&](int i) { return bars + 8u * (kB0 + kNC + i); };
+  constexpr int kB1 = kB0 + 2 * kNC;
+  auto sfull = [&](int i) { return bars + 8u * (kB1 + i); };          // 2 chunks x 2 sample tiles
+  auto sempty = [&](int i) { return bars + 8u * (kB1 + 4 + i); };
+  auto thfull = [&](int i) { return bars + 8u * (kB1 + 8 + i); };      // 2 chunks
+  auto thempty = [&](int i) { return bars + 8u * (kB1 + 10 + i); };
+  constexpr int kB2 = kB1 + 12;
+  auto dfull = [&](int i) { return bars + 8u * (kB2 + i); };
+  auto dempty = [&](int i) { return bars + 8u * (kB2 + kND + i); };
+  constexpr int kB3 = kB2 + 2 * kND;
+  auto rvfull = [&](int i) { return bars + 8u * (kB3 + i); };
+  auto rvempty = [&](int i) { return bars + 8u * (kB3 + kNRV + i); };
+  constexpr int kB4 = kB3 + 2 * kNRV;
+  auto rfmeet = [&](int i) { return bars + 8u * (kB4 + i); };
+  auto pairmeet = [&](int i) { return bars + 8u * (kB4 + 3 + i); };
+  static_assert(kB4 + 3 + kNP == L::kNBars, "barrier table");
 
   float* dhist = reinterpret_cast<float*>(smem + L::kOffDHist);
   float* dmax = reinterpret_cast<float*>(smem + L::kOffDMax);
   float* dpl = reinterpret_cast<float*>(smem + L::kOffDPl);
-  float* sTh = reinterpret_cast<float*>(smem + L::kOffTh);
-  float* sApx = reinterpret_cast<float*>(smem + L::kOffApx);
+  float* sTh = reinterpret_cast<float*>(smem + L::kOffTh);          // [2 chunks][2 samples][8 heads]
+  int* sSeg = reinterpret_cast<int*>(smem + L::kOffSeg);            // [kNSeg][4]: unit, first page, pages, chunk of the unit
   int* kq_page = reinterpret_cast<int*>(smem + L::kOffKq);      // per residual+V slot: page of the (b, kv-head), -1 = end marker
   int* kq_ds = kq_page + 8;                                      // ... and the published-page entry that holds its dots
   int* sAbort = reinterpret_cast<int*>(smem + L::kOffFlags);
-  int* sFlag = sAbort + 1;
-  float* sS = reinterpret_cast<float*>(smem + L::kOffS);
-  float* sZ = reinterpret_cast<float*>(smem + L::kOffZ);
   float* sBook = reinterpret_cast<float*>(smem + L::kOffBook);
-  // epilogue buffers, on top of the coarse ring
-  float* red = reinterpret_cast<float*>(smem + L::kOffCoarse);      // [kNR][8 heads][128]
-  float* lred = red + kNR * 8 * 128;                                // [kNR][8]
-  float* mred = lred + kNR * 8;                                     // [kNR][8]
+  int* sLast = sAbort + 1;                                       // the chunk just finished completed its (batch, kv-head)
+  float* red = reinterpret_cast<float*>(smem + L::kOffRed);      // [kNR][4 NT heads][128]
+  float* redml = reinterpret_cast<float*>(smem + L::kOffRedML);  // [kNR][m: 8, l: 8]
+  float* pairmax = reinterpret_cast<float*>(smem + L::kOffPairMax);
 
   const bool use_res = p.use_res != 0;
   const bool sampled = p.th_in == nullptr;
@@ -295,15 +405,20 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
   const long long prof_c0 = clock64();
   unsigned long long prof_g0;
   asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(prof_g0));
-  uint32_t prof_role = 0, prof_epi = 0;
 #endif
   if (tid == 0) {
-    for (int i = 0; i < L::kNBars - 1; ++i) mbar_init(bars + 8 * i, 1);
-    mbar_init(thfull, 2);                          // the two scoring warps that score the samples
+    for (int i = 0; i < L::kNBars; ++i) mbar_init(bars + 8 * i, 1);
+    for (int i = 0; i < kNSeg; ++i) mbar_init(segempty(i), 1 + kNS + kNR);      // every consumer warp has read the chunk
+    for (int i = 0; i < 2; ++i) mbar_init(thfull(i), 2);                        // the two scoring warps that score the samples
+    for (int i = 0; i < 3; ++i) mbar_init(rfmeet(i), kNR);                      // every refine warp
+    for (int i = 0; i < kNP; ++i) mbar_init(pairmeet(i), 2);                    // the two warps of a refine pair
+    for (int i = 0; i < kND; ++i) mbar_init(dempty(i), 2);                      // both warps of the pair (or the dispatcher, twice)
+    for (int i = 0; i < kNRV; ++i) mbar_init(rvempty(i), 2);
     *sAbort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
+  if (FMT == FFA_K_NF4 && tid < 16) sBook[tid] = c_nf4_book[tid];
   __syncthreads();
 
   enum { kRoleCoarse = 0, kRoleDispatch = 1, kRoleScore = 2, kRoleRefine = 3 };
@@ -311,91 +426,113 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
   const int sw = warp - 2;                         // scoring warp index
   const int rw = warp - 2 - kNS;                   // refine warp index
 
-  // running counters that keep ring positions and mbarrier phases consistent across segments
-  uint32_t gc = 0;                                 // pages of earlier segments (all roles)
-  uint32_t kk = 0;                                 // dispatcher: kept pages + end markers issued so far
-  uint32_t myk = rw;                               // refine warp: ordinal of its next kept page
-  uint32_t act_ord = 0;                            // segments that ran the pipeline (phase of the per-segment barriers)
+  // Every consumer warp walks the published chunks in order.  `gc` counts the pages of earlier chunks:
+  // ring positions and mbarrier phases follow from it and are the same in every role.
+  uint32_t gc = 0;
+  int seg_unit = -1, seg_page0 = 0, seg_n = 0, seg_part = 0;
+  auto next_chunk = [&](uint32_t seg_i) -> bool {          // false: no more work (or a wait gave up)
+    const int slot = seg_i % kNSeg;
+    if (!WS_WAIT(segfull(slot), (seg_i / kNSeg) & 1u, 10, 5)) return false;
+    seg_unit = sSeg[slot * 4 + 0]; seg_page0 = sSeg[slot * 4 + 1]; seg_n = sSeg[slot * 4 + 2]; seg_part = sSeg[slot * 4 + 3];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(segempty(slot));
+    return seg_unit >= 0;
+  };
+  auto to_log2 = [&](float d) -> float { return (d * p.sm_scale) * kLog2e; };
 
-  const int NPp = p.NPp;                           // pages per (b, kv-head) rounded up to whole prune groups
-  const int64_t total_pages = static_cast<int64_t>(p.B) * p.HKV * NPp;
-  int64_t g0 = static_cast<int64_t>(blockIdx.x) * p.ppc;
-  const int64_t g1 = min(total_pages, g0 + p.ppc);
-
-  while (g0 < g1) {
-    // ---- segment geometry ------------------------------------------------------------------------
-    const int unit = static_cast<int>(g0 / NPp);
-    const int b = unit / p.HKV, hkv = unit % p.HKV;
-    const int64_t unit0 = static_cast<int64_t>(unit) * NPp;
-    const int page_begin = static_cast<int>(g0 - unit0);
-    const int n_pad = static_cast<int>(min(g1 - g0, static_cast<int64_t>(NPp - page_begin)));
-    const int n = max(0, min(n_pad, p.NP - page_begin));              // real pages of the segment
-    const int part = static_cast<int>(g0 / p.ppc - unit0 / p.ppc);    // partial slot of this segment
-    g0 += n_pad;
-    const int64_t row0 = static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G;
-    const bool aborted = *reinterpret_cast<volatile int*>(sAbort) != 0;   // uniform: read between CTA barriers
-    const bool active = n > 0 && !aborted;
-    const uint32_t seg_par = act_ord & 1u;
-
-    auto row_of_page = [&](int page, int bt_val) -> int {
-      return p.bt ? bt_val * kPage : b * T + page * kPage;
-    };
-    auto to_log2 = [&](float d) -> float { return (d * p.sm_scale) * kLog2e; };
-
-#ifdef FFA_WS_PROFILE
-    const uint32_t prof_seg0 = static_cast<uint32_t>(clock());
-#endif
-    if (active && role == kRoleCoarse) {
-      // ================= coarse producer ===========================================================
-      if (sampled && lane == 0) {
-        const int tok1 = (p.NTB - 1) * kSample;
-        const int r0 = p.bt ? p.bt[static_cast<int64_t>(b) * p.bt_stride] * kPage : b * T;
-        const int r1 = (p.bt ? p.bt[static_cast<int64_t>(b) * p.bt_stride + tok1 / kPage] * kPage
-                             : b * T + (tok1 / kPage) * kPage) + tok1 % kPage;
-        mbar_expect_tx(sfull(0), kSampleRows * ROW);
-        tma_load_2d(smem_u32(smem + L::kOffSample), &tm_s, hkv * ROW, r0, sfull(0));
-        mbar_expect_tx(sfull(1), kSampleRows * ROW);
-        tma_load_2d(smem_u32(smem + L::kOffSample + L::kSampleSlot), &tm_s, hkv * ROW, r1, sfull(1));
+  if (role == kRoleCoarse) {
+    // ================= coarse producer ===============================================================
+    // lane 0 asks for the next chunk a whole chunk ahead; the answer is only looked at (broadcast) when
+    // the chunk before it has been streamed, so the round trip of the atomic is never waited for
+    int next_raw = 0;
+    if (lane == 0) next_raw = atomicAdd(p.work, 1);
+    for (uint32_t seg_i = 0;; ++seg_i) {
+      const int chunk = __shfl_sync(kFull, next_raw, 0);
+      const bool end = chunk >= total_chunks || *reinterpret_cast<volatile int*>(sAbort) != 0;
+      if (!end && lane == 0) next_raw = atomicAdd(p.work, 1);
+      const int slot = seg_i % kNSeg;
+      if (seg_i >= kNSeg && !WS_WAIT(segempty(slot), ((seg_i / kNSeg) - 1u) & 1u, 11, 1)) break;
+      const int unit = end ? -1 : chunk / n_seg;
+      const int part = end ? 0 : chunk % n_seg;
+      const int page_begin = part * CH;
+      const int n = end ? 0 : min(CH, p.NP - page_begin);             // real pages (>= 1: a chunk never holds padding only)
+      if (lane == 0) {
+        sSeg[slot * 4 + 0] = unit; sSeg[slot * 4 + 1] = page_begin; sSeg[slot * 4 + 2] = n; sSeg[slot * 4 + 3] = part;
+        mbar_arrive(segfull(slot));
       }
-      int btv = 0;
-      for (int c = 0; c < n; ++c) {
-        const uint32_t gcc = gc + c;
-        const int slot = gcc % kNC;
-        if ((c & 31) == 0 && p.bt && c + lane < n)
-          btv = p.bt[static_cast<int64_t>(b) * p.bt_stride + page_begin + c + lane];
-        const int row = row_of_page(page_begin + c, __shfl_sync(kFull, btv, c & 31));
-        if (gcc >= kNC && !WS_WAIT(cempty(slot), ((gcc / kNC) - 1u) & 1u, 1, 0)) break;
+      if (end) break;
+      const int b = unit / p.HKV, hkv = unit % p.HKV;
+      if (sampled) {
+        // the two 16-token sample tiles of this (batch, kv-head), into the pair of slots of this chunk's parity
+        const int ss = seg_i & 1;
+        bool ok = true;
+        if (seg_i >= 2)
+          ok = WS_WAIT(sempty(2 * ss), ((seg_i / 2) - 1u) & 1u, 12, 2) && WS_WAIT(sempty(2 * ss + 1), ((seg_i / 2) - 1u) & 1u, 12, 2);
+        if (!ok) break;
         if (lane == 0) {
-          mbar_expect_tx(cfull(slot), L::kCoarseSlot);
-          tma_load_2d(smem_u32(smem + L::kOffCoarse + slot * L::kCoarseSlot), &tm_c, hkv * ROW, row, cfull(slot));
+          const int tok1 = (p.NTB - 1) * kSample;
+          const int r0 = p.bt ? p.bt[static_cast<int64_t>(b) * p.bt_stride] * kPage : b * T;
+          const int r1 = (p.bt ? p.bt[static_cast<int64_t>(b) * p.bt_stride + tok1 / kPage] * kPage
+                               : b * T + (tok1 / kPage) * kPage) + tok1 % kPage;
+          mbar_expect_tx(sfull(2 * ss), kSampleRows * ROW);
+          tma_load_2d(smem_u32(smem + L::kOffSample + (2 * ss) * L::kSampleSlot), &tm_s, hkv * ROW, r0, sfull(2 * ss));
+          mbar_expect_tx(sfull(2 * ss + 1), kSampleRows * ROW);
+          tma_load_2d(smem_u32(smem + L::kOffSample + (2 * ss + 1) * L::kSampleSlot), &tm_s, hkv * ROW, r1, sfull(2 * ss + 1));
         }
       }
-    } else if (active && role == kRoleDispatch) {
-      // ================= dispatcher ================================================================
-      // Eight pages per trip, four lanes per page (lane = 4 * page + hq, heads 2hq and 2hq + 1): one
-      // chain of wait -> compare -> vote decides eight pages, and the lanes that lead a kept page
-      // request its residual + V side by side.  (One page per trip made this warp the slowest stage:
-      // the chain is a few hundred cycles of latency however little it computes.)
-      const int pj = lane >> 2, hq = lane & 3;
-      float th0 = 0.f, th1 = 0.f;
+      int btv = 0;
       bool ok = true;
+      for (int c = 0; c < n; ++c) {
+        const uint32_t gcc = gc + c;
+        const int cslot = gcc % kNC;
+        if ((c & 31) == 0 && p.bt && c + lane < n)
+          btv = p.bt[static_cast<int64_t>(b) * p.bt_stride + page_begin + c + lane];
+        const int bv = __shfl_sync(kFull, btv, c & 31);
+        const int row = p.bt ? bv * kPage : b * T + (page_begin + c) * kPage;
+        if (gcc >= kNC && !WS_WAIT(cempty(cslot), ((gcc / kNC) - 1u) & 1u, 1, 0)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(cfull(cslot), L::kCoarseSlot);
+          tma_load_2d(smem_u32(smem + L::kOffCoarse + cslot * L::kCoarseSlot), &tm_c, hkv * ROW, row, cfull(cslot));
+        }
+      }
+      if (!ok) break;
+      gc += static_cast<uint32_t>(n);
+    }
+  } else if (role == kRoleDispatch) {
+    // ================= dispatcher ====================================================================
+    // Eight pages per trip, four lanes per page (lane = 4 * page + hq, heads 2hq and 2hq + 1): one
+    // chain of wait -> compare -> vote decides eight pages, and the lanes that lead a kept page
+    // request its residual + V side by side.  (One page per trip made this warp the slowest stage:
+    // the chain is a few hundred cycles of latency however little it computes.)
+    const int pj = lane >> 2, hq = lane & 3;
+    const int gsz = 4 * m_grp;                                   // lanes of one prune group (4 ... 32)
+    const uint32_t gmask = gsz >= 32 ? kFull : (((1u << gsz) - 1u) << ((lane / gsz) * gsz));
+    uint32_t kk = 0;                                             // kept pages + end markers issued so far
+    bool ok = true;
+    for (uint32_t seg_i = 0; ok && next_chunk(seg_i); ++seg_i) {
+      const int unit = seg_unit, page_begin = seg_page0, n = seg_n, part = seg_part;
+      const int b = unit / p.HKV, hkv = unit % p.HKV;
+      const int64_t row0 = static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G;
+      float th0 = 0.f, th1 = 0.f;
       if (sampled) {
-        ok = WS_WAIT(thfull, seg_par, 2, 0);
-        th0 = fmaxf(sTh[2 * hq], sTh[8 + 2 * hq]) - p.delta;
-        th1 = fmaxf(sTh[2 * hq + 1], sTh[8 + 2 * hq + 1]) - p.delta;
+        const int ss = seg_i & 1;
+        ok = WS_WAIT(thfull(ss), (seg_i / 2) & 1u, 2, 0);
+        if (!ok) break;
+        th0 = fmaxf(sTh[ss * 16 + 2 * hq], sTh[ss * 16 + 8 + 2 * hq]) - p.delta;
+        th1 = fmaxf(sTh[ss * 16 + 2 * hq + 1], sTh[ss * 16 + 8 + 2 * hq + 1]) - p.delta;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(thempty(ss));
       } else {
         if (2 * hq < G) th0 = p.th_in[row0 + 2 * hq];
         if (2 * hq + 1 < G) th1 = p.th_in[row0 + 2 * hq + 1];
       }
-      if (ok && p.th_out && page_begin == 0 && pj == 0) {
+      if (p.th_out && page_begin == 0 && pj == 0) {
         if (2 * hq < G) p.th_out[row0 + 2 * hq] = th0;
         if (2 * hq + 1 < G) p.th_out[row0 + 2 * hq + 1] = th1;
       }
-      // mean-V: running maximum / mass of the pruned pages, heads 2hq and 2hq + 1 (meaningful in lanes 0-3)
+      // mean-V: running maximum / mass of the pruned pages, heads 2hq and 2hq + 1 (the same in every page's lanes)
       float apx_m0 = -INFINITY, apx_l0 = 0.f, apx_m1 = -INFINITY, apx_l1 = 0.f;
       int8_t* mask_row = p.mask ? p.mask + (static_cast<int64_t>(b) * p.HKV + hkv) * p.NTBS : nullptr;
-      const int gsz = 4 * m_grp;                                   // lanes of one prune group (4 ... 32)
-      const uint32_t gmask = gsz >= 32 ? kFull : (((1u << gsz) - 1u) << ((lane / gsz) * gsz));
       for (int c0 = 0; ok && c0 < n; c0 += kBatch) {
         const int c = c0 + pj;
         const bool valid = c < n;
@@ -436,7 +573,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
           if (lead && keep && (rank >> 2) == round) {
             const uint32_t ord = kk + rank;
             const int slot = ord % kNRV;
-            const int row = row_of_page(page_begin + c, btv);
+            const int row = p.bt ? btv * kPage : b * T + (page_begin + c) * kPage;
             if (ord >= kNRV) lane_ok = ws_wait_lane(rvempty(slot), ((ord / kNRV) - 1u) & 1u, sAbort, 4);
             if (lane_ok) {
               kq_page[slot] = page_begin + c;
@@ -478,12 +615,13 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
           join(apx_m1, apx_l1, m1, l1);
         }
         // a pruned page's entry is free again; a kept page's is released by the refine warp that reads it
-        if (lead && !keep) mbar_arrive(dempty(ds));
+        if (lead && !keep) mbar_arrive_n(dempty(ds), 2);
         ok = __all_sync(kFull, lane_ok) != 0;
       }
-      // end markers: one per refine warp (kept page k goes to warp k mod kNR, so kNR consecutive
-      // ordinals reach every warp once)
-      for (int i = 0; ok && i < kNR; ++i) {
+      if (!ok) break;
+      // end markers: one per refine pair (kept page k goes to pair k mod kNP, so kNP consecutive
+      // ordinals reach every pair once)
+      for (int i = 0; ok && i < kNP; ++i) {
         const int slot = kk % kNRV;
         if (kk >= kNRV && !WS_WAIT(rvempty(slot), ((kk / kNRV) - 1u) & 1u, 5, 2)) { ok = false; break; }
         if (lane == 0) {
@@ -492,19 +630,44 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
         }
         ++kk;
       }
-      if (MV && lane < 4) {
-        sApx[2 * hq] = apx_m0; sApx[8 + 2 * hq] = apx_l0;
-        sApx[2 * hq + 1] = apx_m1; sApx[8 + 2 * hq + 1] = apx_l1;
+      if (!ok) break;
+      if (mask_row && page_begin + CH >= p.NPp) {
+        // mask entries past the last group that holds tokens (padding blocks count as pruned)
+        for (int i = (p.NP + m_grp - 1) / m_grp + lane; i < p.NTBS; i += 32) mask_row[i] = 0;
       }
-    } else if (active && role == kRoleScore) {
-      // ================= scoring warps =============================================================
-      const int stid = sw * 32 + lane;
+      if (MV) {
+        // this chunk's pruned mass; the dispatcher is one more party to the (batch, kv-head)'s arrival count
+        if (pj == 0) {
+          if (2 * hq < G) {
+            p.part_pm[(row0 + 2 * hq) * p.nch + part] = apx_m0;
+            p.part_pl[(row0 + 2 * hq) * p.nch + part] = apx_l0;
+          }
+          if (2 * hq + 1 < G) {
+            p.part_pm[(row0 + 2 * hq + 1) * p.nch + part] = apx_m1;
+            p.part_pl[(row0 + 2 * hq + 1) * p.nch + part] = apx_l1;
+          }
+        }
+        if (ws_arrive_unit(p, unit, arrive_target, lane)) ws_merge_unit<MV>(p, b, hkv, n_seg, 0, 1, lane);
+      }
+      gc += static_cast<uint32_t>(n);
+    }
+  } else if (role == kRoleScore) {
+    // ================= scoring warps =================================================================
+    float* sS = reinterpret_cast<float*>(smem + L::kOffS) + sw * 256;   // this warp's copy of the channel scales
+    float* sZ = sS + 128;
+    bool ok = true;
+    for (uint32_t seg_i = 0; ok && next_chunk(seg_i); ++seg_i) {
+      const int unit = seg_unit, page_begin = seg_page0, n = seg_n;
+      const int b = unit / p.HKV, hkv = unit % p.HKV;
       if (L::kHasChannelScale) {
-        const int64_t o = (static_cast<int64_t>(b) * p.HKV + hkv) * kHeadDim + stid;
-        sS[stid] = load_as_float(p.ks, o, p.scale_dtype);
-        if (FMT == FFA_K_Q2) sZ[stid] = load_as_float(p.kz, o, p.scale_dtype);
-        if (FMT == FFA_K_NF4 && stid < 16) sBook[stid] = c_nf4_book[stid];
-        bar_sync(1, kNS * 32);
+        __syncwarp();                              // the previous chunk's reads of sS / sZ are done
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int64_t o = (static_cast<int64_t>(b) * p.HKV + hkv) * kHeadDim + lane + 32 * i;
+          sS[lane + 32 * i] = load_as_float(p.ks, o, p.scale_dtype);
+          if (FMT == FFA_K_Q2) sZ[lane + 32 * i] = load_as_float(p.kz, o, p.scale_dtype);
+        }
+        __syncwarp();
       }
       ScaleCtx sc;
       sc.sS = sS; sc.sZ = sZ; sc.book = sBook; sc.page_scale = 1.0f;
@@ -525,9 +688,9 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
           same = same && exact_in_f16(s) && exact_in_f16(z);
           const __half hs = __float2half_rn(s), hz = __float2half_rn(z);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const __half fast = __hfma(__float2half_rn(static_cast<float>(c)), hs, hz);
-            const __half ref = __float2half_rn(fmaf(static_cast<float>(c), s, z));
+          for (int cc = 0; cc < 4; ++cc) {
+            const __half fast = __hfma(__float2half_rn(static_cast<float>(cc)), hs, hz);
+            const __half ref = __float2half_rn(fmaf(static_cast<float>(cc), s, z));
             same = same && (__half_as_ushort(fast) == __half_as_ushort(ref));
           }
         }
@@ -555,16 +718,18 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
         else dot_f16<FMT, NT, false>(out, qh, tile, sc, slice, g, t);
       };
 
-      bool ok = true;
       // ---- prune thresholds (reference ...q2fp8.py:55-82): two 16-token samples of the coarse K,
       // tokens [0,16) and [(NTB-1)*16, +16), scored by the first two scoring warps
       if (sampled && sw < 2) {
-        ok = WS_WAIT(sfull(sw), seg_par, 6, 0);
+        const int ss = seg_i & 1;
+        ok = WS_WAIT(sfull(2 * ss + sw), (seg_i / 2) & 1u, 6, 0);
+        if (ok && seg_i >= 2) ok = WS_WAIT(thempty(ss), ((seg_i / 2) - 1u) & 1u, 13, 0);
+        if (!ok) break;
         const int blk = sw == 0 ? 0 : p.NTB - 1;
         const int tok0 = blk * kSample;
         if (FMT == FFA_K_NVFP4) apply_block_scale(load_block_scale(blk));
         float d[NT][2];
-        coarse_dots(d, smem + L::kOffSample + sw * L::kSampleSlot, 0);
+        coarse_dots(d, smem + L::kOffSample + (2 * ss + sw) * L::kSampleSlot, 0);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const float s0 = tok0 + g < T ? to_log2(d[nt][0]) : -INFINITY;
@@ -572,14 +737,14 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
           float mm = fmaxf(s0, s1);
 #pragma unroll
           for (int off = 4; off < 32; off <<= 1) mm = fmaxf(mm, __shfl_xor_sync(kFull, mm, off));
-          if (g == 0) sTh[sw * 8 + 4 * nt + t] = mm;
+          if (g == 0) sTh[ss * 16 + sw * 8 + 4 * nt + t] = mm;
         }
         __syncwarp();
-        if (lane == 0 && ok) mbar_arrive(thfull);
+        if (lane == 0) { mbar_arrive(thfull(ss)); mbar_arrive(sempty(2 * ss + sw)); }
       }
 
       float ks_batch = 0.f;         // nvfp4: block scales of this warp's next 32 pages, one per lane
-      for (int c = sw; ok && c < n; c += kNS) {
+      for (int c = sw; c < n; c += kNS) {
         const uint32_t gcc = gc + c;
         const int slot = gcc % kNC, ds = gcc % kND;
         const int page = page_begin + c;
@@ -600,7 +765,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
         if (!WS_WAIT(cfull(slot), (gcc / kNC) & 1u, 7, 1)) { ok = false; break; }
         if (gcc >= kND && !WS_WAIT(dempty(ds), ((gcc / kND) - 1u) & 1u, 8, 2)) { ok = false; break; }
         PROF_T(t_dots);
-        PROF_INC(5);
         const uint8_t* tile = smem + L::kOffCoarse + slot * L::kCoarseSlot;
         float* hd = dhist + ds * (NT * 256);
         float cm[NT];
@@ -667,8 +831,21 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
         __syncwarp();
         if (lane == 0) mbar_arrive(dfull(ds));
       }
-    } else if (role == kRoleRefine) {
-      // ================= refine warps ==============================================================
+      gc += static_cast<uint32_t>(n);
+    }
+  } else {
+    // ================= refine warps ==================================================================
+    const int pair = rw >> 1, sub = rw & 1;        // this warp refines tokens [32 sub, 32 sub + 32) of its pair's pages
+    uint32_t myk = pair;                           // ordinal of the pair's next kept page (or end marker)
+    uint32_t pair_pages = 0;                       // pages the pair has refined: phase of its meeting point
+    const int src = 8 * t + (g >> 1);
+    const uint32_t sel = (g & 1) ? 0x7632u : 0x5410u;
+    const int vsel = (lane >> 3) & 1;
+    const float qnan = __int_as_float(0x7fc00000);
+    for (uint32_t seg_i = 0; next_chunk(seg_i); ++seg_i) {
+      const int unit = seg_unit, part = seg_part;
+      const int b = unit / p.HKV, hkv = unit % p.HKV;
+      const int64_t row0 = static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G;
       float run_m[NT], run_l[NT], run_o[NT][8][2];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
@@ -677,314 +854,227 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
 #pragma unroll
         for (int i = 0; i < 8; ++i) run_o[nt][i][0] = run_o[nt][i][1] = 0.f;
       }
-      if (active) {
-        uint32_t qb[NT * (QP - 1)][4][2];
-        uint32_t qh[NT][8][2];
-        float qinv[NT];
-        prep_q<NT, QP, false>(p, b, hkv, G, g, t, qb, qh, qinv);
-        const int src = 8 * t + (g >> 1);
-        const uint32_t sel = (g & 1) ? 0x7632u : 0x5410u;
-        const int vsel = (lane >> 3) & 1;
-        for (;;) {
-          const int slot = myk % kNRV;
-          // as for the coarse ring: the slot's previous page (another warp's) must have been released
-          // before this wait can tell the phase it wants from the one before it
-          if (myk >= kNRV && !WS_WAIT(rvempty(slot), ((myk / kNRV) - 1u) & 1u, 9, 0)) break;
-          if (!WS_WAIT(rvfull(slot), (myk / kNRV) & 1u, 9, 0)) break;
-          const int page = kq_page[slot];
-          const int ds = kq_ds[slot];
-          myk += kNR;
-          if (page < 0) {                                  // end of the segment
-            __syncwarp();
-            if (lane == 0) mbar_arrive(rvempty(slot));
-            break;
-          }
-          PROF_T(t_page);
-          PROF_INC(2);
-          const uint8_t* rtile = smem + L::kOffRv + slot * kRvSlot;
-          const uint8_t* vt = rtile + kPage * kResRow;
-          float* hs = dhist + ds * (NT * 256);
-          const bool partial = (page + 1) * kPage > T;
-          float rm[NT];
+      uint32_t qb[NT * (QP - 1)][4][2];
+      uint32_t qh[NT][8][2];
+      float qinv[NT];
+      prep_q<NT, QP, false>(p, b, hkv, G, g, t, qb, qh, qinv);
+      bool ok = true;
+      for (;;) {
+        const int slot = myk % kNRV;
+        // as for the coarse ring: the slot's previous page (another warp's) must have been released
+        // before this wait can tell the phase it wants from the one before it
+        if (myk >= kNRV && !WS_WAIT(rvempty(slot), ((myk / kNRV) - 1u) & 1u, 9, 0)) { ok = false; break; }
+        if (!WS_WAIT(rvfull(slot), (myk / kNRV) & 1u, 9, 0)) { ok = false; break; }
+        const int page = kq_page[slot];
+        const int ds = kq_ds[slot];
+        myk += kNP;
+        if (page < 0) {                                  // end of the chunk
+          __syncwarp();
+          if (lane == 0) mbar_arrive(rvempty(slot));
+          break;
+        }
+        PROF_T(t_page);
+        PROF_INC(2);
+        const uint8_t* rtile = smem + L::kOffRv + slot * kRvSlot;
+        const uint8_t* vt = rtile + kPage * kResRow;
+        float* hs = dhist + ds * (NT * 256);
+        const bool partial = (page + 1) * kPage > T;
+        float rm[NT];
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) rm[nt] = -INFINITY;
-          // pass 1 (rolled, one 16-token tile per trip): refined scores = coarse dots + residual dots,
-          // written back over the dots (each lane owns its entries), and the page maximum
-#pragma unroll 1
-          for (int mt = 0; mt < 4; ++mt) {
-            float dr[NT][2];
+        for (int nt = 0; nt < NT; ++nt) rm[nt] = -INFINITY;
+        // pass 1 (this warp's two 16-token tiles): refined scores = coarse dots + residual dots, written
+        // back over the dots (each lane owns its entries), and the maximum of its half of the page
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) dr[nt][0] = dr[nt][1] = 0.f;
-            if (use_res) dot_fp8<F8, NT, QP>(dr, qb, qinv, rtile, mt, g, t);
-            const int tok = page * kPage + 16 * mt + g;
+        for (int mt = 2 * sub; mt < 2 * sub + 2; ++mt) {
+          float dr[NT][2];
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              float* e = hs + ((mt * NT + nt) * 2) * 32 + lane;
-              const float s0 = tok < T ? to_log2(e[0] + dr[nt][0]) : -INFINITY;
-              const float s1 = tok + 8 < T ? to_log2(e[32] + dr[nt][1]) : -INFINITY;
-              e[0] = s0;
-              e[32] = s1;
-              rm[nt] = fmaxf(rm[nt], fmaxf(s0, s1));
-            }
-          }
+          for (int nt = 0; nt < NT; ++nt) dr[nt][0] = dr[nt][1] = 0.f;
+          if (use_res) dot_fp8<F8, NT, QP>(dr, qb, qinv, rtile, mt, g, t);
+          const int tok = page * kPage + 16 * mt + g;
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-            for (int off = 4; off < 32; off <<= 1) rm[nt] = fmaxf(rm[nt], __shfl_xor_sync(kFull, rm[nt], off));
+            float* e = hs + ((mt * NT + nt) * 2) * 32 + lane;
+            const float s0 = tok < T ? to_log2(e[0] + dr[nt][0]) : -INFINITY;
+            const float s1 = tok + 8 < T ? to_log2(e[32] + dr[nt][1]) : -INFINITY;
+            e[0] = s0;
+            e[32] = s1;
+            rm[nt] = fmaxf(rm[nt], fmaxf(s0, s1));
           }
+        }
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            // pass 2 (rolled): p = exp2(s - page max), fp32 sum, fp16 rounding for the P.V product
-            // (...q2fp8.py:123-131); the eight 16-channel accumulators of P.V live across the trips
-            float oacc[8][4];
+        for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
-            float l = 0.f;
-#pragma unroll 1
-            for (int mt = 0; mt < 4; ++mt) {
-              const float* e = hs + ((mt * NT + nt) * 2) * 32 + lane;
-              const float s0 = e[0], s1 = e[32];
-              const float p0 = s0 == -INFINITY ? 0.f : ex2_approx(s0 - rm[nt]);
-              const float p1 = s1 == -INFINITY ? 0.f : ex2_approx(s1 - rm[nt]);
-              l += p0 + p1;
-              uint32_t w0, w1;
-              if (VBF) {
-                // fp16(p) = hi + lo exactly, both bf16
-                const float f0 = __half2float(__float2half_rn(p0)), f1 = __half2float(__float2half_rn(p1));
-                const __nv_bfloat16 h0 = __float2bfloat16_rn(f0), h1 = __float2bfloat16_rn(f1);
-                const __nv_bfloat16 l0 = __float2bfloat16_rn(f0 - __bfloat162float(h0));
-                const __nv_bfloat16 l1 = __float2bfloat16_rn(f1 - __bfloat162float(h1));
-                w0 = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l0)) << 16);
-                w1 = static_cast<uint32_t>(__bfloat16_as_ushort(h1)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l1)) << 16);
-              } else {
-                w0 = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(p0)));
-                w1 = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(p1)));
-              }
-              // P^T fragment: tokens 2t, 2t+1 (and +8) of column g = (head 4nt + g/2, piece g&1)
-              const uint32_t x0 = __shfl_sync(kFull, w0, src), x1 = __shfl_sync(kFull, w0, src + 4);
-              const uint32_t y0 = __shfl_sync(kFull, w1, src), y1 = __shfl_sync(kFull, w1, src + 4);
-              const uint32_t pb0 = __byte_perm(x0, x1, sel), pb1 = __byte_perm(y0, y1, sel);
-              const int vrow = 16 * mt + (lane & 7) + ((lane >> 4) & 1) * 8;
-              uint32_t m01 = 0xffffffffu, m23 = 0xffffffffu;
-              if (partial) {
-                const int valid = T - (page * kPage + 16 * mt);       // valid tokens in this 16-token tile
-                m01 = (2 * t < valid ? 0xffffu : 0u) | (2 * t + 1 < valid ? 0xffff0000u : 0u);
-                m23 = (2 * t + 8 < valid ? 0xffffu : 0u) | (2 * t + 9 < valid ? 0xffff0000u : 0u);
-              }
-              const uint32_t vbase = smem_u32(vt + vrow * 128);
+          for (int off = 4; off < 32; off <<= 1) rm[nt] = fmaxf(rm[nt], __shfl_xor_sync(kFull, rm[nt], off));
+        }
+        {
+          // the page maximum (...q2fp8.py:121) is over both halves: the two warps swap theirs
+          float* pm = pairmax + (pair * 2 + (pair_pages & 1u)) * 16;
+          if (g == 0) {
 #pragma unroll
-              for (int half = 0; half < 2; ++half) {
-                uint32_t a[4][4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const int ch = 2 * (4 * half + j) + vsel;
-                  ldmatrix_x4_trans(a[j], vbase + (ch >> 3) * (kPage * 128) + (((ch & 7) ^ (vrow & 7)) * 16));
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  if (partial) { a[j][0] &= m01; a[j][1] &= m01; a[j][2] &= m23; a[j][3] &= m23; }
-                  if (VBF) mma_bf16(oacc[4 * half + j], a[j][0], a[j][1], a[j][2], a[j][3], pb0, pb1);
-                  else mma_f16(oacc[4 * half + j], a[j][0], a[j][1], a[j][2], a[j][3], pb0, pb1);
-                }
-              }
-            }
-            // stage-2 recurrence over the warp's pages in page order (...q2fp8.py:162-167)
-            const float nm = fmaxf(run_m[nt], rm[nt]);
-            const float rp = nm == -INFINITY ? 0.f : ex2_approx(run_m[nt] - nm);
-            const float rb = nm == -INFINITY ? 0.f : ex2_approx(rm[nt] - nm);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              run_o[nt][i][0] = run_o[nt][i][0] * rp + (oacc[i][0] + oacc[i][1]) * rb;
-              run_o[nt][i][1] = run_o[nt][i][1] * rp + (oacc[i][2] + oacc[i][3]) * rb;
-            }
-            run_l[nt] = run_l[nt] * rp + l * rb;
-            run_m[nt] = nm;
+            for (int nt = 0; nt < NT; ++nt) pm[sub * 8 + 4 * nt + t] = rm[nt];
           }
           __syncwarp();
-          if (lane == 0) {                                 // residual, V and the dots of this page are consumed
-            mbar_arrive(rvempty(slot));
-            mbar_arrive(dempty(ds));
+          if (lane == 0) mbar_arrive(pairmeet(pair));
+          if (!WS_WAIT(pairmeet(pair), pair_pages & 1u, 17, 3)) { ok = false; break; }
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) rm[nt] = fmaxf(rm[nt], pm[(sub ^ 1) * 8 + 4 * nt + t]);
+          ++pair_pages;
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          // pass 2 (this warp's two tiles): p = exp2(s - page max), fp32 sum, fp16 rounding for the P.V product
+          // (...q2fp8.py:123-131); the eight 16-channel accumulators of P.V live across the trips
+          float oacc[8][4];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+          float l = 0.f;
+#pragma unroll
+          for (int mt = 2 * sub; mt < 2 * sub + 2; ++mt) {
+            const float* e = hs + ((mt * NT + nt) * 2) * 32 + lane;
+            const float s0 = e[0], s1 = e[32];
+            const float p0 = s0 == -INFINITY ? 0.f : ex2_approx(s0 - rm[nt]);
+            const float p1 = s1 == -INFINITY ? 0.f : ex2_approx(s1 - rm[nt]);
+            l += p0 + p1;
+            uint32_t w0, w1;
+            if (VBF) {
+              // fp16(p) = hi + lo exactly, both bf16
+              const float f0 = __half2float(__float2half_rn(p0)), f1 = __half2float(__float2half_rn(p1));
+              const __nv_bfloat16 h0 = __float2bfloat16_rn(f0), h1 = __float2bfloat16_rn(f1);
+              const __nv_bfloat16 l0 = __float2bfloat16_rn(f0 - __bfloat162float(h0));
+              const __nv_bfloat16 l1 = __float2bfloat16_rn(f1 - __bfloat162float(h1));
+              w0 = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l0)) << 16);
+              w1 = static_cast<uint32_t>(__bfloat16_as_ushort(h1)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l1)) << 16);
+            } else {
+              w0 = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(p0)));
+              w1 = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(p1)));
+            }
+            // P^T fragment: tokens 2t, 2t+1 (and +8) of column g = (head 4nt + g/2, piece g&1)
+            const uint32_t x0 = __shfl_sync(kFull, w0, src), x1 = __shfl_sync(kFull, w0, src + 4);
+            const uint32_t y0 = __shfl_sync(kFull, w1, src), y1 = __shfl_sync(kFull, w1, src + 4);
+            const uint32_t pb0 = __byte_perm(x0, x1, sel), pb1 = __byte_perm(y0, y1, sel);
+            const int vrow = 16 * mt + (lane & 7) + ((lane >> 4) & 1) * 8;
+            uint32_t m01 = 0xffffffffu, m23 = 0xffffffffu;
+            if (partial) {
+              const int valid = T - (page * kPage + 16 * mt);       // valid tokens in this 16-token tile
+              m01 = (2 * t < valid ? 0xffffu : 0u) | (2 * t + 1 < valid ? 0xffff0000u : 0u);
+              m23 = (2 * t + 8 < valid ? 0xffffu : 0u) | (2 * t + 9 < valid ? 0xffff0000u : 0u);
+            }
+            const uint32_t vbase = smem_u32(vt + vrow * 128);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t a[4][4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int ch = 2 * (4 * half + j) + vsel;
+                ldmatrix_x4_trans(a[j], vbase + (ch >> 3) * (kPage * 128) + (((ch & 7) ^ (vrow & 7)) * 16));
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (partial) { a[j][0] &= m01; a[j][1] &= m01; a[j][2] &= m23; a[j][3] &= m23; }
+                if (VBF) mma_bf16(oacc[4 * half + j], a[j][0], a[j][1], a[j][2], a[j][3], pb0, pb1);
+                else mma_f16(oacc[4 * half + j], a[j][0], a[j][1], a[j][2], a[j][3], pb0, pb1);
+              }
+            }
           }
-          PROF_ADD(1, t_page);
+          // stage-2 recurrence over the warp's pages in page order (...q2fp8.py:162-167)
+          const float nm = fmaxf(run_m[nt], rm[nt]);
+          const float rp = nm == -INFINITY ? 0.f : ex2_approx(run_m[nt] - nm);
+          const float rb = nm == -INFINITY ? 0.f : ex2_approx(rm[nt] - nm);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            run_o[nt][i][0] = run_o[nt][i][0] * rp + (oacc[i][0] + oacc[i][1]) * rb;
+            run_o[nt][i][1] = run_o[nt][i][1] * rp + (oacc[i][2] + oacc[i][3]) * rb;
+          }
+          run_l[nt] = run_l[nt] * rp + l * rb;
+          run_m[nt] = nm;
+        }
+        __syncwarp();
+        if (lane == 0) {                                 // residual, V and the dots of this page are consumed
+          mbar_arrive(rvempty(slot));
+          mbar_arrive(dempty(ds));
+        }
+        PROF_ADD(1, t_page);
+      }
+      // ---- chunk end: the refine warps add up their shares and write ONE partial per q head ----------
+      // (separate partials per warp made the merge of a (batch, kv-head) read four times as many rows,
+      // one L2 round trip per eight of them, on a single warp)
+      {
+        float* myred = red + rw * (L::kRedWarp / 4);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          float l = run_l[nt];
+#pragma unroll
+          for (int off = 4; off < 32; off <<= 1) l += __shfl_xor_sync(kFull, l, off);
+          const int h = 4 * nt + t;
+          float* w = myred + h * 128;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            w[16 * i + g] = run_o[nt][i][0];
+            w[16 * i + g + 8] = run_o[nt][i][1];
+          }
+          if (g == 0) { redml[rw * 16 + h] = run_m[nt]; redml[rw * 16 + 8 + h] = l; }
         }
       }
-      // this warp's share of the segment: waits for the other roles to leave the coarse ring alone.
-      // A refine warp holds its end marker only after the dispatcher has consumed every published page,
-      // which is after the scoring warps read their last tile: the ring is idle and can hold `red`.
-      // (An aborted or empty segment has nothing in flight either.)
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        float l = run_l[nt];
-#pragma unroll
-        for (int off = 4; off < 32; off <<= 1) l += __shfl_xor_sync(kFull, l, off);
-        const int h = 4 * nt + t;
-        if (g == 0) { lred[rw * 8 + h] = l; mred[rw * 8 + h] = run_m[nt]; }
-        float* w = red + rw * 1024 + h * 128;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          w[16 * i + g] = run_o[nt][i][0];
-          w[16 * i + g + 8] = run_o[nt][i][1];
-        }
-      }
-    }
-
-#ifdef FFA_WS_PROFILE
-    prof_role += static_cast<uint32_t>(clock()) - prof_seg0;
-    const uint32_t prof_a = static_cast<uint32_t>(clock());
-#endif
-    bar_sync(0, kWsThreads);               // A: every role is done with the segment's pipeline
-
-    if (role == kRoleRefine && rw < 4) {
-      // ---- segment epilogue (128 threads): add the refine warps' shares, write one partial ----------
-      const int ftid = rw * 32 + lane;
-      const bool bad = *reinterpret_cast<volatile int*>(sAbort) != 0;
-      const float qnan = __int_as_float(0x7fc00000);
-      for (int h = 0; h < G; ++h) {
+      const uint32_t mpar = seg_i & 1u;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rfmeet(0));
+      if (ok) ok = WS_WAIT(rfmeet(0), mpar, 14, 4);
+      // heads rw, rw + 4: sum over the warps, rescaled to the common maximum
+      const bool bad = !ok || *reinterpret_cast<volatile int*>(sAbort) != 0;
+      for (int h = rw; h < G; h += kNR) {
         float top = -INFINITY;
 #pragma unroll
-        for (int r = 0; r < kNR; ++r) top = fmaxf(top, mred[r * 8 + h]);
-        float o = 0.f;
+        for (int r = 0; r < kNR; ++r) top = fmaxf(top, redml[r * 16 + h]);
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        float l = 0.f;
 #pragma unroll
         for (int r = 0; r < kNR; ++r) {
-          const float mr = mred[r * 8 + h];
-          if (mr != -INFINITY) o += red[r * 1024 + h * 128 + ftid] * exp2f(mr - top);
+          const float mr = redml[r * 16 + h];
+          if (mr != -INFINITY) {
+            const float sc = exp2f(mr - top);
+            const float4 v = *reinterpret_cast<const float4*>(red + r * (L::kRedWarp / 4) + h * 128 + 4 * lane);
+            o.x += v.x * sc; o.y += v.y * sc; o.z += v.z * sc; o.w += v.w * sc;
+            l += redml[r * 16 + 8 + h] * sc;
+          }
         }
-        p.part_o[((row0 + h) * p.nch + part) * kHeadDim + ftid] = bad ? qnan : o;
-      }
-      if (ftid < G) {
-        float top = -INFINITY, l = 0.f;
-#pragma unroll
-        for (int r = 0; r < kNR; ++r) top = fmaxf(top, mred[r * 8 + ftid]);
-#pragma unroll
-        for (int r = 0; r < kNR; ++r) {
-          const float mr = mred[r * 8 + ftid];
-          if (mr != -INFINITY) l += lred[r * 8 + ftid] * exp2f(mr - top);
-        }
-        p.part_m[(row0 + ftid) * p.nch + part] = bad ? 0.f : top;
-        p.part_l[(row0 + ftid) * p.nch + part] = bad ? qnan : l;
-        if (MV) {
-          p.part_pm[(row0 + ftid) * p.nch + part] = (bad || n == 0) ? -INFINITY : sApx[ftid];
-          p.part_pl[(row0 + ftid) * p.nch + part] = bad ? qnan : (n == 0 ? 0.f : sApx[8 + ftid]);
+        // a chunk whose waits gave up publishes NaN, so that the merged rows are NaN rather than plausible numbers
+        if (bad) { o = make_float4(qnan, qnan, qnan, qnan); l = qnan; top = 0.f; }
+        *reinterpret_cast<float4*>(p.part_o + ((row0 + h) * p.nch + part) * kHeadDim + 4 * lane) = o;
+        if (lane == 0) {
+          p.part_m[(row0 + h) * p.nch + part] = top;
+          p.part_l[(row0 + h) * p.nch + part] = l;
         }
       }
-      if (p.mask && page_begin + n_pad == NPp) {
-        // mask entries past the last group that holds tokens (padding blocks count as pruned)
-        for (int i = (p.NP + m_grp - 1) / m_grp + ftid; i < p.NTBS; i += 128)
-          p.mask[(static_cast<int64_t>(b) * p.HKV + hkv) * p.NTBS + i] = 0;
-      }
-
-      // ---- merge by the last segment of this (b, kv-head) to finish (stage 2, ...q2fp8.py:142-171) ---
-      const int n_seg = static_cast<int>((unit0 + NPp - 1) / p.ppc - unit0 / p.ppc) + 1;
       __threadfence();
-      bar_sync(2, 128);
-      if (ftid == 0) {
-        const int prev = atomicAdd(p.arrivals + unit, 1);
-        *sFlag = (prev == n_seg - 1);
-        if (prev == n_seg - 1) p.arrivals[unit] = 0;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rfmeet(1));
+      if (ok) ok = WS_WAIT(rfmeet(1), mpar, 15, 4);      // every head's partial is written; `red` may be reused
+      if (rw == 0) {
+        const bool last = ws_arrive_unit(p, unit, arrive_target, lane);
+        if (lane == 0) *sLast = last ? 1 : 0;
+        __syncwarp();
       }
-      bar_sync(2, 128);
-      if (*sFlag) {
-        __threadfence();
-        float* sm_m = red;                  // [8][64]
-        float* sm_l = red + 8 * 64;         // [8][64], then mean-V: pm [8][64], pl [8][64]
-        const int per_head = n_seg;         // <= 64 by construction of the page ranges
-        for (int idx = ftid; idx < G * per_head; idx += 128) {
-          const int h = idx / per_head, i = idx % per_head;
-          sm_m[h * 64 + i] = __ldcg(p.part_m + (row0 + h) * p.nch + i);
-          sm_l[h * 64 + i] = __ldcg(p.part_l + (row0 + h) * p.nch + i);
-          if (MV) {
-            sm_l[8 * 64 + h * 64 + i] = __ldcg(p.part_pm + (row0 + h) * p.nch + i);
-            sm_l[16 * 64 + h * 64 + i] = __ldcg(p.part_pl + (row0 + h) * p.nch + i);
-          }
-        }
-        bar_sync(2, 128);
-        for (int h = rw; h < G; h += 4) {
-          const int64_t row = row0 + h;
-          float top = -INFINITY;
-          for (int i = 0; i < per_head; ++i)
-            if (sm_l[h * 64 + i] != 0.f) top = fmaxf(top, sm_m[h * 64 + i]);
-          float acc = 0.f;
-          float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int i0 = 0; i0 < per_head; i0 += 8) {
-            float4 v[8];
-            float w[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int i = i0 + j;
-              const bool live = i < per_head && sm_l[h * 64 + i] != 0.f && sm_m[h * 64 + i] != -INFINITY;
-              w[j] = live ? exp2f(sm_m[h * 64 + i] - top) : 0.f;
-              v[j] = live ? __ldcg(reinterpret_cast<const float4*>(p.part_o + (row * p.nch + i) * kHeadDim) + lane)
-                          : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int i = i0 + j;
-              if (i < per_head && sm_l[h * 64 + i] != 0.f) acc += sm_l[h * 64 + i] * w[j];
-              o.x += v[j].x * w[j]; o.y += v[j].y * w[j]; o.z += v[j].z * w[j]; o.w += v[j].w * w[j];
-            }
-          }
-          if (MV) {
-            // fold the pruned pages in: mass x mean of V (...meanv_bsz_q2fp8.py:188-200)
-            const float* sm_pm = sm_l + 8 * 64;
-            const float* sm_pl = sm_l + 16 * 64;
-            float p_top = -INFINITY, p_acc = 0.f;
-            for (int i = 0; i < per_head; ++i)
-              if (sm_pl[h * 64 + i] != 0.f) p_top = fmaxf(p_top, sm_pm[h * 64 + i]);
-            for (int i = 0; i < per_head; ++i)
-              if (sm_pl[h * 64 + i] != 0.f) p_acc += sm_pl[h * 64 + i] * exp2f(sm_pm[h * 64 + i] - p_top);
-            if (acc > 0.f || p_acc > 0.f) {
-              const float nm = fmaxf(top, p_top);
-              const float rb = acc > 0.f ? exp2f(top - nm) : 0.f, rp = p_acc > 0.f ? exp2f(p_top - nm) : 0.f;
-              const int64_t ve = (static_cast<int64_t>(b) * p.HKV + hkv) * kHeadDim + 4 * lane;
-              const float wv = p_acc * rp;
-              const int vd = p.v_bf16 ? FFA_BF16 : FFA_F16;
-              o.x = o.x * rb + load_as_float(p.v_mean, ve, vd) * wv;
-              o.y = o.y * rb + load_as_float(p.v_mean, ve + 1, vd) * wv;
-              o.z = o.z * rb + load_as_float(p.v_mean, ve + 2, vd) * wv;
-              o.w = o.w * rb + load_as_float(p.v_mean, ve + 3, vd) * wv;
-              acc = acc * rb + wv;
-            }
-          }
-          // a NaN mass marks a segment whose waits gave up: the head's output is NaN, not a guess
-          const float inv = acc == 0.f ? 0.f : 1.f / acc;
-          const float r0 = o.x * inv, r1 = o.y * inv, r2 = o.z * inv, r3 = o.w * inv;
-          const int64_t e = row * kHeadDim + 4 * lane;
-          if (p.out) {
-            store_from_float(p.out, e, p.q_dtype, r0);
-            store_from_float(p.out, e + 1, p.q_dtype, r1);
-            store_from_float(p.out, e + 2, p.q_dtype, r2);
-            store_from_float(p.out, e + 3, p.q_dtype, r3);
-          }
-          if (p.partial_out) {
-            float* po = p.partial_out + row * (kHeadDim + 1);
-            po[4 * lane] = r0; po[4 * lane + 1] = r1; po[4 * lane + 2] = r2; po[4 * lane + 3] = r3;
-            if (lane == 0) po[kHeadDim] = acc == 0.f ? -INFINITY : top + log2f(acc);
-          }
-        }
-      }
+      if (lane == 0) mbar_arrive(rfmeet(2));
+      if (ok) ok = WS_WAIT(rfmeet(2), mpar, 16, 4);
+      if (ok && *reinterpret_cast<volatile int*>(sLast) != 0) ws_merge_unit<MV>(p, b, hkv, n_seg, rw, kNR, lane);
+      if (!ok) break;
     }
-
-    bar_sync(0, kWsThreads);               // B: the coarse ring may be refilled
-#ifdef FFA_WS_PROFILE
-    prof_epi += static_cast<uint32_t>(clock()) - prof_a;
-#endif
-    if (active) { gc += static_cast<uint32_t>(n); ++act_ord; }
   }
+
+  __syncthreads();
 #ifdef FFA_WS_PROFILE
   // 64-bit sums over all CTAs, kept in the middle of the arrival-counter block (byte 32768 of the
-  // workspace; profiling builds serve at most 8192 (batch x kv-head) units): [role * 8 + i] = pacc[i] of the role's
-  // warps (i < 6), [role * 8 + 6] = the role's pipeline cycles, [role * 8 + 7] = cycles between the two
-  // segment barriers; [32] = kernel cycles of a CTA, [33] = its nanoseconds, [34] = the longest CTA's ns.
-  //   coarse producer: 0 wait for a free coarse slot
-  //   dispatcher:      0 thresholds, 1 published page, 2 free residual+V slot, 3 kept-page branch
-  //   scoring:         0 sample tile, 1 coarse tile, 2 free entry, 3 dots, 4 publish, 5 pages
-  //   refine:          0 residual+V landed, 1 page work, 2 pages
+  // workspace; profiling builds serve at most 8192 (batch x kv-head) units): [role * 8 + i] = pacc[i]
+  // of the role's warps (i < 6); [32] = kernel cycles of a CTA, [33] = its nanoseconds, [34] = the
+  // longest CTA's ns.
+  //   coarse producer: 0 wait for a free coarse slot, 1 free chunk entry, 2 free sample slot
+  //   dispatcher:      0 thresholds, 1 published page, 2 free residual+V slot, 3 kept-page branch, 5 next chunk
+  //   scoring:         0 sample tile, 1 coarse tile, 2 free entry, 3 dots, 4 publish, 5 next chunk
+  //   refine:          0 residual+V landed, 1 page work, 2 pages, 4 chunk-end meetings, 5 next chunk
   if (p.arrivals) {
     unsigned long long* gp = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.arrivals) + 32768);
     if (lane == 0) {
       for (int i = 0; i < 6; ++i) atomicAdd(gp + role * 8 + i, static_cast<unsigned long long>(pacc[i]));
-      atomicAdd(gp + role * 8 + 6, static_cast<unsigned long long>(prof_role));
-      atomicAdd(gp + role * 8 + 7, static_cast<unsigned long long>(prof_epi));
     }
     if (tid == 0) {
       unsigned long long g1;
@@ -992,16 +1082,29 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
       atomicAdd(gp + 32, static_cast<unsigned long long>(clock64() - prof_c0));
       atomicAdd(gp + 33, g1 - prof_g0);
       atomicMax(gp + 34, g1 - prof_g0);
+      // per CTA: SM id, start and end time (ns), from byte 36864 of the workspace on
+      unsigned long long* pc = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.arrivals) + 36864) + 3 * blockIdx.x;
+      uint32_t smid;
+      asm volatile("mov.u32 %0, %%smid;\n" : "=r"(smid));
+      pc[0] = smid; pc[1] = prof_g0; pc[2] = g1;
     }
   }
 #endif
-  if (tid == 0 && *sAbort != 0 && p.status && atomicCAS(p.status, 0, 1) == 0) {
-    p.status[1] = *sAbort;                 // which wait gave up first in this CTA
-    p.status[5] = static_cast<int>(blockIdx.x);
+  if (tid == 0) {
+    if (*sAbort != 0 && p.status && atomicCAS(p.status, 0, 1) == 0) {
+      p.status[1] = *sAbort;                 // which wait gave up first in this CTA
+      p.status[5] = static_cast<int>(blockIdx.x);
+    }
+    // the last CTA to leave puts the work counter back to zero for the next launch
+    __threadfence();
+    if (atomicAdd(p.work + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      p.work[0] = 0;
+      p.work[1] = 0;
+    }
   }
 }
 
-// Launches the kernel, or (stream == kWsQueryOnly) only configures it.
+// Configures (once per device) and launches the kernel.
 template <int FMT, int F8, int NT, bool VBF, int QP, bool MV = false>
 int launch_ws_one(const DecodeParams& p, const CUtensorMap* maps, cudaStream_t stream) {
   using L = WsSmem<FMT, NT>;
@@ -1015,9 +1118,7 @@ int launch_ws_one(const DecodeParams& p, const CUtensorMap* maps, cudaStream_t s
     if (e != cudaSuccess) return note_cuda_error(e, "cudaFuncSetAttribute(decode_ws)");
     if (slot) configured[dev] = true;
   }
-  const int64_t total_pages = static_cast<int64_t>(p.B) * p.HKV * p.NPp;
-  const unsigned grid = static_cast<unsigned>((total_pages + p.ppc - 1) / p.ppc);
-  kern<<<grid, kWsThreads, L::kBytes, stream>>>(p, maps[0], maps[1], maps[2], maps[3]);
+  kern<<<static_cast<unsigned>(p.grid), kWsThreads, L::kBytes, stream>>>(p, maps[0], maps[1], maps[2], maps[3]);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? FFA_OK : note_cuda_error(e, "decode_ws launch");
 }

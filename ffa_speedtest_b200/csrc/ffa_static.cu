@@ -21,6 +21,9 @@
 //     everything else is overwritten before it is read.
 //     Two calls whose kernels overlap on the GPU (different streams without an ordering between
 //     them, or concurrent host threads on one device) would race on the array: serialise them.
+//   * the status word a kernel sets when one of its bounded waits gave up (the outputs of the heads it
+//     touched are then NaN) lives in that array too and is cleared by the next call: a caller that
+//     wants to see it enqueues ffa_static_scratch_status() right after the decode call;
 //   * no cudaMalloc, cudaFree or other allocating routine is called, here or in ffa_decode().
 #include <mutex>
 
@@ -74,4 +77,18 @@ extern "C" int ffa_decode_static_scratch(const FfaDecodeArgs* args, ffa_stream_t
   local.workspace = scratch;
   local.workspace_bytes = need;
   return ffa_decode(&local, stream);
+}
+
+
+// Copies the status block of the last ffa_decode_static_scratch() call on the current device (seven
+// ints: [0] = 1 if a bounded wait gave up, then where) to `out`, which may be device memory or pinned
+// host memory; enqueued on `stream`, so it reads what the decode call before it on that stream left.
+extern "C" int ffa_static_scratch_status(int32_t* out, ffa_stream_t stream) {
+  if (!out) return FFA_E_NULL;
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != FFA_OK) return rc;
+  cudaError_t e = cudaMemcpyAsync(out, static_cast<unsigned char*>(scratch) + 64 * 1024 - 256, 7 * sizeof(int32_t),
+                                  cudaMemcpyDefault, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FFA_OK : ffa::note_cuda_error(e, "cudaMemcpyAsync(static scratch status)");
 }

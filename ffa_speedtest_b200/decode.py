@@ -130,12 +130,25 @@ def _fp8_format(*tensors) -> int:
             continue
         if t.dtype not in (torch.float8_e5m2, torch.float8_e4m3fn):
             raise ValueError(
-                f"this build reads fp8 (float8_e5m2 / float8_e4m3fn) K base and residual tensors, got {t.dtype}")
+                f"this build reads fp8 (float8_e5m2 / float8_e4m3fn) K base tensors, got {t.dtype}")
         code = _lib.fp8_code(t.dtype)
         if fmt is not None and fmt != code:
             raise ValueError("fp8 K base and residual must use the same fp8 encoding")
         fmt = code
     return _lib.E5M2 if fmt is None else fmt
+
+
+def _residual_as_fp8(k_residual: torch.Tensor, like: Optional[torch.dtype]) -> torch.Tensor:
+    """The kernels read the residual as fp8.  The reference also takes float16 / bfloat16 / float32
+    residuals (its kernel casts whatever it gets to float16, ...q2fp8.py:110-114; its quantisers fall back
+    to float16 on a torch without fp8 types, fused_kproj_rope_q2fp8.py:81-88): those are rounded to fp8
+    here, to the encoding of the fp8 base when there is one and to e5m2 (float16's exponent range)
+    otherwise - a conversion pass per call, meant for compatibility and not for speed."""
+    if k_residual.dtype in (torch.float8_e5m2, torch.float8_e4m3fn):
+        return k_residual
+    if k_residual.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise ValueError(f"k_residual must be fp8, float16, bfloat16 or float32, got {k_residual.dtype}")
+    return k_residual.to(like if like is not None else torch.float8_e5m2)
 
 
 def decode_call(
@@ -209,6 +222,8 @@ def decode_call(
     NTBS = NTB * (BS // SBS)
 
     use_res = bool(use_fp8_residual and k_residual is not None)
+    if use_res:
+        k_residual = _residual_as_fp8(k_residual, k_codes.dtype if variant == "fp8" else None)
     fp8_fmt = _fp8_format(k_codes if variant == "fp8" else None, k_residual if use_res else None)
 
     if precomputed_threshold is not None:

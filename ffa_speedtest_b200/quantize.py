@@ -98,3 +98,27 @@ def encode_k_nvfp4_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype, page_si
     _lib.check(_lib.lib().ffa_quantize_nvfp4(k.data_ptr(), dt, B, T, HKV, f8, page_size, codes.data_ptr(),
                                              scale.data_ptr(), res.data_ptr(), st), "ffa_quantize_nvfp4")
     return codes, scale, res
+
+
+# variant directory name of the reference -> short name of its coarse-K format
+VARIANTS = {"fp8fp8": "fp8", "q2fp8": "q2", "fp4fp8": "fp4", "nf4fp8": "nf4", "nvfp4fp8": "nvfp4"}
+
+
+def quantize_variant(kind: str, k: torch.Tensor, fp8_dtype: torch.dtype, page_size: int = 64):
+    """``(codes, scale, zero, residual)`` of K in the format ``kind`` (a value of ``VARIANTS``); the
+    parts a format does not have are ``None``."""
+    if kind == "fp8":
+        c, r = quantize_k_fp8_fp8_residual(k, fp8_dtype)
+        return c, None, None, r
+    if kind == "q2":
+        return quantize_k_2bit_fp8_residual(k, fp8_dtype)
+    if kind == "fp4":
+        c, r = encode_k_fp4_fp8_residual(k, fp8_dtype)
+        return c, None, None, r
+    if kind == "nf4":
+        c, s, r = encode_k_nf4_fp8_residual(k, fp8_dtype)
+        return c, s, None, r
+    if kind == "nvfp4":
+        c, s, r = encode_k_nvfp4_fp8_residual(k, fp8_dtype, page_size)
+        return c, s, None, r
+    raise ValueError(f"unknown coarse-K format {kind!r}")

@@ -2,6 +2,8 @@
 
     python -m ffa_speedtest_b200.run_attn_bench --variant q2fp8 --dtype fp16 --BS 128 --SBS 128 \
         --delta 5 --bsz 1 --max-length 32768 --step 4096 --iters 100 --warmup 50
+    python -m ffa_speedtest_b200.run_attn_bench --variant q2fp8 --cudagraph --cg-warmup 2 ...
+    python -m ffa_speedtest_b200.run_attn_bench --variant q2fp8 --kernel some.module.path ...
 
 The reference drivers (ffa-q2fp8/run_attn_bench_q2.py:33-60 for the arguments, :208-262 for the
 per-length measurement, utils/cache.py:36-58 for the result file) sweep a recorded Llama layer over
@@ -10,26 +12,74 @@ store ``{"meta", "lengths", "fused_ms", "flash_ms", "skip_ratios"}`` as JSON.  T
 arguments, the measurement protocol (CUDA events around ``iters`` calls after ``warmup`` calls) and
 the result schema, on seeded synthetic activations (the recordings are not available): ``--layer``
 selects the seed and ``--bsz`` the batch.  The dense column is torch's scaled-dot-product attention
-on the unquantised K (``--no-dense`` leaves it out).
+on the unquantised K (``--no-flash`` leaves it out, like the reference's flag of that name).
+
+``--kernel`` is the reference's plug-in point (run_attn_bench_q2.py:34-39, 108-113): a Python module
+path that exports the variant's entry point (``attn_forward_decode_quantized`` for q2fp8, ...); it
+is imported and called with the reference's keyword arguments.  The default is this package's
+module for the variant.
+
+``--cudagraph`` is the reference's second driver (run_attn_bench_q2_cudagraph.py): each length is
+timed eagerly and through the variant's ``CUDAGraphDecodeRunner*`` (``replay_only()`` unless
+``--cg-with-copies``), and the result file holds ``{"meta", "lengths", "<v>_ms", "<v>_cg_ms",
+"flash_ms", "skip_ratios"}`` with the reference's key prefix per variant (:148-173 there) and its
+``_cudagraph_replay`` / ``_cudagraph`` file-name suffix.
 """
 from __future__ import annotations
 
 import argparse
+import importlib
 import json
 import math
 from pathlib import Path
 
 import torch
 
-from .decode import decode_call
-from .run_case import KINDS, quantise
+from .quantize import VARIANTS, quantize_variant
 from .synth import make_decode_inputs
 
-DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16}
+DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}
+# variant -> (entry point, runner class, key prefix of the cudagraph result file)
+ENTRY = {
+    "q2fp8": ("attn_forward_decode_quantized", "CUDAGraphDecodeRunnerQ2FP8", "q2"),
+    "fp8fp8": ("attn_forward_decode_fp8fp8", "CUDAGraphDecodeRunnerFP8FP8", "fp8"),
+    "fp4fp8": ("attn_forward_decode_fp4", "CUDAGraphDecodeRunnerFP4FP8", "fp4"),
+    "nf4fp8": ("attn_forward_decode_nf4", "CUDAGraphDecodeRunnerNF4FP8", "nf4"),
+    "nvfp4fp8": ("attn_forward_decode_nvfp4fp8", "CUDAGraphDecodeRunnerNVFP4FP8", "nvfp4"),
+}
+
+
+def default_kernel(variant: str) -> str:
+    return f"ffa_speedtest_b200.{variant}.attn_kernel.attn_kernel_v1210_fused_bsz_{variant}"
+
+
+def load_kernel_components(kernel_path: str, variant: str):
+    """The entry point of ``kernel_path`` for the variant (reference run_attn_bench_q2.py:108-113)."""
+    module = importlib.import_module(kernel_path)
+    name = ENTRY[variant][0]
+    if not hasattr(module, name):
+        raise AttributeError(f"Module {kernel_path} does not define '{name}'")
+    return module, getattr(module, name)
+
+
+def load_runner(kernel_path: str, variant: str):
+    """The CUDA-graph runner class that sits next to the kernel module (``<module>_cudagraph``)."""
+    module = importlib.import_module(kernel_path + "_cudagraph")
+    return getattr(module, ENTRY[variant][1])
+
+
+def k_args(kind: str, codes, scale, zero):
+    """Positional K tensors of the variant's call, between q and v."""
+    if kind == "q2":
+        return [codes, scale, zero]
+    if kind in ("nf4", "nvfp4"):
+        return [codes, scale]
+    return [codes]
 
 
 def benchmark(fn, iters: int, warmup: int) -> float:
-    """Milliseconds per call: CUDA events around ``iters`` calls after ``warmup`` calls."""
+    """Milliseconds per call: CUDA events around ``iters`` calls after ``warmup`` calls
+    (the reference's utils/bench.py:7-20)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -49,7 +99,8 @@ def to_k(n: int) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--variant", default="q2fp8", choices=sorted(KINDS))
+    ap.add_argument("--variant", default="q2fp8", choices=sorted(VARIANTS))
+    ap.add_argument("--kernel", default=None, help="Python module path of the variant's decode entry point")
     ap.add_argument("--dtype", default="fp16", choices=sorted(DTYPES))
     ap.add_argument("--BS", type=int, default=128)
     ap.add_argument("--SBS", type=int, default=None)
@@ -61,7 +112,14 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--fp8", default="e5m2", choices=["e5m2", "e4m3"])
-    ap.add_argument("--no-dense", action="store_true")
+    ap.add_argument("--no-flash", "--no-dense", dest="no_flash", action="store_true", help="skip the dense baseline")
+    ap.add_argument("--cudagraph", action="store_true", help="also time the CUDA-graph runner (second reference driver)")
+    ap.add_argument("--cg-warmup", type=int, default=2, help="CUDAGraph warmup calls before capture")
+    ap.add_argument("--cg-replay-only", action="store_true", default=True,
+                    help="measure CUDAGraph replay time only (the reference's default)")
+    ap.add_argument("--cg-with-copies", dest="cg_replay_only", action="store_false",
+                    help="time runner(...) including the copies into its static buffers")
+    ap.add_argument("--no-plot", action="store_true", help="accepted for compatibility: this driver never plots")
     ap.add_argument("--out-dir", default="plot_attn_bench/raw")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -70,46 +128,73 @@ def main() -> None:
     dtype = DTYPES[args.dtype]
     f8 = {"e5m2": torch.float8_e5m2, "e4m3": torch.float8_e4m3fn}[args.fp8]
     BS, SBS = args.BS, args.SBS or args.BS
-    kind = KINDS[args.variant]
+    kind = VARIANTS[args.variant]
+    kernel_path = args.kernel or default_kernel(args.variant)
+    _, entry = load_kernel_components(kernel_path, args.variant)
+    Runner = load_runner(kernel_path, args.variant) if args.cudagraph else None
     HQ, HKV, D = 32, 8, 128
     T_full = args.max_length
-    q_all, k_all, v_all = make_decode_inputs(args.bsz, T_full, HQ, HKV, D, seed=args.layer, device=dev, dtype=dtype)
+    # V (and the K that is quantised) are 16-bit like the reference's recordings; --dtype fp32 only
+    # changes q, which the kernels round to float16 as the reference's do
+    kv_dtype = torch.float16 if dtype == torch.float32 else dtype
+    q_all, k_all, v_all = make_decode_inputs(args.bsz, T_full, HQ, HKV, D, seed=args.layer, device=dev, dtype=kv_dtype)
+    q_all = q_all.to(dtype)
     sm_scale = 1.0 / math.sqrt(D)
     lengths = list(range(args.step, T_full, args.step)) + [T_full]
+    bits = {} if kind == "fp8" else {"k_bits": 2 if kind == "q2" else 4}
 
-    fused_ms, dense_ms, skip_ratios = [], [], []
+    fused_ms, cg_ms, dense_ms, skip_ratios = [], [], [], []
     for L in lengths:
         k, v = k_all[:, :L].contiguous(), v_all[:, :L].contiguous()
-        codes, scale, zero, res = quantise(kind, k, f8, BS)
+        codes, scale, zero, res = quantize_variant(kind, k, f8, BS)
+        kt = k_args(kind, codes, scale, zero)
+        kw = dict(k_residual=res, scale=sm_scale, BS=BS, SBS=SBS, delta=args.delta, **bits)
 
         def run():
-            return decode_call(kind, q_all, codes, v, k_scale=scale, k_zero=zero, k_residual=res, scale=sm_scale,
-                               BS=BS, SBS=SBS, delta=args.delta)
+            return entry(q_all, *kt, v, return_skip_ratio=False, **kw)
 
-        _, skip = decode_call(kind, q_all, codes, v, k_scale=scale, k_zero=zero, k_residual=res, scale=sm_scale,
-                              BS=BS, SBS=SBS, delta=args.delta, return_skip_ratio=True)
+        _, skip = entry(q_all, *kt, v, return_skip_ratio=True, **kw)
         fused_ms.append(benchmark(run, args.iters, args.warmup))
         skip_ratios.append(skip)
-        if args.no_dense:
-            dense_ms.append(float("nan"))
+        if Runner is not None:
+            runner = Runner(q_all, *kt, v, use_fp8_residual=True, warmup=args.cg_warmup, **kw)
+            if args.cg_replay_only:
+                cg_ms.append(benchmark(runner.replay_only, args.iters, args.warmup))
+            else:
+                cg_ms.append(benchmark(lambda: runner(q_all, *kt, v, k_residual=res), args.iters, args.warmup))
+            del runner
+        if args.no_flash:
+            dense_ms.append(None)
         else:
-            qd = q_all.transpose(1, 2)                                   # [B, HQ, 1, D]
+            qd = q_all.to(kv_dtype).transpose(1, 2)                      # [B, HQ, 1, D]
             kd, vd = k.transpose(1, 2), v.transpose(1, 2)                # [B, HKV, L, D]
             dense_ms.append(benchmark(
                 lambda: torch.nn.functional.scaled_dot_product_attention(qd, kd, vd, scale=sm_scale, enable_gqa=True),
                 args.iters, args.warmup))
-        print(f"L={to_k(L):>6}  fused {fused_ms[-1] * 1e3:8.1f} us  dense {dense_ms[-1] * 1e3:8.1f} us  "
-              f"skip {skip:.3f}", flush=True)
+        line = f"L={to_k(L):>6}  fused {fused_ms[-1] * 1e3:8.1f} us"
+        if cg_ms:
+            line += f"  cudagraph {cg_ms[-1] * 1e3:8.1f} us"
+        if dense_ms[-1] is not None:
+            line += f"  dense {dense_ms[-1] * 1e3:8.1f} us"
+        print(line + f"  skip {skip:.3f}", flush=True)
 
     meta = dict(layer_indices=[args.layer], T_full=T_full, Hq=HQ, Hkv=HKV, D=D, Dv=D, BS=BS, SBS=SBS,
                 delta=args.delta, dtype=args.dtype, step=args.step, iters=args.iters, warmup=args.warmup,
-                attn_kernel=f"ffa_speedtest_b200.{args.variant}", bsz=args.bsz, data="synthetic", fp8=args.fp8)
-    name = (f"layer_{args.layer}_Tmax{to_k(T_full)}_Hq{HQ}_Hkv{HKV}_D{D}_Dv{D}_BS{BS}_SBS{SBS}_delta{args.delta:g}_"
-            f"{args.dtype}_step{args.step}_it{args.iters}_wu{args.warmup}_bsz{args.bsz}.json")
-    path = Path(args.out_dir) / args.variant / name
+                attn_kernel=kernel_path, bsz=args.bsz, data="synthetic", fp8=args.fp8)
+    stem = (f"layer_{args.layer}_Tmax{to_k(T_full)}_Hq{HQ}_Hkv{HKV}_D{D}_Dv{D}_BS{BS}_SBS{SBS}_delta{args.delta:g}_"
+            f"{args.dtype}_step{args.step}_it{args.iters}_wu{args.warmup}_bsz{args.bsz}")
+    if args.cudagraph:
+        prefix = ENTRY[args.variant][2]
+        meta["cudagraph_replay_only"] = bool(args.cg_replay_only)
+        payload = {"meta": meta, "lengths": lengths, f"{prefix}_ms": fused_ms, f"{prefix}_cg_ms": cg_ms,
+                   "flash_ms": dense_ms, "skip_ratios": skip_ratios}
+        stem += "_cudagraph_replay" if args.cg_replay_only else "_cudagraph"
+    else:
+        payload = {"meta": meta, "lengths": lengths, "fused_ms": fused_ms,
+                   "flash_ms": [float("nan") if x is None else x for x in dense_ms], "skip_ratios": skip_ratios}
+    path = Path(args.out_dir) / args.variant / (stem + ".json")
     path.parent.mkdir(parents=True, exist_ok=True)
-    path.write_text(json.dumps({"meta": meta, "lengths": lengths, "fused_ms": fused_ms, "flash_ms": dense_ms,
-                                "skip_ratios": skip_ratios}, indent=2))
+    path.write_text(json.dumps(payload, indent=2))
     print(f"saved {path}")
 
 

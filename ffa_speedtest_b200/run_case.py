@@ -3,10 +3,10 @@
     python -m ffa_speedtest_b200.run_case decode --variant fp8fp8 --B 2 --T 32768 --iters 3
     python -m ffa_speedtest_b200.run_case kproj  --variant q2fp8  --T 8192 --iters 3
 
-A small, self-contained driver for profilers and quick checks: it builds the seeded inputs,
-quantises K with this package's quantisers, calls the public entry point ``iters`` times and
-prints the kept-page fraction (decode) or the output shapes (kproj).  Sizes are whatever is
-asked for; pick a case a profiler can replay (a few hundred MB of cache).
+The command behind the profiler captures of this package (their summaries quote it): it builds the
+seeded inputs, quantises K with this package's quantisers, calls the public entry point ``iters``
+times and prints the kept-page fraction (decode) or the output shapes (kproj).  Sizes are whatever
+is asked for; for a profiler pick a case it can replay (a few hundred MB of cache).
 """
 from __future__ import annotations
 
@@ -19,25 +19,8 @@ from .decode import allocate_decode_workspace, decode_call
 from .kproj import build_rope_cache, kproj_fused
 from .synth import make_decode_inputs, make_kproj_inputs
 
-KINDS = {"fp8fp8": "fp8", "q2fp8": "q2", "fp4fp8": "fp4", "nf4fp8": "nf4", "nvfp4fp8": "nvfp4"}
-
-
-def quantise(kind: str, k: torch.Tensor, f8: torch.dtype, page: int):
-    """(codes, scale, zero, residual) of K in the variant's format (absent parts are None)."""
-    if kind == "fp8":
-        c, r = Q.quantize_k_fp8_fp8_residual(k, f8)
-        return c, None, None, r
-    if kind == "q2":
-        c, s, z, r = Q.quantize_k_2bit_fp8_residual(k, f8)
-        return c, s, z, r
-    if kind == "fp4":
-        c, r = Q.encode_k_fp4_fp8_residual(k, f8)
-        return c, None, None, r
-    if kind == "nf4":
-        c, s, r = Q.encode_k_nf4_fp8_residual(k, f8)
-        return c, s, None, r
-    c, s, r = Q.encode_k_nvfp4_fp8_residual(k, f8, page)
-    return c, s, None, r
+KINDS = Q.VARIANTS
+quantise = Q.quantize_variant
 
 
 def main() -> None:

@@ -104,16 +104,25 @@ class SequenceShardedDecode:
         import torch.distributed as dist
         self.dist, self.group = dist, group
         self.world = dist.get_world_size(group)
-        self.local = torch.empty((B, HQ, 129), dtype=torch.float32, device=device)
+        self.rank = dist.get_rank(group)
         self.gathered = torch.empty((self.world, B, HQ, 129), dtype=torch.float32, device=device)
+        # this rank's partial is written straight into its slot of the gathered buffer, so the
+        # all-gather runs in place (no staging copy of the send buffer)
+        self.local = self.gathered[self.rank]
         self.out = torch.empty((B, HQ, 128), dtype=out_dtype, device=device)
         # the CUDA merge kernel by default; CPU-rank tests of the protocol pass their own
         self._merge = merge_fn or (lambda parts, out: merge_partials(parts, out.dtype, out=out))
+
+    def gather(self) -> None:
+        """All-gather the partials: rank r's lands in ``gathered[r]`` on every rank."""
+        self.dist.all_gather_into_tensor(self.gathered.view(-1, *self.local.shape[1:]), self.local, group=self.group)
+
+    def merge(self) -> torch.Tensor:
+        return self._merge(self.gathered, self.out)
 
     def step(self, local_decode) -> torch.Tensor:
         """``local_decode(partial_out=...)`` must enqueue this rank's decode writing the partial
         ``[B, HQ, 129]`` (normalised output, base-2 LSE; LSE = -inf if the rank kept nothing)."""
         local_decode(partial_out=self.local)
-        # rank r's partial lands in gathered[r]; the flat view is the form every backend accepts
-        self.dist.all_gather_into_tensor(self.gathered.view(-1, *self.local.shape[1:]), self.local, group=self.group)
-        return self._merge(self.gathered, self.out)
+        self.gather()
+        return self.merge()

@@ -59,9 +59,8 @@ typedef struct FfaDecodeArgs {
   int32_t variant;          /* FFA_K_*                                                          */
   int32_t B, T, HQ, HKV;    /* batch, context length, query heads, kv heads (G = HQ/HKV <= 8)   */
   int32_t head_dim;         /* K = V = 128                                                      */
-  int32_t BS, SBS;          /* reference block sizes: SBS (prune granularity) a multiple of 64,
-                               BS a multiple of SBS.  SBS = 64 is one launch; a larger SBS runs a
-                               scoring pass, a group decision and the step (bf16 / fp16 q only)  */
+  int32_t BS, SBS;          /* reference block sizes: SBS (prune granularity) 64, 128, 256 or 512,
+                               BS a multiple of SBS; always one launch                           */
   float sm_scale;           /* softmax scale, reference default 1/sqrt(K)                       */
   float delta;              /* threshold offset in log2 units                                   */
   int32_t q_dtype;          /* FFA_F16 | FFA_BF16 | FFA_F32; the output has the same type       */
@@ -85,18 +84,25 @@ typedef struct FfaDecodeArgs {
                                base-2 log-sum-exp of the kept scores (-inf if none kept), the
                                form ffa_merge_partials consumes                                 */
   void* workspace;          /* >= ffa_decode_workspace_bytes(...) bytes, 256-byte aligned.  Its
-                               first 64 KiB must be zero before the first call; every call leaves
-                               them zero, except the int at byte 65280, which a kernel sets when
-                               one of its bounded waits gave up (the results are then invalid)  */
+                               first 64 KiB (per-(batch, kv-head) arrival counters) must be zero
+                               before the first call; every call that returns FFA_OK and runs to
+                               completion leaves them zero.  Zero them again (cudaMemsetAsync)
+                               after a call that failed or whose stream was torn down mid-kernel:
+                               with stale counters the merge of a (batch, kv-head) never runs and
+                               its output rows keep their old contents.  The int at byte 65280 is
+                               set by a kernel when one of its bounded waits gave up; the outputs
+                               of the heads it touched are then NaN                             */
   size_t workspace_bytes;
   int32_t pages_per_chunk;  /* 0 = choose automatically                                         */
-  int32_t reserved;         /* bit 0: use the fp16 tensor-core kernel even when the TMA/fp8 kernel
-                               applies (bf16 q); 0 otherwise                                    */
+  int32_t reserved;         /* 0: the warp-specialised TMA kernel.  Bit 0: the fp16 tensor-core kernel
+                               (the reference's rounding sequence to the letter; SBS = 64 only).
+                               Bit 1: the earlier TMA kernel (bf16 q, or fp16 q with fp16 V;
+                               SBS = 64 only)                                                   */
   int64_t kv_rows;          /* token rows in the K/V tensors: pages*64 of a pool, 0 = B*T       */
   const void* v_mean;       /* optional [B, HKV, 128] in V's type: the mean-V variant
                                (ffa-q2fp8-meanv/attn_kernel/attn_kernel_v1210_meanv_bsz_q2fp8.py): pruned
                                pages contribute their coarse softmax mass times this vector.  2-bit
-                               format, bf16 / fp16 q, no partial_out.  NULL = pruned pages are dropped */
+                               format, no partial_out.  NULL = pruned pages are dropped */
 } FfaDecodeArgs;
 
 /* Replaces attn_forward_decode_quantized / _fp8fp8 / _fp4 / _nf4 / _nvfp4fp8 after validation:
@@ -129,6 +135,13 @@ size_t ffa_static_scratch_bytes(void);
  * stream capture.  Calls on one device share the array: do not let two of them overlap on the GPU.
  * Allocates nothing. */
 int ffa_decode_static_scratch(const FfaDecodeArgs* args, ffa_stream_t stream);
+
+/* Status block of the last ffa_decode_static_scratch call on the current device: seven ints, [0] = 1
+ * when one of the kernel's bounded waits gave up (outputs of the affected heads are NaN), the rest
+ * say where.  `out` is device memory or pinned host memory; the copy is enqueued on `stream`, after
+ * the decode call whose status it reports.  The next ffa_decode_static_scratch call clears the block.
+ * No counterpart in the reference.  Allocates nothing. */
+int ffa_static_scratch_status(int32_t* out, ffa_stream_t stream);
 
 /* Merge R partial results (split-KV inside a GPU, or one per rank after an all-gather):
  * parts is [R, rows, 129] fp32 holding a normalised partial output (128) followed by its
@@ -201,7 +214,8 @@ size_t ffa_kproj_workspace_bytes(int32_t B, int32_t T, int32_t HKV, int32_t rope
 
 /* Text of the last CUDA runtime error seen by this library on the calling thread ("" if none). */
 const char* ffa_last_cuda_error(void);
-/* Library version, bumped when the ABI changes (2: FfaDecodeArgs ends in v_mean; FfaKprojArgs.slot_pos0). */
+/* Library version, bumped when the ABI changes (2: FfaDecodeArgs ends in v_mean; FfaKprojArgs.slot_pos0;
+ * 3: ffa_static_scratch_status, every SBS in one launch). */
 int ffa_abi_version(void);
 
 #ifdef __cplusplus

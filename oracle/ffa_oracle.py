@@ -246,8 +246,13 @@ def decode_attention(
     out_dtype: Optional[torch.dtype] = None,
     return_parts: bool = False,
     mean_v: Optional[torch.Tensor] = None,                  # [B, HKV, V]: the mean-V variant
+    keep_override: Optional[torch.Tensor] = None,           # [B, HKV, NTBS]: kept set imposed by the caller
 ):
     """Stage 1 + stage 2 of the reference decode path on CPU.
+
+    ``keep_override`` replaces the prune decision (the coarse maxima and thresholds are still
+    computed and returned): the tests use it to check an output whose kept set differs from the
+    reference's on pages that sit within the allowed band around a threshold.
 
     Returns ``o [B,HQ,V]`` (and, with ``return_parts``, a dict holding the kept mask
     ``[B,HKV,NTBS]`` int8, the thresholds ``[B,HQ]`` and the per-block coarse maxima
@@ -299,6 +304,8 @@ def decode_attention(
             m_c = s_c.amax(dim=-1)                       # [B,HKV,G]
             blk_max[..., idx] = m_c
             keep = ~((m_c < th).all(dim=-1))             # strict <, all heads of the group
+            if keep_override is not None:
+                keep = keep_override[..., idx].to(torch.bool)
             mask[..., idx] = keep.to(torch.int8)
             if mean_v is not None and not bool(keep.all()):
                 p_c = torch.where(live, torch.exp2(s_c - m_c.unsqueeze(-1)), torch.tensor(0.0))
@@ -351,12 +358,14 @@ def decode_attention(
 
 def decode_attention_fast(
     q, coarse: CoarseK, v, k_residual=None, *, sm_scale=None, BS=128, SBS=None, delta=5.0,
-    precomputed_threshold=None, use_fp8_residual=True, out_dtype=None,
+    precomputed_threshold=None, use_fp8_residual=True, out_dtype=None, keep_override=None, return_parts=False,
 ):
     """Same math as :func:`decode_attention`, batched over all sub-blocks at once
     (requires T % SBS == 0).  This is the torch-eager CPU baseline that ``bench.py``
     times; the merge uses one global maximum instead of the serial block order, which
-    changes results only in the last fp32 bits."""
+    changes results only in the last fp32 bits.  ``keep_override [B,HKV,N]`` imposes a kept
+    set; ``return_parts`` adds a dict with the thresholds ``[B,HQ]`` and the per-block coarse
+    maxima ``[B,HQ,N]`` to the returned tuple."""
     if q.dim() == 4:
         q = q[:, 0]
     B, HQ, K = q.shape
@@ -376,6 +385,8 @@ def decode_attention_fast(
     s_c = _scores(q16, k16, sm_scale).reshape(B, HKV, G, N, SBS)
     m_c = s_c.amax(dim=-1)                                               # [B,HKV,G,N]
     keep = ~((m_c < th.unsqueeze(-1)).all(dim=2))                        # [B,HKV,N]
+    if keep_override is not None:
+        keep = keep_override.to(torch.bool)
     bi, hi, ni = keep.nonzero(as_tuple=True)
     out = torch.zeros(B, HKV, G, V)
     if bi.numel():
@@ -397,7 +408,10 @@ def decode_attention_fast(
         acc = torch.zeros(B * HKV, G).index_add_(0, unit, l * w)
         osum = torch.zeros(B * HKV, G, V).index_add_(0, unit, ob * w.unsqueeze(-1))
         out = torch.where((acc == 0).unsqueeze(-1), torch.zeros_like(osum), osum / acc.unsqueeze(-1))
-    return out.reshape(B, HQ, V).to(out_dtype or q.dtype), keep.to(torch.int8)
+    out = out.reshape(B, HQ, V).to(out_dtype or q.dtype)
+    if return_parts:
+        return out, keep.to(torch.int8), {"threshold": th.reshape(B, HQ), "block_max": m_c.reshape(B, HQ, N)}
+    return out, keep.to(torch.int8)
 
 
 # --------------------------------------------------------------------------------------

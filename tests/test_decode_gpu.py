@@ -80,6 +80,13 @@ def test_against_reference_goldens(kind, name, kernel):
         err = check_output(o, c.o_ref)
         # far tighter than the tolerance when the kept sets agree: only accumulation order differs
         assert err <= 4e-3 * max(1.0, c.o_ref.abs().max().item())
+    else:
+        # the kept sets differ on pages inside the band: judge the output against the oracle run on
+        # the kept set the GPU used
+        o_ref = fo.decode_attention(c.q, coarse, c.v, res, BS=c.BS, SBS=c.SBS, delta=c.delta,
+                                    precomputed_threshold=c.th, use_fp8_residual=c.use_res, out_dtype=torch.float32,
+                                    keep_override=ws.mask.cpu())
+        check_output(o, o_ref)
 
 
 @pytest.mark.parametrize("kernel", ["auto", "fp16"])

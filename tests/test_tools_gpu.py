@@ -33,3 +33,25 @@ def test_run_case(what, variant):
     r = run("-m", "ffa_speedtest_b200.run_case", what, "--variant", variant, "--B", "1", "--T", "512", "--iters", "2")
     assert r.returncode == 0, r.stderr[-2000:]
     assert variant in r.stdout and ("status 0" in r.stdout or "outputs" in r.stdout)
+
+
+def test_run_attn_bench_cudagraph_schema_and_kernel_option(tmp_path):
+    """The second reference driver: eager and CUDA-graph columns under the variant's key prefix
+    (ffa-q2fp8/run_attn_bench_q2_cudagraph.py:148-173), with the kernel given as a module path."""
+    r = run("-m", "ffa_speedtest_b200.run_attn_bench", "--variant", "q2fp8", "--dtype", "fp16", "--BS", "128",
+            "--kernel", "ffa_speedtest_b200.q2fp8.attn_kernel.attn_kernel_v1210_fused_bsz_q2fp8", "--cudagraph",
+            "--cg-warmup", "1", "--no-flash", "--max-length", "4096", "--step", "2048", "--iters", "3", "--warmup", "1",
+            "--out-dir", str(tmp_path))
+    assert r.returncode == 0, r.stderr[-2000:]
+    files = list(tmp_path.rglob("*.json"))
+    assert len(files) == 1 and files[0].name.endswith("_bsz1_cudagraph_replay.json")
+    d = json.loads(files[0].read_text())
+    assert set(d) == {"meta", "lengths", "q2_ms", "q2_cg_ms", "flash_ms", "skip_ratios"}
+    assert d["lengths"] == [2048, 4096] and all(x > 0 for x in d["q2_ms"] + d["q2_cg_ms"])
+    assert d["flash_ms"] == [None, None] and d["meta"]["cudagraph_replay_only"] is True
+
+
+def test_run_attn_bench_rejects_a_module_without_the_entry_point(tmp_path):
+    r = run("-m", "ffa_speedtest_b200.run_attn_bench", "--variant", "fp8fp8", "--kernel", "ffa_speedtest_b200.synth",
+            "--max-length", "1024", "--out-dir", str(tmp_path))
+    assert r.returncode != 0 and "does not define 'attn_forward_decode_fp8fp8'" in r.stderr
