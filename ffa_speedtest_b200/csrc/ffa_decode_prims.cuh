@@ -135,13 +135,31 @@ __device__ __forceinline__ void load_fp8_rows(uint32_t (&ra)[8], uint32_t (&rb)[
   rb[0] = b0.x; rb[1] = b0.y; rb[2] = b0.z; rb[3] = b0.w; rb[4] = b1.x; rb[5] = b1.y; rb[6] = b1.z; rb[7] = b1.w;
 }
 
+// 16 token rows in GLOBAL memory (not a staged tile): row r of the block starts at base + r * stride;
+// rows >= valid read as zeros.  Used for the two 16-token threshold samples, which are read once.
+struct RowsRef {
+  const uint8_t* base;
+  int64_t stride;
+  int valid;
+};
+__device__ __forceinline__ void load_fp8_rows(uint32_t (&ra)[8], uint32_t (&rb)[8], const RowsRef& rows, int /*slice*/,
+                                              int g, int t) {
+  const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+  const uint4* rowA = reinterpret_cast<const uint4*>(rows.base + g * rows.stride) + 2 * t;
+  const uint4* rowB = reinterpret_cast<const uint4*>(rows.base + (g + 8) * rows.stride) + 2 * t;
+  const uint4 a0 = g < rows.valid ? __ldg(rowA) : z, a1 = g < rows.valid ? __ldg(rowA + 1) : z;
+  const uint4 b0 = g + 8 < rows.valid ? __ldg(rowB) : z, b1 = g + 8 < rows.valid ? __ldg(rowB + 1) : z;
+  ra[0] = a0.x; ra[1] = a0.y; ra[2] = a0.z; ra[3] = a0.w; ra[4] = a1.x; ra[5] = a1.y; ra[6] = a1.z; ra[7] = a1.w;
+  rb[0] = b0.x; rb[1] = b0.y; rb[2] = b0.z; rb[3] = b0.w; rb[4] = b1.x; rb[5] = b1.y; rb[6] = b1.z; rb[7] = b1.w;
+}
+
 // q . k for the warp's 16 tokens from raw fp8 K bytes and the e4m3 pieces of q.
 // out[nt][0] : token g, head 4nt+t;  out[nt][1] : token g+8, head 4nt+t   (unscaled dot products)
 // QP = 2 (bf16 q): one n-tile per four heads, columns 2t / 2t+1 = pieces hi / lo x16.
 // QP = 3 (fp16 q): a second n-tile per four heads whose column 2t is the third piece (x256).
-template <int F8, int NT, int QP>
+template <int F8, int NT, int QP, typename Tile = const uint8_t*>
 __device__ __forceinline__ void dot_fp8(float (&out)[NT][2], const uint32_t (&qb)[NT * (QP - 1)][4][2],
-                                        const float (&qinv)[NT], const uint8_t* tile, int warp, int g, int t) {
+                                        const float (&qinv)[NT], const Tile& tile, int warp, int g, int t) {
   uint32_t ra[8], rb[8];
   load_fp8_rows(ra, rb, tile, warp, g, t);
 #pragma unroll
@@ -210,12 +228,11 @@ __device__ __forceinline__ void coarse_pair16(uint32_t& lo, uint32_t& hi, const 
   }
 }
 
-// q . k_coarse for 2-bit / 4-bit formats: codes -> fp16 -> m16n8k16 against fp16 q (odd columns 0)
-template <int FMT, int NT, bool FAST>
-__device__ __forceinline__ void dot_f16(float (&out)[NT][2], const uint32_t (&qh)[NT][8][2], const uint8_t* tile,
-                                        const ScaleCtx& sc, int warp, int g, int t) {
+// the raw code bytes of rows (16*warp+g) and (+8) that this thread contracts over: channels [32t, 32t+32)
+template <int FMT>
+__device__ __forceinline__ void load_code_rows(uint32_t (&ra)[4], uint32_t (&rb)[4], const uint8_t* tile, int warp, int g,
+                                               int t) {
   constexpr int ROW = Fmt<FMT>::kRow;
-  uint32_t ra[4], rb[4];
   const uint8_t* rowA = tile + (16 * warp + g) * ROW;
   const uint8_t* rowB = rowA + 8 * ROW;
   if (FMT == FFA_K_Q2) {
@@ -227,6 +244,31 @@ __device__ __forceinline__ void dot_f16(float (&out)[NT][2], const uint32_t (&qh
     const uint4 b = *reinterpret_cast<const uint4*>(rowB + 16 * t);
     ra[0] = a.x; ra[1] = a.y; ra[2] = a.z; ra[3] = a.w; rb[0] = b.x; rb[1] = b.y; rb[2] = b.z; rb[3] = b.w;
   }
+}
+template <int FMT>
+__device__ __forceinline__ void load_code_rows(uint32_t (&ra)[4], uint32_t (&rb)[4], const RowsRef& rows, int /*slice*/,
+                                               int g, int t) {
+  const uint8_t* rowA = rows.base + g * rows.stride;
+  const uint8_t* rowB = rows.base + (g + 8) * rows.stride;
+  if (FMT == FFA_K_Q2) {
+    const uint2 z = make_uint2(0u, 0u);
+    const uint2 a = g < rows.valid ? __ldg(reinterpret_cast<const uint2*>(rowA + 8 * t)) : z;
+    const uint2 b = g + 8 < rows.valid ? __ldg(reinterpret_cast<const uint2*>(rowB + 8 * t)) : z;
+    ra[0] = a.x; ra[1] = a.y; rb[0] = b.x; rb[1] = b.y; ra[2] = ra[3] = rb[2] = rb[3] = 0;
+  } else {
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    const uint4 a = g < rows.valid ? __ldg(reinterpret_cast<const uint4*>(rowA + 16 * t)) : z;
+    const uint4 b = g + 8 < rows.valid ? __ldg(reinterpret_cast<const uint4*>(rowB + 16 * t)) : z;
+    ra[0] = a.x; ra[1] = a.y; ra[2] = a.z; ra[3] = a.w; rb[0] = b.x; rb[1] = b.y; rb[2] = b.z; rb[3] = b.w;
+  }
+}
+
+// q . k_coarse for 2-bit / 4-bit formats: codes -> fp16 -> m16n8k16 against fp16 q (odd columns 0)
+template <int FMT, int NT, bool FAST, typename Tile = const uint8_t*>
+__device__ __forceinline__ void dot_f16(float (&out)[NT][2], const uint32_t (&qh)[NT][8][2], const Tile& tile,
+                                        const ScaleCtx& sc, int warp, int g, int t) {
+  uint32_t ra[4], rb[4];
+  load_code_rows<FMT>(ra, rb, tile, warp, g, t);
   float acc[NT][2][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)

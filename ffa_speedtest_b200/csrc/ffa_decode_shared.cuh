@@ -83,6 +83,7 @@ struct DecodeParams {
   int nseg;          // chunks per (b, kv-head); `ppc` is the pages of a chunk
   int grid;          // CTAs to launch
   int* work;         // [0] next chunk to hand out, [1] CTAs that have left
+  int64_t kv_rows;   // token rows of the K/V tensors
   float* part_pm;            // [B*HQ, nch]
   float* part_pl;            // [B*HQ, nch]
 };

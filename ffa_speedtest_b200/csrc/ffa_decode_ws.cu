@@ -111,7 +111,13 @@ int decode_nch_bound(int B, int HKV, int NP, int wc_in) {
     if (f16 > want) f16 = want;
   }
   if (f16 < 1) f16 = 1;
-  return static_cast<int>(ws > f16 ? ws : f16);
+  // page-pipeline kernel (decode_tma_plan): ceil(NP / wc) + 1 with wc >= max(4 or the caller's size, ceil(NP / 63))
+  long long pipe = (static_cast<long long>(NP) + (wc_in > 0 ? wc_in : 4) - 1) / (wc_in > 0 ? wc_in : 4);
+  if (pipe > 63) pipe = 63;
+  pipe += 1;
+  long long best = ws > f16 ? ws : f16;
+  if (pipe > best) best = pipe;
+  return static_cast<int>(best);
 }
 
 bool decode_ws_supported(const DecodeParams& p, int group) {
@@ -133,7 +139,7 @@ int launch_decode_ws(const DecodeParams& p, int variant, int f8, int64_t kv_rows
     const int64_t all_c = static_cast<int64_t>(p.HKV) * row_c;
     const bool swz = variant == FFA_K_FP8;
     if (!make_map(&mc.maps[0], p.kc, kv_rows, all_c, row_c, kPage, swz, promo_c)) return FFA_E_LAUNCH;
-    if (!make_map(&mc.maps[1], p.kc, kv_rows, all_c, row_c, kSample, swz, promo_c)) return FFA_E_LAUNCH;
+    mc.maps[1] = mc.maps[0];              // (second descriptor unused)
     // without a residual the map is never used; point it at the coarse tensor to keep it valid
     if (p.kr) {
       if (!make_map(&mc.maps[2], p.kr, kv_rows, static_cast<int64_t>(p.HKV) * kResRow, kResRow, kPage, true,

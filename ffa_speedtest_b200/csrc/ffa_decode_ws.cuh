@@ -17,17 +17,20 @@
 //                 rule (a group of SBS/64 pages is dropped only if every head's maximum over the group
 //                 is strictly below that head's threshold), writes the kept mask and, for kept pages,
 //                 requests residual + V with TMA into the next free slot of a second ring.
-//   warps 6..9    refine: kept page number k goes to refine warp k mod 4, which adds the residual
-//                 dot to the coarse dots, does the page's softmax and accumulates P.V for all 64
-//                 tokens.  At the end of a chunk each refine warp writes its own partial
-//                 (m, l, o[128]) per q head; whichever warp arrives last for a (batch, kv-head) merges
-//                 all its partials (stage 2, ...q2fp8.py:142-171) while the others carry on.
+//   warps 6..9    refine, in pairs: kept page number k goes to pair k mod 2, each warp of the pair
+//                 taking 32 of its 64 tokens (a page leaves its shared-memory slot twice as fast as
+//                 with one warp, which leaves more of the ring for loads in flight).  A warp adds the
+//                 residual dot to the coarse dots, the pair agrees on the page maximum through shared
+//                 memory, and each warp does the softmax and P.V of its tokens.  At the end of a
+//                 chunk the four warps add their (m, l, o[128]) per q head in shared memory and write
+//                 one partial for the chunk; whichever CTA arrives last for a (batch, kv-head) merges
+//                 all its partials (stage 2, ...q2fp8.py:142-171), the heads split over the four warps.
 //
 // Chunks are handed out dynamically, so an SM whose pages are mostly pruned simply takes more of
 // them; the kept fraction differs a lot between (batch, kv-head)s, and equal page ranges per SM left
 // the slowest SM 40 % behind the average.
 //
-// Numerics are those of the TMA kernel this replaces: q split into exact e4m3 pieces against raw
+// Numerics are those of the page-pipeline kernel (ffa_decode_tma.cu): q split into exact e4m3 pieces against raw
 // fp8 K bytes (fp8 coarse and the residual), fp16 q against dequantised codes (2-/4-bit coarse),
 // P rounded to fp16 and split into exact bf16 pieces for bf16 V.  The refined score is
 // q.k_coarse + q.k_residual (the reference rounds k_coarse + k_residual to fp16 first).
@@ -60,22 +63,20 @@ struct WsSmem {
   static constexpr int kCoarseSlot = kPage * kRow;                                  // 8 / 2 / 4 KiB
   // coarse ring: each scoring warp should find its next tile already landed, i.e. more than one slot
   // per warp in flight; the residual + V ring takes what is left of the 227 KiB
-  static constexpr int kNC = FMT == FFA_K_FP8 ? 5 : (FMT == FFA_K_Q2 ? 16 : 8);
+  static constexpr int kNC = FMT == FFA_K_FP8 ? 6 : (FMT == FFA_K_Q2 ? 16 : 8);
   static constexpr int kNRV = NT == 2 ? 5 : 6;                                      // residual + V slots (24 KiB each)
-  static constexpr int kSampleSlot = kSampleRows * kRow < 1024 ? 1024 : kSampleRows * kRow;
   static constexpr int kHist = NT * 1024;                                           // raw dots of one page
   static constexpr bool kHasChannelScale = (FMT == FFA_K_Q2 || FMT == FFA_K_NF4);
   static constexpr int kOffRv = 0;
   static constexpr int kOffCoarse = kOffRv + kNRV * kRvSlot;
-  static constexpr int kOffSample = kOffCoarse + kNC * kCoarseSlot;                 // 2 chunks x 2 tiles
-  static constexpr int kOffDHist = kOffSample + 4 * kSampleSlot;
+  static constexpr int kOffDHist = kOffCoarse + kNC * kCoarseSlot;
   static constexpr int kOffDMax = kOffDHist + kND * kHist;      // [kND][8] page maxima
   static constexpr int kOffDPl = kOffDMax + kND * 32;           // [kND][8] mean-V: mass relative to the maximum
   static constexpr int kOffBars = kOffDPl + kND * 32;
-  // barriers: chunk full/empty | coarse full/empty | sample full/empty | threshold full/empty |
+  // barriers: chunk full/empty | coarse full/empty | threshold full/empty |
   //           page full/empty | residual+V full/empty
   //           | three chunk-end meeting points of the refine warps | one meeting point per refine pair
-  static constexpr int kNBars = 2 * kNSeg + 2 * kNC + 8 + 4 + 2 * kND + 2 * kNRV + 3 + kNP;
+  static constexpr int kNBars = 2 * kNSeg + 2 * kNC + 4 + 2 * kND + 2 * kNRV + 3 + kNP;
   static constexpr int kOffMisc = kOffBars + ((kNBars * 8 + 63) / 64) * 64;
   // misc: sTh[2][16] | seg[kNSeg][4] | kq_page[8] | kq_ds[8] | abort, last, pad[6] | book[16] | per scoring warp sS[128], sZ[128]
   static constexpr int kOffTh = kOffMisc;
@@ -338,7 +339,6 @@ __device__ __forceinline__ bool ws_arrive_unit(const DecodeParams& p, int unit, 
 template <int FMT, int F8, int NT, bool VBF, int QP, bool MV>
 __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_constant__ DecodeParams p,
                                                                   const __grid_constant__ CUtensorMap tm_c,
-                                                                  const __grid_constant__ CUtensorMap tm_s,
                                                                   const __grid_constant__ CUtensorMap tm_r,
                                                                   const __grid_constant__ CUtensorMap tm_v) {
   using L = WsSmem<FMT, NT>;
@@ -367,11 +367,9 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
   auto cfull = [&](int i) { return bars + 8u * (kB0 + i); };
   auto cempty = [&](int i) { return bars + 8u * (kB0 + kNC + i); };
   constexpr int kB1 = kB0 + 2 * kNC;
-  auto sfull = [&](int i) { return bars + 8u * (kB1 + i); };          // 2 chunks x 2 sample tiles
-  auto sempty = [&](int i) { return bars + 8u * (kB1 + 4 + i); };
-  auto thfull = [&](int i) { return bars + 8u * (kB1 + 8 + i); };      // 2 chunks
-  auto thempty = [&](int i) { return bars + 8u * (kB1 + 10 + i); };
-  constexpr int kB2 = kB1 + 12;
+  auto thfull = [&](int i) { return bars + 8u * (kB1 + i); };          // 2 chunks
+  auto thempty = [&](int i) { return bars + 8u * (kB1 + 2 + i); };
+  constexpr int kB2 = kB1 + 4;
   auto dfull = [&](int i) { return bars + 8u * (kB2 + i); };
   auto dempty = [&](int i) { return bars + 8u * (kB2 + kND + i); };
   constexpr int kB3 = kB2 + 2 * kND;
@@ -452,8 +450,13 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
       if (!end && lane == 0) next_raw = atomicAdd(p.work, 1);
       const int slot = seg_i % kNSeg;
       if (seg_i >= kNSeg && !WS_WAIT(segempty(slot), ((seg_i / kNSeg) - 1u) & 1u, 11, 1)) break;
-      const int unit = end ? -1 : chunk / n_seg;
-      const int part = end ? 0 : chunk % n_seg;
+      // chunk numbering: kv-head fastest, then the chunk of the sequence, then the batch.  Chunks that
+      // are claimed one after the other - and so are in flight together - then cover the same token
+      // rows of the same sequence for all kv-heads: a token row holds the heads side by side, and DRAM
+      // serves the pieces of one row together far better than pieces of unrelated rows
+      const int c_hkv = chunk % p.HKV, c_rest = chunk / p.HKV;
+      const int part = end ? 0 : c_rest % n_seg;
+      const int unit = end ? -1 : (c_rest / n_seg) * p.HKV + c_hkv;
       const int page_begin = part * CH;
       const int n = end ? 0 : min(CH, p.NP - page_begin);             // real pages (>= 1: a chunk never holds padding only)
       if (lane == 0) {
@@ -462,24 +465,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
       }
       if (end) break;
       const int b = unit / p.HKV, hkv = unit % p.HKV;
-      if (sampled) {
-        // the two 16-token sample tiles of this (batch, kv-head), into the pair of slots of this chunk's parity
-        const int ss = seg_i & 1;
-        bool ok = true;
-        if (seg_i >= 2)
-          ok = WS_WAIT(sempty(2 * ss), ((seg_i / 2) - 1u) & 1u, 12, 2) && WS_WAIT(sempty(2 * ss + 1), ((seg_i / 2) - 1u) & 1u, 12, 2);
-        if (!ok) break;
-        if (lane == 0) {
-          const int tok1 = (p.NTB - 1) * kSample;
-          const int r0 = p.bt ? p.bt[static_cast<int64_t>(b) * p.bt_stride] * kPage : b * T;
-          const int r1 = (p.bt ? p.bt[static_cast<int64_t>(b) * p.bt_stride + tok1 / kPage] * kPage
-                               : b * T + (tok1 / kPage) * kPage) + tok1 % kPage;
-          mbar_expect_tx(sfull(2 * ss), kSampleRows * ROW);
-          tma_load_2d(smem_u32(smem + L::kOffSample + (2 * ss) * L::kSampleSlot), &tm_s, hkv * ROW, r0, sfull(2 * ss));
-          mbar_expect_tx(sfull(2 * ss + 1), kSampleRows * ROW);
-          tma_load_2d(smem_u32(smem + L::kOffSample + (2 * ss + 1) * L::kSampleSlot), &tm_s, hkv * ROW, r1, sfull(2 * ss + 1));
-        }
-      }
       int btv = 0;
       bool ok = true;
       for (int c = 0; c < n; ++c) {
@@ -722,14 +707,23 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
       // tokens [0,16) and [(NTB-1)*16, +16), scored by the first two scoring warps
       if (sampled && sw < 2) {
         const int ss = seg_i & 1;
-        ok = WS_WAIT(sfull(2 * ss + sw), (seg_i / 2) & 1u, 6, 0);
-        if (ok && seg_i >= 2) ok = WS_WAIT(thempty(ss), ((seg_i / 2) - 1u) & 1u, 13, 0);
+        if (seg_i >= 2) ok = WS_WAIT(thempty(ss), ((seg_i / 2) - 1u) & 1u, 13, 0);
         if (!ok) break;
         const int blk = sw == 0 ? 0 : p.NTB - 1;
         const int tok0 = blk * kSample;
         if (FMT == FFA_K_NVFP4) apply_block_scale(load_block_scale(blk));
+        // the 16 sample rows are read straight from global memory (once per chunk: not worth a slot)
+        const int64_t row = (p.bt ? static_cast<int64_t>(p.bt[static_cast<int64_t>(b) * p.bt_stride + tok0 / kPage]) * kPage
+                                  : static_cast<int64_t>(b) * T + (tok0 / kPage) * kPage) + tok0 % kPage;
+        RowsRef rows;
+        rows.stride = static_cast<int64_t>(p.HKV) * ROW;
+        rows.base = p.kc + row * rows.stride + hkv * ROW;
+        rows.valid = static_cast<int>(min(static_cast<int64_t>(kSampleRows), p.kv_rows - row));
         float d[NT][2];
-        coarse_dots(d, smem + L::kOffSample + (2 * ss + sw) * L::kSampleSlot, 0);
+        if constexpr (kFp8Coarse) dot_fp8<F8, NT, QP, RowsRef>(d, qb, qinv, rows, 0, g, t);
+        else if (FMT == FFA_K_Q2 ? sc.q2_fast : (FMT == FFA_K_NVFP4 && sc.page_fast))
+          dot_f16<FMT, NT, true, RowsRef>(d, qh, rows, sc, 0, g, t);
+        else dot_f16<FMT, NT, false, RowsRef>(d, qh, rows, sc, 0, g, t);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const float s0 = tok0 + g < T ? to_log2(d[nt][0]) : -INFINITY;
@@ -740,7 +734,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
           if (g == 0) sTh[ss * 16 + sw * 8 + 4 * nt + t] = mm;
         }
         __syncwarp();
-        if (lane == 0) { mbar_arrive(thfull(ss)); mbar_arrive(sempty(2 * ss + sw)); }
+        if (lane == 0) mbar_arrive(thfull(ss));
       }
 
       float ks_batch = 0.f;         // nvfp4: block scales of this warp's next 32 pages, one per lane
@@ -1067,9 +1061,9 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
   // workspace; profiling builds serve at most 8192 (batch x kv-head) units): [role * 8 + i] = pacc[i]
   // of the role's warps (i < 6); [32] = kernel cycles of a CTA, [33] = its nanoseconds, [34] = the
   // longest CTA's ns.
-  //   coarse producer: 0 wait for a free coarse slot, 1 free chunk entry, 2 free sample slot
+  //   coarse producer: 0 wait for a free coarse slot, 1 free chunk entry
   //   dispatcher:      0 thresholds, 1 published page, 2 free residual+V slot, 3 kept-page branch, 5 next chunk
-  //   scoring:         0 sample tile, 1 coarse tile, 2 free entry, 3 dots, 4 publish, 5 next chunk
+  //   scoring:         0 thresholds read, 1 coarse tile, 2 free entry, 3 dots, 4 publish, 5 next chunk
   //   refine:          0 residual+V landed, 1 page work, 2 pages, 4 chunk-end meetings, 5 next chunk
   if (p.arrivals) {
     unsigned long long* gp = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.arrivals) + 32768);
@@ -1118,7 +1112,7 @@ int launch_ws_one(const DecodeParams& p, const CUtensorMap* maps, cudaStream_t s
     if (e != cudaSuccess) return note_cuda_error(e, "cudaFuncSetAttribute(decode_ws)");
     if (slot) configured[dev] = true;
   }
-  kern<<<static_cast<unsigned>(p.grid), kWsThreads, L::kBytes, stream>>>(p, maps[0], maps[1], maps[2], maps[3]);
+  kern<<<static_cast<unsigned>(p.grid), kWsThreads, L::kBytes, stream>>>(p, maps[0], maps[2], maps[3]);   // coarse K, residual, V (maps[1] is unused)
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? FFA_OK : note_cuda_error(e, "decode_ws launch");
 }

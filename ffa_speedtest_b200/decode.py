@@ -181,12 +181,14 @@ def decode_call(
     ``mean_v [B, HKV, 128]`` (V's dtype) selects the mean-V variant of the 2-bit format: pruned pages
     are not dropped but contribute their coarse softmax mass times this vector.
 
-    ``kernel``: "auto" is the warp-specialised TMA kernel (any q dtype, either V dtype, prune groups of
-    up to eight pages); "fp16" forces the fp16 tensor-core kernel, which follows the reference's fp16
-    rounding of the refined K tile to the letter and prunes page by page only; "tma_v1" is the earlier
-    TMA kernel (one CTA barrier per page), kept for side-by-side timing."""
-    if kernel not in ("auto", "fp16", "tma_v1"):
-        raise ValueError(f"kernel must be 'auto', 'fp16' or 'tma_v1', got {kernel!r}")
+    ``kernel``: "ws" is the warp-specialised TMA kernel (any q dtype, either V dtype, prune groups of
+    up to eight pages); "pipe" the page-pipeline TMA kernel (bfloat16 q, or float16 q with float16 V;
+    pages pruned one by one); "auto" takes "pipe" for the fp8 coarse format where it applies (it is
+    the faster of the two there) and "ws" otherwise; "fp16" forces the fp16 tensor-core kernel, which
+    follows the reference's fp16 rounding of the refined K tile to the letter and prunes page by page
+    only."""
+    if kernel not in ("auto", "fp16", "pipe", "ws"):
+        raise ValueError(f"kernel must be 'auto', 'ws', 'pipe' or 'fp16', got {kernel!r}")
     B, Tq, HQ, K = q.shape
     HKV, V = v.shape[2], v.shape[3]
     if block_table is None:
@@ -216,8 +218,8 @@ def decode_call(
                          f"multiple of SBS (got BS={BS}, SBS={SBS})")
     if SBS > MAX_SBS or (SBS // PAGE) & (SBS // PAGE - 1):
         raise ValueError(f"this build prunes groups of 1, 2, 4 or 8 pages: SBS must be 64, 128, 256 or 512 (got {SBS})")
-    if SBS != PAGE and kernel != "auto":
-        raise ValueError("SBS above 64 needs kernel='auto': the other kernels prune page by page only")
+    if SBS != PAGE and kernel not in ("auto", "ws"):
+        raise ValueError("SBS above 64 needs kernel='auto' or 'ws': the other kernels prune page by page only")
     NTB = -(-T // BS)
     NTBS = NTB * (BS // SBS)
 
@@ -275,13 +277,13 @@ def decode_call(
         if mean_v.shape != (B, HKV, V) or mean_v.dtype != v.dtype or not mean_v.is_cuda:
             raise ValueError(f"mean_v must be a CUDA tensor [B, HKV, V] = [{B}, {HKV}, {V}] of v's dtype")
         if partial_out is not None or kernel == "fp16":
-            raise ValueError("the mean-V variant has no partial output and runs on the TMA kernel only")
+            raise ValueError("the mean-V variant has no partial output and runs on the TMA kernels only")
         mean_v = mean_v.contiguous()
     a.v_mean = _lib.ptr(mean_v)
     a.workspace = workspace.scratch.data_ptr()
     a.workspace_bytes = workspace.scratch.numel()
     a.pages_per_chunk = pages_per_chunk
-    a.reserved = {"auto": 0, "fp16": 1, "tma_v1": 2}[kernel]
+    a.reserved = {"auto": 0, "fp16": 1, "pipe": 2, "ws": 4}[kernel]
     a.kv_rows = k_codes.shape[0] * k_codes.shape[1]
     _lib.check(_lib.lib().ffa_decode(a, _lib.current_stream(q.device)), "ffa_decode")
 

@@ -71,20 +71,31 @@ def global_threshold(variant: str, q: torch.Tensor, k_codes: torch.Tensor, *, de
 
     The thresholds depend on the coarse codes of the token rows ``sample_token_rows(T, BS)`` only, so
     a rank that owns other pages can compute them from a replicated copy of those 32 rows: ``k_codes``
-    is ``[B, 32, HKV, code_bytes]`` (first block, then second block).  The two blocks are placed in a five-page stand-in sequence at
-    the positions the kernel samples and one decode call over it writes the thresholds.  nvfp4 is
-    excluded: its page scales sit at other indices in the stand-in."""
+    is ``[B, 32, HKV, code_bytes]`` (first block, then second block).  The two blocks are placed in a
+    short stand-in sequence at the positions the kernel samples and one decode call over it writes the
+    thresholds.  For nvfp4 ``k_scale`` is the sequence's ``[B, NTB, HKV]`` page scales (or just its
+    first and last block, ``[B, 2, HKV]``): the kernel scales the first sample by block 0 and the
+    second by block NTB-1 (reference ...nvfp4fp8.py:80,99), and the stand-in carries those two."""
     from .decode import DecodeWorkspace, decode_call
-    if variant == "nvfp4":
-        raise ValueError("global_threshold does not cover nvfp4 (page scales)")
     if k_codes.dim() != 4 or k_codes.shape[1] != 32:
         raise ValueError("k_codes must be [B, 32, HKV, code_bytes]: the two 16-token sample blocks")
     B, _, HKV, W = k_codes.shape
     HQ = q.shape[2]
-    T_s = 5 * 64                                          # ceil(320 / 64) = 5 pages; second sample at (5-1)*16 = 64
+    # five pages: the second sample sits at (5-1)*16 = 64; six when a 5 x 5 nvfp4 scale would be
+    # ambiguous between [NTB, HKV] and its transpose
+    n_pages = 6 if (variant == "nvfp4" and HKV == 5) else 5
+    T_s = n_pages * 64
+    second = (n_pages - 1) * 16
     mini = torch.zeros((B, T_s, HKV, W), dtype=k_codes.dtype, device=k_codes.device)
     mini.view(torch.uint8)[:, 0:16] = k_codes.view(torch.uint8)[:, 0:16]
-    mini.view(torch.uint8)[:, 64:80] = k_codes.view(torch.uint8)[:, 16:32]
+    mini.view(torch.uint8)[:, second:second + 16] = k_codes.view(torch.uint8)[:, 16:32]
+    if variant == "nvfp4":
+        if k_scale is None or k_scale.dim() != 3 or k_scale.shape[0] != B or k_scale.shape[2] != HKV or k_scale.shape[1] < 1:
+            raise ValueError("nvfp4 needs k_scale [B, NTB, HKV] (or its first and last block)")
+        mini_scale = torch.ones((B, n_pages, HKV), dtype=k_scale.dtype, device=k_scale.device)
+        mini_scale[:, 0] = k_scale[:, 0]
+        mini_scale[:, n_pages - 1] = k_scale[:, -1]
+        k_scale = mini_scale
     v = torch.zeros((B, T_s, HKV, 128), dtype=q.dtype if q.dtype != torch.float32 else torch.float16, device=q.device)
     ws = DecodeWorkspace.for_shape(B, T_s, HQ, HKV, 128, BS=64, SBS=64, device=q.device, dtype=q.dtype)
     decode_call(variant, q, mini, v, k_scale=k_scale, k_zero=k_zero, k_residual=None, scale=scale, BS=64, SBS=64,

@@ -27,6 +27,11 @@ def entry(kind):
     return getattr(importlib.import_module("ffa_speedtest_b200." + mod), fn)
 
 
+def pipe_ok(q, v):
+    """The page-pipeline kernel takes bfloat16 q, or float16 q with float16 V."""
+    return q.dtype == torch.bfloat16 or (q.dtype == torch.float16 and v.dtype == torch.float16)
+
+
 def call(kind, q, coarse, v, res, **kw):
     """Call the variant's public entry point the way a user of the reference would."""
     dev = "cuda"
@@ -55,7 +60,7 @@ def check_output(o_gpu, o_ref):
     return max_abs
 
 
-@pytest.mark.parametrize("kernel", ["auto", "fp16"])
+@pytest.mark.parametrize("kernel", ["ws", "pipe", "fp16"])
 @pytest.mark.parametrize("kind", KINDS)
 @pytest.mark.parametrize("name", SMALL_CASES)
 def test_against_reference_goldens(kind, name, kernel):
@@ -63,8 +68,10 @@ def test_against_reference_goldens(kind, name, kernel):
     output within the north-star tolerance of the reference's fp32 output."""
     from ffa_speedtest_b200.decode import allocate_decode_workspace
     c = GoldenCase(kind, name)
-    if c.SBS != 64 and kernel == "fp16":
-        pytest.skip("the fp16 tensor-core kernel prunes page by page only")
+    if c.SBS != 64 and kernel != "ws":
+        pytest.skip("only the warp-specialised kernel prunes groups of pages")
+    if kernel == "pipe" and not pipe_ok(c.q, c.v):
+        pytest.skip("dtype pair outside the page-pipeline kernel")
     coarse, res = c.quantise()
     ws = allocate_decode_workspace(c.q.cuda(), c.v.cuda(), BS=c.BS, SBS=c.SBS)
     th = None if c.th is None else c.th.cuda()
@@ -89,7 +96,7 @@ def test_against_reference_goldens(kind, name, kernel):
         check_output(o, o_ref)
 
 
-@pytest.mark.parametrize("kernel", ["auto", "fp16"])
+@pytest.mark.parametrize("kernel", ["auto", "pipe", "fp16"])
 @pytest.mark.parametrize("fp8", ["e5m2", "e4m3"])
 def test_config0_q2fp8(fp8, kernel):
     """benchmark config 0: B=1, 32 q / 8 kv heads, T=4096, page 64, delta 8."""
@@ -108,7 +115,7 @@ def test_config0_q2fp8(fp8, kernel):
     check_output(o, torch.from_numpy(z["o"]))
 
 
-@pytest.mark.parametrize("kernel", ["auto", "fp16"])
+@pytest.mark.parametrize("kernel", ["ws", "pipe", "fp16"])
 @pytest.mark.parametrize("kind", KINDS)
 def test_paged_block_table_matches_contiguous(kind, kernel):
     """A seeded random permutation of pages gives bit-identical results to the identity layout."""
@@ -135,17 +142,18 @@ def test_paged_block_table_matches_contiguous(kind, kernel):
     assert torch.equal(o.cpu(), o_ref.cpu())
 
 
+@pytest.mark.parametrize("kernel", ["ws", "pipe"])
 @pytest.mark.parametrize("ppc", [1, 2, 3, 7, 64])
-def test_chunking_is_invariant(ppc):
+def test_chunking_is_invariant(ppc, kernel):
     """Any split of the page range over CTAs merges to the same result (fp32 merge noise only)."""
     q, k, v = make_decode_inputs(1, 64 * 21 + 5, 8, 2, 128, seed=22, n_heavy=3)
     coarse, res = fo.make_coarse("fp8", k, torch.float8_e4m3fn, 64)
-    base = call("fp8", q, coarse, v, res, BS=64, delta=5.0, pages_per_chunk=1000).float().cpu()
-    o = call("fp8", q, coarse, v, res, BS=64, delta=5.0, pages_per_chunk=ppc).float().cpu()
+    base = call("fp8", q, coarse, v, res, BS=64, delta=5.0, pages_per_chunk=1000, kernel=kernel).float().cpu()
+    o = call("fp8", q, coarse, v, res, BS=64, delta=5.0, pages_per_chunk=ppc, kernel=kernel).float().cpu()
     assert (o - base).abs().max().item() <= 1.0 / 128      # one bf16 ulp at |o| < 2
 
 
-@pytest.mark.parametrize("kernel", ["auto", "fp16"])
+@pytest.mark.parametrize("kernel", ["ws", "pipe", "fp16"])
 @pytest.mark.parametrize("T", [1, 15, 16, 17, 63, 64, 65, 127, 129, 257])
 def test_short_and_ragged_sequences(T, kernel):
     q, k, v = make_decode_inputs(2, T, 8, 2, 128, seed=30 + T, n_heavy=0)
@@ -178,7 +186,7 @@ def test_garbage_beyond_the_sequence_is_ignored():
             return out.view(x.dtype)
 
         paged = fo.CoarseK(kind, pool(coarse.codes, 0x7f), coarse.scale, coarse.zero, 128)
-        for kernel in ("auto", "fp16"):
+        for kernel in ("ws", "pipe", "fp16"):
             o = call(kind, q, paged, pool(v, 0x7fff), pool(res, 0x7f), block_table=bt.cuda(), seq_len=T, BS=64,
                      delta=5.0, kernel=kernel)
             check_output(o, ref)
@@ -253,7 +261,7 @@ def test_validation_errors_match_reference():
         f(args[0], v.to(d)[..., :32].contiguous(), *args[2:], k_residual=res.to(d))
 
 
-@pytest.mark.parametrize("kind", ["q2", "fp8", "fp4", "nf4"])
+@pytest.mark.parametrize("kind", ["q2", "fp8", "fp4", "nf4", "nvfp4"])
 def test_global_threshold_from_replicated_sample_rows(kind):
     """Thresholds computed from the 32 sample rows alone equal those of a decode over the sequence."""
     from ffa_speedtest_b200 import sharded
@@ -309,6 +317,36 @@ def test_full_size_properties(kind, B, T):
                     precomputed_threshold=th, partial_out=parts[i], **kw)
     merged = merge_partials(parts, torch.bfloat16)
     assert (merged.float() - o.float()).abs().max().item() <= 2.0 ** -7 * max(1.0, o.float().abs().max().item())
+
+
+@pytest.mark.parametrize("kind", ["fp8", "q2"])
+def test_long_single_sequence_on_every_kernel(kind):
+    """One sequence of 128K tokens and a single kv-head group: the case with the most partials per
+    q head.  The default workspace holds every kernel's plan, the kept sets are identical and the
+    outputs agree to accumulation order."""
+    from ffa_speedtest_b200 import quantize as Q
+    from ffa_speedtest_b200.decode import allocate_decode_workspace, decode_call
+    B, T, HQ, HKV = 1, 131072, 8, 2
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, 128, seed=9, device="cuda")
+    scale = zero = None
+    if kind == "fp8":
+        codes, res = Q.quantize_k_fp8_fp8_residual(k, torch.float8_e4m3fn)
+    else:
+        codes, scale, zero, res = Q.quantize_k_2bit_fp8_residual(k, torch.float8_e4m3fn)
+    ws = allocate_decode_workspace(q, v, BS=64)
+    outs, masks = {}, {}
+    for kernel in ("ws", "pipe", "fp16"):
+        o = decode_call(kind, q, codes, v, k_scale=scale, k_zero=zero, k_residual=res, BS=64, SBS=64, delta=6.0,
+                        workspace=ws, kernel=kernel)
+        torch.cuda.synchronize()
+        assert ws.status() == 0
+        outs[kernel], masks[kernel] = o.float().clone(), ws.mask.clone()
+    assert torch.equal(masks["ws"], masks["pipe"])
+    # the fp16 kernel computes its dots in another order: pages within 1e-3 of the threshold may differ
+    assert (masks["ws"] != masks["fp16"]).float().mean().item() < 1e-3
+    top = max(1.0, outs["ws"].abs().max().item())
+    assert (outs["ws"] - outs["pipe"]).abs().max().item() <= 2.0 ** -7 * top
+    assert (outs["ws"] - outs["fp16"]).abs().max().item() <= 1e-2 * top
 
 
 @pytest.mark.parametrize("name", ["meanv_ragged", "meanv_fp16", "meanv_sbs128"])
