@@ -572,6 +572,10 @@ extern "C" size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, i
          align_up(rows * nch * kHeadDim * sizeof(float), 256) + 256;
 }
 
+// fp8 coarse K goes to the warp-specialised kernel from this many pages (batch x kv-heads x pages per
+// sequence) up: 2^20 cached tokens at 8 kv-heads
+constexpr long long kFp8WsPages = 131072;
+
 extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!a || !a->q || !a->k_codes || !a->v || !a->out || !a->workspace) return FFA_E_NULL;
@@ -609,11 +613,13 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   p.q_dtype = a->q_dtype; p.scale_dtype = a->scale_dtype;
   p.use_res = a->use_residual ? 1 : 0;
   p.v_bf16 = a->v_dtype == FFA_BF16 ? 1 : 0;
-  // Kernel choice.  reserved = 0 picks by measurement: the warp-specialised kernel everywhere except
-  // fp8 coarse K pruned page by page with bf16 q (or fp16 q and V), where the page-pipeline kernel
-  // (three CTAs per SM, every warp scores and refines) keeps more loads in flight per SM and is
-  // about 10 % faster at high kept fractions.  Bit 0 forces the fp16 tensor-core kernel, bit 1 the
-  // page-pipeline kernel, bit 2 the warp-specialised kernel.
+  // Kernel choice.  reserved = 0 picks by measurement (both TMA kernels timed over batch 1-16,
+  // 4K-128K tokens, kept fractions 0.2-0.98): the warp-specialised kernel for the 2- and 4-bit coarse
+  // formats, for prune groups of more than one page, for the dtype pairs only it takes, and for fp8
+  // coarse K from about a million cached tokens up; below that fp8 coarse K runs on the page-pipeline
+  // kernel (three CTAs per SM, every warp scores and refines), which keeps more loads in flight per
+  // SM when the coarse pass is cheap and is 3-10 % faster there.  Bit 0 forces the fp16 tensor-core
+  // kernel, bit 1 the page-pipeline kernel, bit 2 the warp-specialised kernel.
   const int m = a->SBS / kPage;                 // pages per prune group
   const bool want_fp16 = (a->reserved & 1) != 0;
   const bool want_v1 = (a->reserved & 2) != 0;
@@ -626,7 +632,8 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   if (!want_fp16) {
     if (want_v1) use_tma = v1_ok;
     else if (want_ws) use_ws = ws_ok;
-    else if (a->variant == FFA_K_FP8 && v1_ok) use_tma = true;
+    else if (a->variant == FFA_K_FP8 && v1_ok &&
+             static_cast<long long>(a->B) * a->HKV * p.NP < kFp8WsPages) use_tma = true;
     else use_ws = ws_ok;
     if (!use_ws && !use_tma && !want_v1 && !want_ws) use_tma = v1_ok;
     if ((want_v1 || want_ws) && !use_ws && !use_tma) return m > 1 ? FFA_E_SHAPE : FFA_E_DTYPE;   // asked for by name

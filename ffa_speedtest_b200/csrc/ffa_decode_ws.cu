@@ -75,11 +75,20 @@ void decode_ws_plan(int B, int HKV, int NP, int group, int chunk_in, int* NPp_ou
   const long long sms = sm_count();
   long long ch = chunk_in;
   if (ch <= 0) {
-    // about six chunks per SM when there is that much work (fine enough for the SMs to even out
-    // their different kept fractions, coarse enough that a chunk's set-up - q operands, thresholds,
-    // one partial per refine warp - stays small beside its pages); never less than four pages
+    // Plenty of work: about six chunks per SM, handed out dynamically - fine enough for the SMs to even
+    // out their different kept fractions, coarse enough that a chunk's set-up (q operands, scales,
+    // thresholds, one partial) stays small beside its pages.  Less work: the set-up and the hand-over
+    // between chunks weigh more than the imbalance, so the chunks are cut to fill `waves` x SMs as
+    // exactly as whole chunks per (batch, kv-head) allow - one chunk per SM for the smallest cases.
     const long long per_cta = (total + sms - 1) / sms;
-    ch = per_cta >= 96 ? (per_cta + 5) / 6 : (per_cta >= 16 ? 16 : (per_cta > 4 ? per_cta : 4));
+    if (per_cta >= 256) ch = (per_cta + 5) / 6;
+    else {
+      const long long waves = per_cta < 64 ? 1 : (per_cta < 128 ? 2 : 3);
+      ch = (per_cta + waves - 1) / waves;
+      if (ch < 4) ch = 4;
+      if (ch > NPp) ch = NPp;
+      while (ch < NPp && units * ((NPp + ch - 1) / ch) > sms * waves) ++ch;
+    }
   }
   // the merge of a (b, kv-head) holds at most kWsMaxParts partials per q head, one per chunk
   const long long max_seg = kWsMaxParts;

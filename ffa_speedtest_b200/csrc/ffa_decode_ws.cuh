@@ -440,14 +440,18 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
 
   if (role == kRoleCoarse) {
     // ================= coarse producer ===============================================================
-    // lane 0 asks for the next chunk a whole chunk ahead; the answer is only looked at (broadcast) when
-    // the chunk before it has been streamed, so the round trip of the atomic is never waited for
+    // The first chunk of a CTA is its own number; further ones come from a global counter.  Lane 0 asks
+    // for the next chunk a few pages before the current one has been streamed - early enough that the
+    // round trip of the atomic and the first loads of the new chunk hide behind the pages the other
+    // warps still hold, late enough that no CTA sits on a chunk it will not start for a long time
+    // (asking a whole chunk ahead let the CTAs that started first take two chunks each and left
+    // others with none).
+    constexpr int kClaimLead = 8;
     int next_raw = 0;
-    if (lane == 0) next_raw = atomicAdd(p.work, 1);
     for (uint32_t seg_i = 0;; ++seg_i) {
-      const int chunk = __shfl_sync(kFull, next_raw, 0);
+      const int chunk = seg_i == 0 ? static_cast<int>(blockIdx.x)
+                                   : __shfl_sync(kFull, next_raw, 0) + static_cast<int>(gridDim.x);
       const bool end = chunk >= total_chunks || *reinterpret_cast<volatile int*>(sAbort) != 0;
-      if (!end && lane == 0) next_raw = atomicAdd(p.work, 1);
       const int slot = seg_i % kNSeg;
       if (seg_i >= kNSeg && !WS_WAIT(segempty(slot), ((seg_i / kNSeg) - 1u) & 1u, 11, 1)) break;
       // chunk numbering: kv-head fastest, then the chunk of the sequence, then the batch.  Chunks that
@@ -467,9 +471,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
       const int b = unit / p.HKV, hkv = unit % p.HKV;
       int btv = 0;
       bool ok = true;
+      const int claim_at = n > kClaimLead ? n - kClaimLead : 0;
       for (int c = 0; c < n; ++c) {
         const uint32_t gcc = gc + c;
         const int cslot = gcc % kNC;
+        if (c == claim_at && lane == 0) next_raw = atomicAdd(p.work, 1);
         if ((c & 31) == 0 && p.bt && c + lane < n)
           btv = p.bt[static_cast<int64_t>(b) * p.bt_stride + page_begin + c + lane];
         const int bv = __shfl_sync(kFull, btv, c & 31);

@@ -183,10 +183,10 @@ def decode_call(
 
     ``kernel``: "ws" is the warp-specialised TMA kernel (any q dtype, either V dtype, prune groups of
     up to eight pages); "pipe" the page-pipeline TMA kernel (bfloat16 q, or float16 q with float16 V;
-    pages pruned one by one); "auto" takes "pipe" for the fp8 coarse format where it applies (it is
-    the faster of the two there) and "ws" otherwise; "fp16" forces the fp16 tensor-core kernel, which
-    follows the reference's fp16 rounding of the refined K tile to the letter and prunes page by page
-    only."""
+    pages pruned one by one); "auto" takes "pipe" for fp8 coarse K below about a million cached tokens
+    where it applies (it is the faster of the two there) and "ws" otherwise; "fp16" forces the fp16
+    tensor-core kernel, which follows the reference's fp16 rounding of the refined K tile to the
+    letter and prunes page by page only."""
     if kernel not in ("auto", "fp16", "pipe", "ws"):
         raise ValueError(f"kernel must be 'auto', 'ws', 'pipe' or 'fp16', got {kernel!r}")
     B, Tq, HQ, K = q.shape

@@ -33,6 +33,8 @@ def main() -> None:
     ap.add_argument("--delta", type=float, default=8.0)
     ap.add_argument("--fp8", default="e4m3", choices=["e4m3", "e5m2"])
     ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--kernel", default="auto", choices=["auto", "ws", "pipe", "fp16"], help="decode kernel")
+    ap.add_argument("--SBS", type=int, default=64, help="tokens per prune group (decode)")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
@@ -42,12 +44,13 @@ def main() -> None:
 
     if args.what == "decode":
         q, k, v = make_decode_inputs(args.B, args.T, 32, 8, 128, seed=args.seed, device=dev)
-        codes, scale, zero, res = quantise(kind, k, f8, 64)
+        BS = max(64, args.SBS)
+        codes, scale, zero, res = quantise(kind, k, f8, BS)
         del k
-        ws = allocate_decode_workspace(q, v, BS=64, SBS=64)
+        ws = allocate_decode_workspace(q, v, BS=BS, SBS=args.SBS)
         for _ in range(args.iters):
-            decode_call(kind, q, codes, v, k_scale=scale, k_zero=zero, k_residual=res, BS=64, SBS=64,
-                        delta=args.delta, workspace=ws)
+            decode_call(kind, q, codes, v, k_scale=scale, k_zero=zero, k_residual=res, BS=BS, SBS=args.SBS,
+                        delta=args.delta, workspace=ws, kernel=args.kernel)
         torch.cuda.synchronize()
         print(f"decode {args.variant} B={args.B} T={args.T}: kept fraction {float(ws.mask.float().mean()):.4f}, "
               f"status {ws.status()}")

@@ -95,11 +95,13 @@ typedef struct FfaDecodeArgs {
   size_t workspace_bytes;
   int32_t pages_per_chunk;  /* 0 = choose automatically                                         */
   int32_t reserved;         /* kernel choice.  0: by measurement - the warp-specialised TMA kernel,
-                               except for fp8 coarse K with SBS = 64 and bf16 q (or fp16 q and V),
-                               where the page-pipeline TMA kernel is the faster one.  Bit 0: the
-                               fp16 tensor-core kernel (the reference's rounding sequence to the
-                               letter; SBS = 64 only).  Bit 1: the page-pipeline kernel (SBS = 64,
-                               bf16 q or fp16 q with fp16 V).  Bit 2: the warp-specialised kernel  */
+                               except for fp8 coarse K with SBS = 64, bf16 q (or fp16 q and V) and
+                               fewer than 131072 pages in all (B x HKV x pages per sequence), where
+                               the page-pipeline TMA kernel is the faster one.  Bit 0: the fp16
+                               tensor-core kernel (the reference's rounding sequence to the letter;
+                               SBS = 64 only).  Bit 1: the page-pipeline kernel (SBS = 64, bf16 q
+                               or fp16 q with fp16 V).  Bit 2: the warp-specialised kernel.  A
+                               kernel asked for by bit that cannot take the call is an error  */
   int64_t kv_rows;          /* token rows in the K/V tensors: pages*64 of a pool, 0 = B*T       */
   const void* v_mean;       /* optional [B, HKV, 128] in V's type: the mean-V variant
                                (ffa-q2fp8-meanv/attn_kernel/attn_kernel_v1210_meanv_bsz_q2fp8.py): pruned
