@@ -98,6 +98,8 @@ def lib() -> C.CDLL:
     for name in ("ffa_quantize_q2", "ffa_quantize_fp8fp8", "ffa_quantize_fp4", "ffa_quantize_nf4",
                  "ffa_quantize_nvfp4"):
         getattr(L, name).restype = C.c_int
+    L.ffa_cache_append.argtypes = [i32, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, i32, vp]
+    L.ffa_cache_append.restype = C.c_int
     L.ffa_kproj_rope.argtypes = [C.POINTER(FfaKprojArgs), C.c_void_p]
     L.ffa_kproj_rope.restype = C.c_int
     L.ffa_kproj_workspace_bytes.argtypes = [i32, i32, i32, i32]

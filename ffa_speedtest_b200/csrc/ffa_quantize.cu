@@ -425,6 +425,16 @@ int quantize_impl(int variant, const void* k, int dt, int B, int T, int HKV, int
 
 }  // namespace
 
+// Copies rows of `vec_per_row` 16-byte pieces to the rows the map names (V into its page slots).
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const uint4* __restrict__ src, int64_t n_vec, int vec_per_row,
+                                                           uint4* __restrict__ dst, RowMap map) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / vec_per_row, c = i % vec_per_row;
+    dst[map(r) * vec_per_row + c] = src[i];
+  }
+}
+
 int quantize_dispatch(int variant, const void* k, int k_dtype, int B, int T, int HKV, int fp8, int page_size,
                       uint8_t* codes, void* scale, void* zero, uint8_t* residual, void* scratch,
                       const int32_t* slot_table, int slot_stride, int slot_pos0, cudaStream_t st) {
@@ -472,4 +482,32 @@ extern "C" int ffa_quantize_nvfp4(const void* k, int32_t dt, int32_t B, int32_t 
                                   ffa_stream_t stream) {
   return quantize_impl(FFA_K_NVFP4, k, dt, B, T, HKV, fp8, page_size, codes, scale, nullptr, residual, nullptr,
                        RowMap{nullptr, 0, T, 0}, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ffa_cache_append(int32_t variant, const void* k, const void* v, int32_t dt, int32_t B, int32_t T_new,
+                                int32_t HKV, int32_t fp8, uint8_t* codes_pool, uint8_t* residual_pool, void* v_pool,
+                                const int32_t* block_table, int32_t bt_stride, int32_t pos0, ffa_stream_t stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (!block_table || (!k && !v)) return FFA_E_NULL;
+  if (B <= 0 || T_new <= 0 || HKV <= 0 || pos0 < 0 || bt_stride < (pos0 + T_new + kPage - 1) / kPage) return FFA_E_SHAPE;
+  if (variant != FFA_K_FP8 && variant != FFA_K_FP4) return FFA_E_VARIANT;     // formats without per-sequence statistics
+  if (k) {
+    const int rc = quantize_dispatch(variant, k, dt, B, T_new, HKV, fp8, kPage, codes_pool, nullptr, nullptr, residual_pool,
+                                     nullptr, block_table, bt_stride, pos0, st);
+    if (rc != FFA_OK) return rc;
+  }
+  if (v) {
+    if (!v_pool) return FFA_E_NULL;
+    if (dt != FFA_F16 && dt != FFA_BF16) return FFA_E_DTYPE;
+    if (!aligned16(v) || !aligned16(v_pool)) return FFA_E_ALIGN;
+    const int vec_per_row = HKV * D * 2 / 16;
+    const int64_t n_vec = static_cast<int64_t>(B) * T_new * vec_per_row;
+    int64_t blocks = (n_vec + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    scatter_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<const uint4*>(v), n_vec, vec_per_row,
+                                                                      static_cast<uint4*>(v_pool),
+                                                                      RowMap{block_table, bt_stride, T_new, pos0});
+    return last_launch("ffa_cache_append");
+  }
+  return FFA_OK;
 }

@@ -18,7 +18,7 @@ from typing import Any, Optional
 
 import torch
 
-from ... import quantize as Q
+from ... import _lib
 from ...decode import DecodeWorkspace, allocate_decode_workspace
 from ...kproj import kproj_fused
 from ..attn_kernel.attn_kernel_v1210_fused_bsz_fp8fp8 import attn_forward_decode_fp8fp8
@@ -65,6 +65,28 @@ class PagedFP8Fp8Layer:
         page = self.block_table[:, (t // PAGE)].long()                                     # [B, count]
         return (page * PAGE + (t % PAGE)[None, :]).reshape(-1)
 
+    def _append(self, key_states: Optional[torch.Tensor], value_states: torch.Tensor, T_new: int) -> None:
+        """One library call: quantise K (if given) into the base and residual pools and copy V into
+        its pool, all at the page slots of positions ``seq_len .. seq_len + T_new - 1``."""
+        value_states = value_states.to(self.dtype).contiguous()
+        k_ptr = 0
+        if key_states is not None and self.key_residual is None:
+            # no residual pool: quantise to a temporary and place the base codes with torch
+            from ... import quantize as Q
+            base, _ = Q.quantize_k_fp8_fp8_residual(key_states.to(self.dtype).contiguous(), self.fp8_dtype)
+            rows = self._rows(self.seq_len, T_new)
+            self.key_base.view(-1, self.num_kv_heads, self.head_dim).view(torch.uint8)[rows] = \
+                base.view(torch.uint8).reshape(-1, self.num_kv_heads, self.head_dim)
+        elif key_states is not None:
+            key_states = key_states.to(self.dtype).contiguous()
+            k_ptr = key_states.data_ptr()
+        _lib.check(_lib.lib().ffa_cache_append(
+            _lib.VARIANT_CODE["fp8"], k_ptr, value_states.data_ptr(), _lib.float_code(self.dtype), self.batch, T_new,
+            self.num_kv_heads, _lib.fp8_code(self.fp8_dtype), self.key_base.data_ptr(),
+            self.key_residual.data_ptr() if self.key_residual is not None else 0,
+            self.value.data_ptr(), self.block_table.data_ptr(), self.block_table.shape[1], self.seq_len,
+            _lib.current_stream(self.device)), "ffa_cache_append")
+
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor,
                cache_kwargs: Optional[dict[str, Any]] = None) -> None:
         """Append ``key_states, value_states [B, T_new, HKV, D]`` (post-RoPE K)."""
@@ -73,13 +95,7 @@ class PagedFP8Fp8Layer:
             raise ValueError(f"expected [B={self.batch}, T, HKV={self.num_kv_heads}, D={self.head_dim}] keys and values")
         if self.seq_len + T_new > self.max_seq_len:
             raise ValueError(f"cache capacity {self.max_seq_len} exceeded ({self.seq_len} + {T_new})")
-        base, res = Q.quantize_k_fp8_fp8_residual(key_states.contiguous(), self.fp8_dtype)
-        rows = self._rows(self.seq_len, T_new)
-        flat = lambda pool: pool.view(-1, HKV, D)
-        flat(self.key_base).view(torch.uint8)[rows] = base.view(torch.uint8).reshape(-1, HKV, D)
-        if self.use_fp8_residual:
-            flat(self.key_residual).view(torch.uint8)[rows] = res.view(torch.uint8).reshape(-1, HKV, D)
-        flat(self.value)[rows] = value_states.to(self.dtype).reshape(-1, HKV, D)
+        self._append(key_states, value_states, T_new)
         self.seq_len += T_new
 
     def update_from_hidden(self, hidden: torch.Tensor, w_k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
@@ -97,8 +113,7 @@ class PagedFP8Fp8Layer:
             raise ValueError(f"cache capacity {self.max_seq_len} exceeded ({self.seq_len} + {T_new})")
         kproj_fused("fp8", hidden, w_k, cos, sin, HKV, D, bias=bias, fp8_dtype=self.fp8_dtype,
                     block_table=self.block_table, out=(self.key_base, self.key_residual), position=self.seq_len)
-        rows = self._rows(self.seq_len, T_new)
-        self.value.view(-1, HKV, D)[rows] = value_states.to(self.dtype).reshape(-1, HKV, D)
+        self._append(None, value_states, T_new)
         self.seq_len += T_new
 
     # ---- decode ----------------------------------------------------------------------------------

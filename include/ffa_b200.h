@@ -176,6 +176,18 @@ int ffa_quantize_nvfp4(const void* k, int32_t k_dtype, int32_t B, int32_t T, int
                        int32_t page_size, uint8_t* codes, void* scale, uint8_t* residual, ffa_stream_t stream);
 
 /*
+ * Appends T_new tokens per sequence to a paged cache: K [B, T_new, HKV, 128] (post-RoPE) is quantised
+ * (variant FFA_K_FP8 or FFA_K_FP4, the formats without per-sequence statistics) and its codes and fp8
+ * residual are written into the page slots that block_table [B, bt_stride] names for positions
+ * pos0 .. pos0 + T_new - 1; V [B, T_new, HKV, 128] (fp16 / bf16) is copied into the same slots of
+ * v_pool.  Either of k, v may be NULL (only the other is appended).  Replaces the torch.cat append of
+ * ffa-fp8fp8/e2e/fp8fp8_cache.py:74-121 (FP8Fp8DynamicLayer.update).
+ */
+int ffa_cache_append(int32_t variant, const void* k, const void* v, int32_t dtype, int32_t B, int32_t T_new, int32_t HKV,
+                     int32_t fp8_format, uint8_t* codes_pool, uint8_t* residual_pool, void* v_pool,
+                     const int32_t* block_table, int32_t bt_stride, int32_t pos0, ffa_stream_t stream);
+
+/*
  * Fused K projection + bias + RoPE (+ quantise and scatter into the cache).  Replaces
  *   kproj_rope_quantize_{triton,fused}   ffa-q2fp8/fused_kproj_rope_q2fp8.py:427-566 (two GEMM passes there)
  *   kproj_rope_fp4_{triton,fused}        ffa-fp4fp8/fused_kproj_rope_fp4fp8.py:415-522
