@@ -100,6 +100,8 @@ def lib() -> C.CDLL:
         getattr(L, name).restype = C.c_int
     L.ffa_cache_append.argtypes = [i32, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, i32, vp]
     L.ffa_cache_append.restype = C.c_int
+    L.ffa_quantize_append.argtypes = [i32, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp]
+    L.ffa_quantize_append.restype = C.c_int
     L.ffa_kproj_rope.argtypes = [C.POINTER(FfaKprojArgs), C.c_void_p]
     L.ffa_kproj_rope.restype = C.c_int
     L.ffa_kproj_workspace_bytes.argtypes = [i32, i32, i32, i32]

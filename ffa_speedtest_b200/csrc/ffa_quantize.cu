@@ -158,6 +158,15 @@ __global__ void nf4_finalize_kernel(const uint32_t* mm, int n, int dt, void* sca
   if (i < n) store_elem(scale, i, dt, fmaxf(ord_decode(mm[2 * i + 1]), 1e-6f));
 }
 
+// nf4 append: the encoder reads absmax as ordered uints; rebuild them from the (frozen) scale tensor
+__global__ void nf4_mm_from_scale_kernel(const void* scale, int n, int dt, uint32_t* mm) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    mm[2 * i] = ord_encode(0.f);
+    mm[2 * i + 1] = ord_encode(load_elem(scale, i, dt));
+  }
+}
+
 // Encode pass of q2 / fp8fp8 / fp4 / nf4: a block walks token rows, a thread takes one group of
 // eight channels of the row.  Two rows are in flight per thread.
 enum { kEncFp8 = 0, kEncFp4 = 1, kEncNf4 = 2, kEncQ2 = 3 };
@@ -342,10 +351,11 @@ int last_launch(const char* what) {
     else { if ((fp8) == FFA_E4M3) { CALL(kF32, kE4M3); } else { CALL(kF32, kE5M2); } }                    \
   } while (0)
 
-void launch_minmax(bool abs_only, const void* k, int dt, int B, int T, int HKV, uint32_t* mm, cudaStream_t st) {
+void launch_minmax(bool abs_only, const void* k, int dt, int B, int T, int HKV, uint32_t* mm, cudaStream_t st,
+                   bool init = true) {
   const int row_elems = HKV * D;
   const int n = B * row_elems;
-  minmax_init_kernel<<<(n + 255) / 256, 256, 0, st>>>(mm, n);
+  if (init) minmax_init_kernel<<<(n + 255) / 256, 256, 0, st>>>(mm, n);   // else: fold into running statistics
   const int gpr = row_elems / 8;
   const int lanes = gpr >= 256 ? 1 : 256 / gpr;
   // enough blocks to fill the GPU, at least 16 tokens per token lane
@@ -510,4 +520,42 @@ extern "C" int ffa_cache_append(int32_t variant, const void* k, const void* v, i
     return last_launch("ffa_cache_append");
   }
   return FFA_OK;
+}
+
+extern "C" int ffa_quantize_append(int32_t variant, const void* k, int32_t dt, int32_t B, int32_t T_new, int32_t HKV,
+                                   int32_t fp8, uint8_t* codes_pool, const void* scale, const void* zero,
+                                   uint8_t* residual_pool, void* running_minmax, void* scratch,
+                                   const int32_t* block_table, int32_t bt_stride, int32_t pos0, ffa_stream_t stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int rc = check_common(k, dt, B, T_new, HKV, fp8);
+  if (rc) return rc;
+  if (!codes_pool || !residual_pool || !block_table) return FFA_E_NULL;
+  if (pos0 < 0 || bt_stride < (pos0 + T_new + kPage - 1) / kPage) return FFA_E_SHAPE;
+  if (!aligned16(k) || !aligned16(codes_pool) || !aligned16(residual_pool) || !aligned16(scale) || !aligned16(zero) ||
+      !aligned16(running_minmax) || !aligned16(scratch))
+    return FFA_E_ALIGN;
+  const RowMap map{block_table, bt_stride, T_new, pos0};
+  const int n = B * HKV * D;
+  switch (variant) {
+    case FFA_K_FP8:
+      launch_encode<kEncFp8>(k, dt, fp8, B, T_new, HKV, nullptr, nullptr, codes_pool, residual_pool, map, st);
+      break;
+    case FFA_K_FP4:
+      launch_encode<kEncFp4>(k, dt, fp8, B, T_new, HKV, nullptr, nullptr, codes_pool, residual_pool, map, st);
+      break;
+    case FFA_K_Q2:
+      if (!scale || !zero) return FFA_E_NULL;
+      if (running_minmax) launch_minmax(false, k, dt, B, T_new, HKV, static_cast<uint32_t*>(running_minmax), st, false);
+      launch_encode<kEncQ2>(k, dt, fp8, B, T_new, HKV, scale, zero, codes_pool, residual_pool, map, st);
+      break;
+    case FFA_K_NF4:
+      if (!scale || !scratch) return FFA_E_NULL;
+      if (running_minmax) launch_minmax(true, k, dt, B, T_new, HKV, static_cast<uint32_t*>(running_minmax), st, false);
+      nf4_mm_from_scale_kernel<<<(n + 255) / 256, 256, 0, st>>>(scale, n, dt, static_cast<uint32_t*>(scratch));
+      launch_encode<kEncNf4>(k, dt, fp8, B, T_new, HKV, scratch, nullptr, codes_pool, residual_pool, map, st);
+      break;
+    default:
+      return FFA_E_VARIANT;       // nvfp4: page-local scales, re-encode the open page with ffa_quantize_nvfp4
+  }
+  return last_launch("ffa_quantize_append");
 }

@@ -15,7 +15,7 @@ this module                           reference
 """
 from __future__ import annotations
 
-from typing import Tuple
+from typing import Optional, Tuple
 
 import torch
 
@@ -38,7 +38,14 @@ def _scratch(B: int, HKV: int, device) -> torch.Tensor:
     return torch.empty(_lib.lib().ffa_quantize_scratch_bytes(B, HKV), dtype=torch.uint8, device=device)
 
 
-def quantize_k_2bit_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype
+def minmax_scratch(B: int, HKV: int, device) -> torch.Tensor:
+    """Scratch buffer of the 2-bit / NF4 quantisers.  Passed as ``scratch=`` it holds, after the call,
+    the per-channel (min, max) of K as ordered integers: the running statistics that
+    ``quantize_append`` keeps up to date."""
+    return _scratch(B, HKV, device)
+
+
+def quantize_k_2bit_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype, *, scratch: Optional[torch.Tensor] = None
                                  ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """-> (codes [B,T,HKV,32] u8, scale [B,HKV,128], zero [B,HKV,128], residual [B,T,HKV,128] fp8)."""
     k, B, T, HKV, dt, f8, st = _prep(k, fp8_dtype)
@@ -46,7 +53,8 @@ def quantize_k_2bit_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype
     scale = torch.empty((B, HKV, 128), dtype=k.dtype, device=k.device)
     zero = torch.empty_like(scale)
     res = torch.empty((B, T, HKV, 128), dtype=fp8_dtype, device=k.device)
-    scratch = _scratch(B, HKV, k.device)
+    if scratch is None:
+        scratch = _scratch(B, HKV, k.device)
     _lib.check(_lib.lib().ffa_quantize_q2(k.data_ptr(), dt, B, T, HKV, f8, codes.data_ptr(), scale.data_ptr(),
                                           zero.data_ptr(), res.data_ptr(), scratch.data_ptr(), st), "ffa_quantize_q2")
     return codes, scale, zero, res
@@ -72,14 +80,15 @@ def encode_k_fp4_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype) -> Tuple[
     return codes, res
 
 
-def encode_k_nf4_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype
+def encode_k_nf4_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype, *, scratch: Optional[torch.Tensor] = None
                               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """-> (nibbles [B,T,HKV,64] u8, absmax [B,HKV,128] in k's dtype, residual fp8)."""
     k, B, T, HKV, dt, f8, st = _prep(k, fp8_dtype)
     codes = torch.empty((B, T, HKV, 64), dtype=torch.uint8, device=k.device)
     scale = torch.empty((B, HKV, 128), dtype=k.dtype, device=k.device)
     res = torch.empty((B, T, HKV, 128), dtype=fp8_dtype, device=k.device)
-    scratch = _scratch(B, HKV, k.device)
+    if scratch is None:
+        scratch = _scratch(B, HKV, k.device)
     _lib.check(_lib.lib().ffa_quantize_nf4(k.data_ptr(), dt, B, T, HKV, f8, codes.data_ptr(), scale.data_ptr(),
                                            res.data_ptr(), scratch.data_ptr(), st), "ffa_quantize_nf4")
     return codes, scale, res
@@ -98,6 +107,25 @@ def encode_k_nvfp4_fp8_residual(k: torch.Tensor, fp8_dtype: torch.dtype, page_si
     _lib.check(_lib.lib().ffa_quantize_nvfp4(k.data_ptr(), dt, B, T, HKV, f8, page_size, codes.data_ptr(),
                                              scale.data_ptr(), res.data_ptr(), st), "ffa_quantize_nvfp4")
     return codes, scale, res
+
+
+def quantize_append(kind: str, k_new: torch.Tensor, codes_pool: torch.Tensor, residual_pool: torch.Tensor,
+                    block_table: torch.Tensor, position: int, *, fp8_dtype: torch.dtype,
+                    scale: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None,
+                    running_minmax: Optional[torch.Tensor] = None) -> None:
+    """Encode ``k_new [B, T_new, HKV, 128]`` against the scales the cache already has and write codes and
+    residual into the page slots of positions ``position ..`` (``ffa_quantize_append``): q2 needs
+    ``scale`` and ``zero``, nf4 ``scale``; fp8 / fp4 have none.  ``running_minmax`` is the scratch buffer
+    of the whole-sequence quantiser; the new tokens' extremes are folded into it."""
+    k_new, B, T_new, HKV, dt, f8, st = _prep(k_new, fp8_dtype)
+    if kind not in ("q2", "nf4", "fp8", "fp4"):
+        raise ValueError(f"quantize_append serves q2, nf4, fp8 and fp4, got {kind!r}")
+    scratch = _scratch(B, HKV, k_new.device) if kind == "nf4" else None
+    ptr = lambda t: 0 if t is None else t.data_ptr()
+    _lib.check(_lib.lib().ffa_quantize_append(
+        _lib.VARIANT_CODE[kind], k_new.data_ptr(), dt, B, T_new, HKV, f8, codes_pool.data_ptr(), ptr(scale), ptr(zero),
+        residual_pool.data_ptr(), ptr(running_minmax), ptr(scratch), block_table.data_ptr(), block_table.shape[1],
+        int(position), st), "ffa_quantize_append")
 
 
 # variant directory name of the reference -> short name of its coarse-K format

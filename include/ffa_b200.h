@@ -176,6 +176,26 @@ int ffa_quantize_nvfp4(const void* k, int32_t k_dtype, int32_t B, int32_t T, int
                        int32_t page_size, uint8_t* codes, void* scale, uint8_t* residual, ffa_stream_t stream);
 
 /*
+ * Streaming append for the formats whose scales span the sequence (the incremental update the reference
+ * lists as future work, ffa-q2fp8/OPTIMIZATION_NOTES.md:23-27).  K [B, T_new, HKV, 128] of the new tokens
+ * is encoded against the scales the cache already has - q2: scale and zero, nf4: scale (absmax), each
+ * [B, HKV, 128] in K's dtype, read only - and written into the page slots of positions pos0 .. pos0 +
+ * T_new - 1.  Codes saturate at the ends of the existing range; the fp8 residual (k - dequantised code)
+ * carries what the code cannot, so refined scores stay as accurate as the fp8 residual allows.  As long
+ * as the new tokens stay inside the range the scales were made from, the result is bit-identical to
+ * quantising the whole lengthened sequence.  running_minmax (optional) is the scratch buffer a previous
+ * ffa_quantize_q2 / ffa_quantize_nf4 call left its per-channel min/max in; the new tokens are folded in,
+ * so a caller can see how far the range has drifted and decide to requantise.  scratch: nf4 only,
+ * ffa_quantize_scratch_bytes(B, HKV) bytes, distinct from running_minmax.  FFA_K_FP8 / FFA_K_FP4 are
+ * accepted too (no statistics).  nvfp4 keeps page-local scales: re-encode the open page with
+ * ffa_quantize_nvfp4.
+ */
+int ffa_quantize_append(int32_t variant, const void* k, int32_t k_dtype, int32_t B, int32_t T_new, int32_t HKV,
+                        int32_t fp8_format, uint8_t* codes_pool, const void* scale, const void* zero,
+                        uint8_t* residual_pool, void* running_minmax, void* scratch, const int32_t* block_table,
+                        int32_t bt_stride, int32_t pos0, ffa_stream_t stream);
+
+/*
  * Appends T_new tokens per sequence to a paged cache: K [B, T_new, HKV, 128] (post-RoPE) is quantised
  * (variant FFA_K_FP8 or FFA_K_FP4, the formats without per-sequence statistics) and its codes and fp8
  * residual are written into the page slots that block_table [B, bt_stride] names for positions
@@ -231,7 +251,7 @@ size_t ffa_kproj_workspace_bytes(int32_t B, int32_t T, int32_t HKV, int32_t rope
 /* Text of the last CUDA runtime error seen by this library on the calling thread ("" if none). */
 const char* ffa_last_cuda_error(void);
 /* Library version, bumped when the ABI changes (2: FfaDecodeArgs ends in v_mean; FfaKprojArgs.slot_pos0;
- * 3: ffa_static_scratch_status, every SBS in one launch). */
+ * 3: ffa_static_scratch_status, every SBS in one launch; 4: ffa_cache_append, ffa_quantize_append). */
 int ffa_abi_version(void);
 
 #ifdef __cplusplus
