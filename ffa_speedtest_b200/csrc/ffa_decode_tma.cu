@@ -546,6 +546,10 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
         w[16 * i + g + 8] = run_o[nt][i][1];
       }
     }
+    // A segment one of whose waits gave up computed on tiles that may never have landed: its mass is
+    // published as NaN, so the merged rows of this (b, kv-head) are NaN rather than plausible numbers.
+    const bool seg_bad = __syncthreads_or(timed_out ? 1 : 0) != 0;
+    if (seg_bad && tid < 32) lred[tid] = __int_as_float(0x7fc00000);
     __syncthreads();
     const int64_t row0 = static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G;
     for (int h = 0; h < G; ++h) {
@@ -801,23 +805,43 @@ bool decode_tma_supported(const DecodeParams& p) {
   return types_ok && encode_tiled_fn() != nullptr;
 }
 
+namespace {
+// The three tensor maps of the last call on this thread: a decode loop calls with the same tensors step
+// after step, and encoding the maps (three driver calls) is most of an eager call's host time.
+struct TmaMapCache {
+  bool valid = false;
+  const void *kc = nullptr, *kr = nullptr, *v = nullptr;
+  int64_t rows = 0;
+  int hkv = 0, variant = 0;
+  alignas(64) CUtensorMap mc, mr, mv;
+};
+thread_local TmaMapCache g_tma_maps;
+}  // namespace
+
 int launch_decode_tma(const DecodeParams& p, int variant, int f8, int64_t kv_rows, cudaStream_t stream) {
   if (kv_rows <= 0 || kv_rows > 0x7fffffffLL) return FFA_E_LIMIT;
-  alignas(64) CUtensorMap mc, mr, mv;
-  const int row_c = variant == FFA_K_FP8 ? 128 : (variant == FFA_K_Q2 ? 32 : 64);
-  // L2 promotion no wider than one head's row: a 256-byte promotion on 128-byte rows pulled the
-  // neighbouring head's bytes from DRAM too early to be reused (+15 % DRAM traffic, -11 % speed).
-  const int promo_c = row_c >= 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
-                                   : (row_c >= 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B : CU_TENSOR_MAP_L2_PROMOTION_NONE);
-  const int promo_r = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
-  const int promo_v = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
-  if (!make_map(&mc, p.kc, kv_rows, static_cast<int64_t>(p.HKV) * row_c, row_c, variant == FFA_K_FP8, promo_c))
-    return FFA_E_LAUNCH;
-  // without a residual the map is never used; point it at the coarse tensor to keep it valid
-  if (!make_map(&mr, p.kr ? p.kr : p.kc, kv_rows, static_cast<int64_t>(p.HKV) * (p.kr ? kResRow : row_c),
-                p.kr ? kResRow : row_c, p.kr != nullptr, p.kr ? promo_r : promo_c))
-    return FFA_E_LAUNCH;
-  if (!make_map(&mv, p.v, kv_rows, static_cast<int64_t>(p.HKV) * kVRow, 128, true, promo_v)) return FFA_E_LAUNCH;
+  TmaMapCache& c = g_tma_maps;
+  if (!(c.valid && c.kc == p.kc && c.kr == p.kr && c.v == p.v && c.rows == kv_rows && c.hkv == p.HKV &&
+        c.variant == variant)) {
+    c.valid = false;
+    const int row_c = variant == FFA_K_FP8 ? 128 : (variant == FFA_K_Q2 ? 32 : 64);
+    // L2 promotion no wider than one head's row: a 256-byte promotion on 128-byte rows pulled the
+    // neighbouring head's bytes from DRAM too early to be reused (+15 % DRAM traffic, -11 % speed).
+    const int promo_c = row_c >= 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                     : (row_c >= 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B : CU_TENSOR_MAP_L2_PROMOTION_NONE);
+    const int promo_r = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+    const int promo_v = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    if (!make_map(&c.mc, p.kc, kv_rows, static_cast<int64_t>(p.HKV) * row_c, row_c, variant == FFA_K_FP8, promo_c))
+      return FFA_E_LAUNCH;
+    // without a residual the map is never used; point it at the coarse tensor to keep it valid
+    if (!make_map(&c.mr, p.kr ? p.kr : p.kc, kv_rows, static_cast<int64_t>(p.HKV) * (p.kr ? kResRow : row_c),
+                  p.kr ? kResRow : row_c, p.kr != nullptr, p.kr ? promo_r : promo_c))
+      return FFA_E_LAUNCH;
+    if (!make_map(&c.mv, p.v, kv_rows, static_cast<int64_t>(p.HKV) * kVRow, 128, true, promo_v)) return FFA_E_LAUNCH;
+    c.kc = p.kc; c.kr = p.kr; c.v = p.v; c.rows = kv_rows; c.hkv = p.HKV; c.variant = variant;
+    c.valid = true;
+  }
+  const CUtensorMap &mc = c.mc, &mr = c.mr, &mv = c.mv;
   switch (variant) {
     case FFA_K_FP8:   return launch_fmt<FFA_K_FP8>(p, f8, mc, mr, mv, stream);
     case FFA_K_Q2:    return launch_fmt<FFA_K_Q2>(p, f8, mc, mr, mv, stream);
