@@ -222,6 +222,52 @@ def test_group_sizes():
         check_output(o, ref)
 
 
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("qdt,vdt", [(torch.float32, torch.bfloat16), (torch.float16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float16), (torch.float32, torch.float16)])
+def test_ws_kernel_takes_every_dtype_pair(kind, qdt, vdt):
+    """fp32 q (rounded to fp16 like the reference's q.to(float16)) and the mixed q / V pairs run on the
+    warp-specialised kernel - by name and by default - and match the oracle."""
+    from ffa_speedtest_b200.decode import allocate_decode_workspace
+    B, T, HQ, HKV = 2, 64 * 7 + 9, 8, 2
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, 128, seed=31, n_heavy=3, dtype=torch.float16)
+    q, v = q.to(qdt), v.to(vdt)
+    coarse, res = fo.make_coarse(kind, k, torch.float8_e5m2, 64)
+    ref, parts = fo.decode_attention(q, coarse, v, res, BS=64, delta=4.0, out_dtype=torch.float32, return_parts=True)
+    for kernel in ("ws", "auto"):
+        ws = allocate_decode_workspace(q.cuda(), v.cuda(), BS=64)
+        o = call(kind, q, coarse, v, res, BS=64, delta=4.0, workspace=ws, kernel=kernel)
+        torch.cuda.synchronize()
+        assert ws.status() == 0 and o.dtype == qdt
+        assert band_ok(ws.mask.cpu(), parts["mask"], parts["block_max"], parts["threshold"], HQ // HKV)
+        if torch.equal(ws.mask.cpu(), parts["mask"]):
+            check_output(o, ref)
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("HQ,HKV", [(2, 2), (6, 2), (10, 2), (16, 2)])
+@pytest.mark.parametrize("SBS", [64, 256])
+def test_ws_kernel_group_sizes_and_prune_groups(kind, HQ, HKV, SBS):
+    """GQA groups 1, 3, 5 and 8 (the last two use the second head tile) with pages pruned one by one
+    and in groups of four, against the oracle."""
+    from ffa_speedtest_b200.decode import allocate_decode_workspace
+    B, T = 1, 64 * 13 + 21
+    q, k, v = make_decode_inputs(B, T, HQ, HKV, 128, seed=70 + HQ, n_heavy=3)
+    coarse, res = fo.make_coarse(kind, k, torch.float8_e4m3fn, SBS)
+    ref, parts = fo.decode_attention(q, coarse, v, res, BS=SBS, SBS=SBS, delta=4.0, out_dtype=torch.float32,
+                                     return_parts=True)
+    ws = allocate_decode_workspace(q.cuda(), v.cuda(), BS=SBS, SBS=SBS)
+    o = call(kind, q, coarse, v, res, BS=SBS, SBS=SBS, delta=4.0, workspace=ws, kernel="ws")
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    assert band_ok(ws.mask.cpu(), parts["mask"], parts["block_max"], parts["threshold"], HQ // HKV)
+    if torch.equal(ws.mask.cpu(), parts["mask"]):
+        check_output(o, ref)
+    else:
+        check_output(o, fo.decode_attention(q, coarse, v, res, BS=SBS, SBS=SBS, delta=4.0, out_dtype=torch.float32,
+                                            keep_override=ws.mask.cpu()))
+
+
 def test_partial_out_and_merge_across_sequence_shards():
     """Two sequence halves -> (O, LSE) partials -> ffa_merge_partials == unsplit result."""
     from ffa_speedtest_b200.sharded import merge_partials
