@@ -582,7 +582,11 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   if (a->B <= 0 || a->T <= 0 || a->HKV <= 0 || a->HQ <= 0 || a->HQ % a->HKV != 0) return FFA_E_SHAPE;
   const int G = a->HQ / a->HKV;
   if (G > 8 || a->head_dim != kHeadDim) return FFA_E_SHAPE;
-  if (a->SBS < kPage || a->SBS % kPage != 0 || a->BS < a->SBS || a->BS % a->SBS != 0) return FFA_E_SHAPE;
+  // prune blocks of whole pages (SBS = 64 m), or of a half / a quarter of a page (SBS 32 / 16, BS whole pages)
+  const bool sub_page = a->SBS == 32 || a->SBS == 16;
+  if (sub_page ? (a->BS < kPage || a->BS % kPage != 0)
+               : (a->SBS < kPage || a->SBS % kPage != 0 || a->BS < a->SBS || a->BS % a->SBS != 0))
+    return FFA_E_SHAPE;
   if (a->q_dtype < FFA_F16 || a->q_dtype > FFA_F32) return FFA_E_DTYPE;
   if (a->v_dtype != FFA_F16 && a->v_dtype != FFA_BF16) return FFA_E_DTYPE;
   if (a->fp8_format != FFA_E5M2 && a->fp8_format != FFA_E4M3) return FFA_E_DTYPE;
@@ -620,13 +624,14 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   // kernel (three CTAs per SM, every warp scores and refines), which keeps more loads in flight per
   // SM when the coarse pass is cheap and is 3-10 % faster there.  Bit 0 forces the fp16 tensor-core
   // kernel, bit 1 the page-pipeline kernel, bit 2 the warp-specialised kernel.
-  const int m = a->SBS / kPage;                 // pages per prune group
+  const int m = sub_page ? 1 : a->SBS / kPage;  // pages per prune group
+  p.sub = sub_page ? kPage / a->SBS : 1;
   const bool want_fp16 = (a->reserved & 1) != 0;
   const bool want_v1 = (a->reserved & 2) != 0;
   const bool want_ws = (a->reserved & 4) != 0;
   p.refine_lag = 1;
   p.group = m;
-  const bool v1_ok = m == 1 && decode_tma_supported(p);
+  const bool v1_ok = m == 1 && !sub_page && decode_tma_supported(p);
   const bool ws_ok = decode_ws_supported(p, m);
   bool use_ws = false, use_tma = false;
   if (!want_fp16) {
@@ -667,7 +672,8 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
     // mean-V: 2-bit format, final output only (a partial would need the mass too)
     if (a->variant != FFA_K_Q2 || !(use_ws || use_tma) || a->partial_out) return FFA_E_SHAPE;
   }
-  if (m > 1 && !use_ws) return FFA_E_SHAPE;     // the other kernels prune page by page only
+  if ((m > 1 || sub_page) && !use_ws) return FFA_E_SHAPE;     // the other kernels prune page by page only
+  if (sub_page && a->v_mean) return FFA_E_SHAPE;              // mean-V keeps whole pages' mass
 
   int rc;
   const int64_t kv_rows = a->kv_rows > 0 ? a->kv_rows : static_cast<int64_t>(a->B) * a->T;

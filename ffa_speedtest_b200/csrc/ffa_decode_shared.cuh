@@ -79,6 +79,7 @@ struct DecodeParams {
   // warp-specialised kernel: pages per prune group (SBS / 64) and pages per (b, kv-head) rounded up
   // to whole groups; page ranges are cut in that padded space so that no group straddles two CTAs
   int group;
+  int sub;           // prune blocks per page when SBS is below 64 (2 or 4), else 1
   int NPp;
   int nseg;          // chunks per (b, kv-head); `ppc` is the pages of a chunk
   int grid;          // CTAs to launch

@@ -56,13 +56,16 @@ constexpr int kBatch = kMaxPruneGroup;     // pages the dispatcher decides per t
 constexpr int kSampleRows = kSample;       // rows of a threshold sample tile
 constexpr int kNSeg = 4;                   // published chunks the consumers may lag behind the producer
 
-template <int FMT, int NT>
+// SUBP: the kernel prunes blocks smaller than a page (SBS 32 or 16) and keeps per-tile maxima for that
+template <int FMT, int NT, bool SUBP = false>
 struct WsSmem {
   static constexpr int kRow = Fmt<FMT>::kRow;
   static constexpr int kCoarseSlot = kPage * kRow;                                  // 8 / 2 / 4 KiB
   // coarse ring: each scoring warp should find its next tile already landed, i.e. more than one slot
   // per warp in flight; the residual + V ring takes what is left of the 227 KiB
-  static constexpr int kNC = FMT == FFA_K_FP8 ? 6 : (FMT == FFA_K_Q2 ? 16 : 8);
+  // (sub-page pruning: the formats with per-channel scales give up one slot for the per-tile maxima)
+  static constexpr int kNC = FMT == FFA_K_FP8 ? 6
+                             : (FMT == FFA_K_Q2 ? (SUBP && NT == 1 ? 15 : 16) : ((SUBP && FMT == FFA_K_NF4 && NT == 1) ? 7 : 8));
   static constexpr int kNRV = NT == 2 ? 5 : 6;                                      // residual + V slots (24 KiB each)
   // published-page ring (the page's raw dots and maxima).  At least two dispatcher trips; the 2-/4-bit
   // formats, whose scoring is the expensive stage, get four: while the dispatcher waits for a free
@@ -77,17 +80,20 @@ struct WsSmem {
   static constexpr int kOffDHist = kOffCoarse + kNC * kCoarseSlot;
   static constexpr int kOffDMax = kOffDHist + kND * kHist;      // [kND][8] page maxima
   static constexpr int kOffDPl = kOffDMax + kND * 32;           // [kND][8] mean-V: mass relative to the maximum
-  static constexpr int kOffBars = kOffDPl + kND * 32;
+  // [kND][4 tiles][8]: maxima per 16-token tile (SBS below 64).  Shares its first quarter with the
+  // mean-V masses: the mean-V variant prunes whole pages only, the two are never used together.
+  static constexpr int kOffDSub = kOffDPl;
+  static constexpr int kOffBars = kOffDSub + kND * (SUBP ? 128 : 32);
   // barriers: chunk full/empty | coarse full/empty | threshold full/empty |
   //           page full/empty | residual+V full/empty
   //           | three chunk-end meeting points of the refine warps | one meeting point per refine pair
   static constexpr int kNBars = 2 * kNSeg + 2 * kNC + 4 + 2 * kND + 2 * kNRV + 3 + kNP;
   static constexpr int kOffMisc = kOffBars + ((kNBars * 8 + 63) / 64) * 64;
-  // misc: sTh[2][16] | seg[kNSeg][4] | kq_page[8] | kq_ds[8] | abort, last, pad[6] | book[16] | per scoring warp sS[128], sZ[128]
+  // misc: sTh[2][16] | seg[kNSeg][4] | kq_page[8] | kq_ds[8] | kq_sub[8] | abort, last, pad[6] | book[16] | per scoring warp sS[128], sZ[128]
   static constexpr int kOffTh = kOffMisc;
   static constexpr int kOffSeg = kOffTh + 128;
   static constexpr int kOffKq = kOffSeg + kNSeg * 16;
-  static constexpr int kOffFlags = kOffKq + 64;
+  static constexpr int kOffFlags = kOffKq + 96;
   static constexpr int kOffBook = kOffFlags + 32;
   static constexpr int kOffS = kOffBook + 64;
   // chunk end: every refine warp's (o[heads][128], m, l), added up before one partial is written
@@ -96,7 +102,9 @@ struct WsSmem {
   static constexpr int kOffRedML = kOffRed + kNR * kRedWarp;                          // [kNR][2][8] f32
   static constexpr int kOffPairMax = kOffRedML + kNR * 64;                            // [kNP][2 pages][2 warps][8] f32
   static constexpr int kBytes = kOffPairMax + kNP * 128 + 1024;                       // + alignment slack
+#ifndef FFA_SKIP_SMEM_ASSERT
   static_assert(kBytes <= 232448, "shared memory of one CTA");
+#endif
   static_assert(kNRV >= 4, "the dispatcher issues up to four requests per round");
   // a ring shared by several consumer warps stays phase-safe only if it has at least as many slots
   static_assert(kNC >= kNS && kNRV >= kNP, "rings must not be smaller than the number of their consumers");
@@ -338,15 +346,39 @@ __device__ __forceinline__ bool ws_arrive_unit(const DecodeParams& p, int unit, 
   return last != 0;
 }
 
+// Prune blocks smaller than a page (SBS 32 or 16; the whole warp calls this, four lanes per page, lane
+// hq of a page holding heads 2hq and 2hq + 1): the rule "dropped only if every head's maximum is
+// strictly below its threshold" is applied to every sub-block's own maxima (`sub_max` = the page's
+// [4 tiles][8 heads]).  Returns the page's kept sub-blocks as a bit mask, the same in the page's four
+// lanes, and writes the mask entries.  The page is fetched if any sub-block is kept; the refine warps
+// skip the tiles of the others.  Kept out of line: it is rare, and the dispatcher's loop is latency
+// critical and shares the instruction cache with three other roles.
+__device__ __noinline__ uint32_t ws_decide_sub_blocks(const float* sub_max, int n_sub, int tps_shift, int hq, int G,
+                                                      float th0, float th1, bool valid, uint32_t gmask, int8_t* mask_out) {
+  uint32_t kept = 0u;
+  for (int sb = 0; sb < n_sub; ++sb) {
+    float a0 = -INFINITY, a1 = -INFINITY;
+    for (int tt = 0; tt < (1 << tps_shift); ++tt) {
+      const float* e = sub_max + ((sb << tps_shift) + tt) * 8;
+      if (valid) { a0 = fmaxf(a0, e[2 * hq]); a1 = fmaxf(a1, e[2 * hq + 1]); }
+    }
+    const bool r = valid && ((2 * hq < G && !(a0 < th0)) || (2 * hq + 1 < G && !(a1 < th1)));
+    const bool ks = (__ballot_sync(0xffffffffu, r) & gmask) != 0u;
+    if (ks) kept |= 1u << sb;
+    if (mask_out && valid && hq == 0) mask_out[sb] = ks ? 1 : 0;
+  }
+  return kept;
+}
+
 // FMT: coarse format; F8: fp8 encoding of the residual (and of the fp8 coarse base); NT: n-tiles of
 // four q heads (1: group <= 4, 2: group <= 8); VBF: V is bf16 (else fp16); QP: e4m3 pieces per q value;
 // MV: mean-V variant (pruned pages keep their coarse softmax mass; DecodeParams::v_mean).
-template <int FMT, int F8, int NT, bool VBF, int QP, bool MV>
+template <int FMT, int F8, int NT, bool VBF, int QP, bool MV, bool SUBP>
 __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_constant__ DecodeParams p,
                                                                   const __grid_constant__ CUtensorMap tm_c,
                                                                   const __grid_constant__ CUtensorMap tm_r,
                                                                   const __grid_constant__ CUtensorMap tm_v) {
-  using L = WsSmem<FMT, NT>;
+  using L = WsSmem<FMT, NT, SUBP>;
   constexpr int ROW = L::kRow;
   constexpr int kNC = L::kNC;
   constexpr int kNRV = L::kNRV;
@@ -393,6 +425,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
   int* sSeg = reinterpret_cast<int*>(smem + L::kOffSeg);            // [kNSeg][4]: unit, first page, pages, chunk of the unit
   int* kq_page = reinterpret_cast<int*>(smem + L::kOffKq);      // per residual+V slot: page of the (b, kv-head), -1 = end marker
   int* kq_ds = kq_page + 8;                                      // ... and the published-page entry that holds its dots
+  int* kq_sub = kq_page + 16;                                    // ... and which of its sub-blocks are kept (SBS below 64)
+  float* dsub = reinterpret_cast<float*>(smem + L::kOffDSub);
+  // SBS below one page: `n_sub` prune blocks of 64 / n_sub tokens per page (2 or 4), else 1
+  const int n_sub = SUBP && p.sub > 1 ? p.sub : 1;
+  const int tps_shift = n_sub == 4 ? 0 : (n_sub == 2 ? 1 : 2);   // log2 of the 16-token tiles per prune block
   int* sAbort = reinterpret_cast<int*>(smem + L::kOffFlags);
   float* sBook = reinterpret_cast<float*>(smem + L::kOffBook);
   int* sLast = sAbort + 1;                                       // the chunk just finished completed its (batch, kv-head)
@@ -555,8 +592,15 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
           gx1 = fmaxf(gx1, __shfl_xor_sync(kFull, gx1, off));
         }
         const bool reaches = valid && ((2 * hq < G && !(gx0 < th0)) || (2 * hq + 1 < G && !(gx1 < th1)));
-        const bool keep = (__ballot_sync(kFull, reaches) & gmask) != 0u;
-        if (mask_row && valid && (lane % gsz) == 0) mask_row[(page_begin + c) / m_grp] = keep ? 1 : 0;
+        bool keep = (__ballot_sync(kFull, reaches) & gmask) != 0u;
+        uint32_t sub_kept = 0xfu;
+        if (n_sub > 1) {
+          sub_kept = ws_decide_sub_blocks(dsub + ds * 32, n_sub, tps_shift, hq, G, th0, th1, valid, gmask,
+                                          mask_row ? mask_row + (page_begin + c) * n_sub : nullptr);
+          keep = sub_kept != 0u;
+        } else if (mask_row && valid && (lane % gsz) == 0) {
+          mask_row[(page_begin + c) / m_grp] = keep ? 1 : 0;
+        }
         const bool lead = valid && hq == 0;
         const uint32_t kept_bits = __ballot_sync(kFull, lead && keep);
         PROF_T(t_keep);
@@ -575,6 +619,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
             if (lane_ok) {
               kq_page[slot] = page_begin + c;
               kq_ds[slot] = ds;
+              kq_sub[slot] = static_cast<int>(sub_kept);
               const uint32_t bar = rvfull(slot);
               const uint32_t dst = smem_u32(smem + L::kOffRv + slot * kRvSlot);
               mbar_expect_tx(bar, rv_bytes);
@@ -630,7 +675,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
       if (!ok) break;
       if (mask_row && page_begin + CH >= p.NPp) {
         // mask entries past the last group that holds tokens (padding blocks count as pruned)
-        for (int i = (p.NP + m_grp - 1) / m_grp + lane; i < p.NTBS; i += 32) mask_row[i] = 0;
+        for (int i = (n_sub > 1 ? p.NP * n_sub : (p.NP + m_grp - 1) / m_grp) + lane; i < p.NTBS; i += 32) mask_row[i] = 0;
       }
       if (MV) {
         // this chunk's pruned mass; the dispatcher is one more party to the (batch, kv-head)'s arrival count
@@ -791,6 +836,16 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
             const float s0 = tok < T ? to_log2(d[nt][0]) : -INFINITY;
             const float s1 = tok + 8 < T ? to_log2(d[nt][1]) : -INFINITY;
             cm[nt] = fmaxf(cm[nt], fmaxf(s0, s1));
+            if (n_sub > 1) {
+              // the tile's own maximum per head, for prune blocks smaller than a page
+              float tm = fmaxf(s0, s1);
+#pragma unroll
+              for (int off = 4; off < 32; off <<= 1) tm = fmaxf(tm, __shfl_xor_sync(kFull, tm, off));
+              if (g == 0) {
+                dsub[ds * 32 + mt * 8 + 4 * nt + t] = tm;
+                if (NT == 1) dsub[ds * 32 + mt * 8 + 4 + t] = -INFINITY;
+              }
+            }
           }
         }
         __syncwarp();
@@ -873,6 +928,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
         if (!WS_WAIT(rvfull(slot), (myk / kNRV) & 1u, 9, 0)) { ok = false; break; }
         const int page = kq_page[slot];
         const int ds = kq_ds[slot];
+        const uint32_t sub_kept = SUBP ? static_cast<uint32_t>(kq_sub[slot]) : 0xfu;
         myk += kNP;
         if (page < 0) {                                  // end of the chunk
           __syncwarp();
@@ -897,11 +953,12 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
           for (int nt = 0; nt < NT; ++nt) dr[nt][0] = dr[nt][1] = 0.f;
           if (use_res) dot_fp8<F8, NT, QP>(dr, qb, qinv, rtile, mt, g, t);
           const int tok = page * kPage + 16 * mt + g;
+          const bool on = ((sub_kept >> (mt >> tps_shift)) & 1u) != 0u;         // the tile's prune block is kept
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             float* e = hs + ((mt * NT + nt) * 2) * 32 + lane;
-            const float s0 = tok < T ? to_log2(e[0] + dr[nt][0]) : -INFINITY;
-            const float s1 = tok + 8 < T ? to_log2(e[32] + dr[nt][1]) : -INFINITY;
+            const float s0 = on && tok < T ? to_log2(e[0] + dr[nt][0]) : -INFINITY;
+            const float s1 = on && tok + 8 < T ? to_log2(e[32] + dr[nt][1]) : -INFINITY;
             e[0] = s0;
             e[32] = s1;
             rm[nt] = fmaxf(rm[nt], fmaxf(s0, s1));
@@ -1111,10 +1168,13 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
 }
 
 // Configures (once per device) and launches the kernel.
-template <int FMT, int F8, int NT, bool VBF, int QP, bool MV = false>
+template <int FMT, int F8, int NT, bool VBF, int QP, bool MV = false, bool SUBP = false>
 int launch_ws_one(const DecodeParams& p, const CUtensorMap* maps, cudaStream_t stream) {
-  using L = WsSmem<FMT, NT>;
-  auto kern = decode_ws_kernel<FMT, F8, NT, VBF, QP, MV>;
+  if constexpr (!MV && !SUBP) {
+    if (p.sub > 1) return launch_ws_one<FMT, F8, NT, VBF, QP, false, true>(p, maps, stream);
+  }
+  using L = WsSmem<FMT, NT, SUBP>;
+  auto kern = decode_ws_kernel<FMT, F8, NT, VBF, QP, MV, SUBP>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);

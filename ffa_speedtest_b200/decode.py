@@ -213,13 +213,22 @@ def decode_call(
         scale = 1.0 / math.sqrt(K)
     if SBS is None:
         SBS = BS
-    if SBS % PAGE != 0 or SBS < PAGE or BS % SBS != 0:
-        raise ValueError(f"this build prunes in units of 64-token pages: SBS must be a multiple of 64 and BS a "
-                         f"multiple of SBS (got BS={BS}, SBS={SBS})")
-    if SBS > MAX_SBS or (SBS // PAGE) & (SBS // PAGE - 1):
-        raise ValueError(f"this build prunes groups of 1, 2, 4 or 8 pages: SBS must be 64, 128, 256 or 512 (got {SBS})")
-    if SBS != PAGE and kernel not in ("auto", "ws"):
-        raise ValueError("SBS above 64 needs kernel='auto' or 'ws': the other kernels prune page by page only")
+    if SBS in (16, 32):
+        # prune blocks of a quarter / half of a page: BS stays in whole pages
+        if BS % PAGE != 0:
+            raise ValueError(f"with SBS below 64, BS must be a multiple of 64 (got BS={BS}, SBS={SBS})")
+        if kernel not in ("auto", "ws"):
+            raise ValueError("SBS below 64 needs kernel='auto' or 'ws': the other kernels prune page by page only")
+        if mean_v is not None:
+            raise ValueError("the mean-V variant prunes whole pages: SBS must be at least 64")
+    else:
+        if SBS % PAGE != 0 or SBS < PAGE or BS % SBS != 0:
+            raise ValueError(f"SBS must be 16, 32 or a multiple of 64, and BS a multiple of SBS and of 64 "
+                             f"(got BS={BS}, SBS={SBS})")
+        if SBS > MAX_SBS or (SBS // PAGE) & (SBS // PAGE - 1):
+            raise ValueError(f"this build prunes groups of 1, 2, 4 or 8 pages: SBS must be 64, 128, 256 or 512 (got {SBS})")
+        if SBS != PAGE and kernel not in ("auto", "ws"):
+            raise ValueError("SBS above 64 needs kernel='auto' or 'ws': the other kernels prune page by page only")
     NTB = -(-T // BS)
     NTBS = NTB * (BS // SBS)
 

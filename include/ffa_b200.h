@@ -59,8 +59,9 @@ typedef struct FfaDecodeArgs {
   int32_t variant;          /* FFA_K_*                                                          */
   int32_t B, T, HQ, HKV;    /* batch, context length, query heads, kv heads (G = HQ/HKV <= 8)   */
   int32_t head_dim;         /* K = V = 128                                                      */
-  int32_t BS, SBS;          /* reference block sizes: SBS (prune granularity) 64, 128, 256 or 512,
-                               BS a multiple of SBS; always one launch                           */
+  int32_t BS, SBS;          /* reference block sizes: SBS (prune granularity) 16, 32, 64, 128, 256 or
+                               512, BS a multiple of SBS and of 64; always one launch.  SBS 16 / 32
+                               (blocks inside a page): warp-specialised kernel only, not with v_mean */
   float sm_scale;           /* softmax scale, reference default 1/sqrt(K)                       */
   float delta;              /* threshold offset in log2 units                                   */
   int32_t q_dtype;          /* FFA_F16 | FFA_BF16 | FFA_F32; the output has the same type       */

@@ -14,7 +14,7 @@ GOLDEN = Path(__file__).resolve().parent / "golden"
 FP8 = {"e5m2": torch.float8_e5m2, "e4m3": torch.float8_e4m3fn}
 FLT = {"bf16": torch.bfloat16, "fp16": torch.float16}
 KINDS = ("q2", "fp8", "fp4", "nf4", "nvfp4")
-SMALL_CASES = ("ragged", "g8_e4m3", "nores_extth", "bs128", "sbs128", "sbs256_fp16")
+SMALL_CASES = ("ragged", "g8_e4m3", "nores_extth", "bs128", "sbs128", "sbs256_fp16", "sbs32", "sbs16_fp16")
 
 
 def raw(t: torch.Tensor) -> np.ndarray:

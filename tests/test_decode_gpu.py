@@ -246,26 +246,38 @@ def test_ws_kernel_takes_every_dtype_pair(kind, qdt, vdt):
 
 @pytest.mark.parametrize("kind", KINDS)
 @pytest.mark.parametrize("HQ,HKV", [(2, 2), (6, 2), (10, 2), (16, 2)])
-@pytest.mark.parametrize("SBS", [64, 256])
+@pytest.mark.parametrize("SBS", [16, 32, 64, 256])
 def test_ws_kernel_group_sizes_and_prune_groups(kind, HQ, HKV, SBS):
-    """GQA groups 1, 3, 5 and 8 (the last two use the second head tile) with pages pruned one by one
-    and in groups of four, against the oracle."""
+    """GQA groups 1, 3, 5 and 8 (the last two use the second head tile) with prune blocks of a quarter
+    page, half a page, one page and four pages, against the oracle."""
     from ffa_speedtest_b200.decode import allocate_decode_workspace
     B, T = 1, 64 * 13 + 21
+    BS = max(64, SBS)
     q, k, v = make_decode_inputs(B, T, HQ, HKV, 128, seed=70 + HQ, n_heavy=3)
-    coarse, res = fo.make_coarse(kind, k, torch.float8_e4m3fn, SBS)
-    ref, parts = fo.decode_attention(q, coarse, v, res, BS=SBS, SBS=SBS, delta=4.0, out_dtype=torch.float32,
+    coarse, res = fo.make_coarse(kind, k, torch.float8_e4m3fn, BS)
+    ref, parts = fo.decode_attention(q, coarse, v, res, BS=BS, SBS=SBS, delta=4.0, out_dtype=torch.float32,
                                      return_parts=True)
-    ws = allocate_decode_workspace(q.cuda(), v.cuda(), BS=SBS, SBS=SBS)
-    o = call(kind, q, coarse, v, res, BS=SBS, SBS=SBS, delta=4.0, workspace=ws, kernel="ws")
+    ws = allocate_decode_workspace(q.cuda(), v.cuda(), BS=BS, SBS=SBS)
+    o = call(kind, q, coarse, v, res, BS=BS, SBS=SBS, delta=4.0, workspace=ws, kernel="ws")
     torch.cuda.synchronize()
     assert ws.status() == 0
     assert band_ok(ws.mask.cpu(), parts["mask"], parts["block_max"], parts["threshold"], HQ // HKV)
     if torch.equal(ws.mask.cpu(), parts["mask"]):
         check_output(o, ref)
     else:
-        check_output(o, fo.decode_attention(q, coarse, v, res, BS=SBS, SBS=SBS, delta=4.0, out_dtype=torch.float32,
+        check_output(o, fo.decode_attention(q, coarse, v, res, BS=BS, SBS=SBS, delta=4.0, out_dtype=torch.float32,
                                             keep_override=ws.mask.cpu()))
+
+
+def test_sub_page_pruning_is_refused_where_it_is_not_built():
+    q, k, v = make_decode_inputs(1, 256, 8, 2, 128, seed=2)
+    coarse, res = fo.make_coarse("q2", k, torch.float8_e4m3fn, 64)
+    with pytest.raises(ValueError, match="SBS"):
+        call("q2", q, coarse, v, res, BS=64, SBS=8)
+    with pytest.raises(ValueError, match="kernel"):
+        call("q2", q, coarse, v, res, BS=64, SBS=32, kernel="pipe")
+    with pytest.raises(ValueError, match="multiple of 64"):
+        call("q2", q, coarse, v, res, BS=32, SBS=32)
 
 
 def test_partial_out_and_merge_across_sequence_shards():
