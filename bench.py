@@ -369,14 +369,20 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
         return decode_call(kind, q_dev, ck, vk, k_scale=scale, k_zero=zero, k_residual=rk, BS=PAGE, SBS=PAGE,
                            delta=delta, precomputed_threshold=th, workspace=ws, partial_out=partial_out, out=out)
 
-    runner = None
+    runner = peer = None
     if world > 1:
+        # the step: local decode, then the exchange over peer memory fused with the merge.  The
+        # library-only way (NCCL all-gather + merge kernel) is timed next to it.
         runner = sharded.SequenceShardedDecode(dist.group.WORLD, B, HQ, dev, q.dtype)
-        step = lambda: runner.step(local)
+        peer = sharded.PeerShardedDecode(dist.group.WORLD, B, HQ, dev, q.dtype)
+        step = lambda: peer.step(local)
+        o_nccl = runner.step(local).clone()
     else:
         step = lambda: local()
     o = step()
     torch.cuda.synchronize()
+    if peer is not None and not torch.equal(o, o_nccl):
+        raise SystemExit("peer-memory exchange + merge differs from all-gather + merge")
     err_vs_unsplit = float((o.float() - o_full).abs().max())
     th_err = float((th - th_full).abs().max())
     kept_local = float(ws.mask.float().mean())
@@ -408,6 +414,10 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     ms_local = timed(lambda: local(partial_out=runner.local) if runner else local(), steps)
     ms_gather = timed(runner.gather, steps) if runner else 0.0
     ms_merge = timed(runner.merge, steps) if runner else 0.0
+    ms_nccl = timed(lambda: runner.step(local), steps) if runner else 0.0
+    ms_exchange = timed(peer.exchange_and_merge, steps) if peer else 0.0
+    if peer is not None and int(peer.status[0]) != 0:
+        raise SystemExit("a bounded wait of the peer-memory exchange gave up (status word set): results are invalid")
 
     q_host = q.cpu().pin_memory()
     o_host = torch.empty((B, HQ, D), dtype=q.dtype).pin_memory()
@@ -428,8 +438,8 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     s_e2e = (time.perf_counter() - t0) / n_e2e
     if ws.status() != 0:
         raise SystemExit("a bounded wait inside the decode kernel gave up (status word set): results are invalid")
-    t = torch.tensor([ms, s_e2e, step_bytes, kept_local, ms_local, ms_gather, ms_merge, err_vs_unsplit, us_unsplit],
-                     dtype=torch.float64, device=dev)
+    t = torch.tensor([ms, s_e2e, step_bytes, kept_local, ms_local, ms_gather, ms_merge, err_vs_unsplit, us_unsplit,
+                      ms_nccl, ms_exchange], dtype=torch.float64, device=dev)
     tmax, tsum = t.clone(), t.clone()
     if world > 1:
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
@@ -448,21 +458,26 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
                        "kept_fraction": float(tsum[3]) / world, "pages_per_rank": hi - lo,
                        "algorithmic_bytes_per_step": job_bytes, "cuda_graph": False,
                        "l2": "inputs_larger_than_l2 (no flush)",
-                       "sharding": "sequence split: page range per rank, all-gather of [B,HQ,129] partials + merge"},
+                       "sharding": "sequence split: page range per rank, [B,HQ,129] partials exchanged over peer memory "
+                                   "and merged by one fused call (NCCL all-gather + merge timed beside it)"},
             "roofline": {"bound": "hbm", "achieved": job_bytes / world / per_step_s / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": job_bytes / world / per_step_s / 1e9 / peak, "peak_source": peak_kind, "traffic": None,
-                         "note": "per-GPU rate of the whole step (local decode + all-gather + merge)"},
+                         "note": "per-GPU rate of the whole step (local decode + exchange + merge)"},
             "seqsplit": {"us_per_step": per_step_s * 1e6, "value": job_bytes / per_step_s / 1e12,
                          "unsplit_us_per_step_on_one_gpu": float(tmax[8]),
                          "speedup_vs_unsplit": float(tmax[8]) / (per_step_s * 1e6),
                          "max_abs_err_vs_unsplit": float(tmax[7]), "threshold_max_abs_diff": th_err,
-                         "local_decode_us": float(tmax[4]) * 1e3 / steps, "allgather_us": float(tmax[5]) * 1e3 / steps,
-                         "merge_us": float(tmax[6]) * 1e3 / steps, "kept_fraction_unsplit": kept_full},
+                         "local_decode_us": float(tmax[4]) * 1e3 / steps,
+                         "peer_exchange_merge_us": float(tmax[10]) * 1e3 / steps,
+                         "nccl_step_us": float(tmax[9]) * 1e3 / steps, "nccl_allgather_us": float(tmax[5]) * 1e3 / steps,
+                         "merge_kernel_us": float(tmax[6]) * 1e3 / steps, "kept_fraction_unsplit": kept_full},
             "e2e": {"value": job_bytes / float(tmax[1]) / 1e12, "unit": UNIT, "h2d_bytes_per_step": q_host.numel() * 2,
                     "d2h_bytes_per_step": o_host.numel() * 2, "us_per_step": float(tmax[1]) * 1e6, "steps": n_e2e},
-            "gpu_launches": steps * (1 if world == 1 else 2),     # decode (+ merge); the all-gather is NCCL's
+            "gpu_launches": steps * (1 if world == 1 else 3),     # decode (+ peer push + wait-and-merge)
             "clocks": clocks,
         }
+    if peer is not None:
+        peer.close()
     if world > 1 and own_group:
         dist.destroy_process_group()
     return out

@@ -100,6 +100,14 @@ def lib() -> C.CDLL:
         getattr(L, name).restype = C.c_int
     L.ffa_cache_append.argtypes = [i32, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, i32, vp]
     L.ffa_cache_append.restype = C.c_int
+    L.ffa_peer_exchange_merge.argtypes = [vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), i32, vp, i32, vp, vp]
+    L.ffa_peer_exchange_merge.restype = C.c_int
+    L.ffa_peer_alloc.argtypes = [C.c_size_t, C.POINTER(vp), C.c_char_p]
+    L.ffa_peer_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    L.ffa_peer_close.argtypes = [vp]
+    L.ffa_peer_free.argtypes = [vp]
+    for name in ("ffa_peer_alloc", "ffa_peer_open", "ffa_peer_close", "ffa_peer_free"):
+        getattr(L, name).restype = C.c_int
     L.ffa_quantize_append.argtypes = [i32, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp]
     L.ffa_quantize_append.restype = C.c_int
     L.ffa_kproj_rope.argtypes = [C.POINTER(FfaKprojArgs), C.c_void_p]

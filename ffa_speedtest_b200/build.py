@@ -16,7 +16,7 @@ CSRC = PKG / "csrc"
 OUT = PKG / "libffa_b200.so"
 SOURCES = ["ffa_lib.cu", "ffa_decode.cu", "ffa_decode_tma.cu", "ffa_decode_ws.cu", "ffa_decode_ws_fp8.cu",
            "ffa_decode_ws_q2.cu", "ffa_decode_ws_fp4.cu", "ffa_decode_ws_nf4.cu", "ffa_decode_ws_nvfp4.cu",
-           "ffa_quantize.cu", "ffa_kproj.cu", "ffa_static.cu"]
+           "ffa_quantize.cu", "ffa_kproj.cu", "ffa_static.cu", "ffa_peer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--use_fast_math=false",

@@ -82,6 +82,31 @@ def kproj_reference(variant, h, w_k, cos, sin, num_kv_heads, head_dim, bias=None
     return _QUANT[variant](k.contiguous(), fp8_dtype, page_size)
 
 
+_WORKSPACES: dict = {}
+
+
+def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
+    """Scratch of the fused call (post-RoPE K for the two-pass formats, split-K partials, status word in
+    the last 256 bytes).  Few-token calls - a decode loop makes one per layer and token - keep theirs per
+    (device, stream, size): an allocation plus a memset per call cost as much as the kernel itself, calls
+    on one stream run in order, and the status word is only ever written by a kernel whose bounded wait
+    gave up.  Larger (prompt-sized) workspaces are made per call."""
+    if nbytes > (8 << 20):
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        ws[-256:].zero_()
+        return ws
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream, nbytes)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        if len(_WORKSPACES) >= 64:
+            _WORKSPACES.clear()
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        ws[-256:].zero_()
+        _WORKSPACES[key] = ws
+    return ws
+
+
 def kproj_fused(variant: Optional[str], h, w_k, cos, sin, num_kv_heads, head_dim, bias=None, fp8_dtype=None,
                 page_size: int = PAGE, *, block_table: Optional[torch.Tensor] = None, out=None,
                 return_k: bool = False, position: int = 0):
@@ -127,8 +152,7 @@ def kproj_fused(variant: Optional[str], h, w_k, cos, sin, num_kv_heads, head_dim
 
     k_rope = torch.empty((B, T, HKV, head_dim), dtype=k_dtype, device=dev) if (return_k or variant is None) else None
     a.k_rope_out = _lib.ptr(k_rope)
-    ws = torch.empty(_lib.lib().ffa_kproj_workspace_bytes(B, T, HKV, a.rope_dtype), dtype=torch.uint8, device=dev)
-    ws[-256:].zero_()
+    ws = _workspace(_lib.lib().ffa_kproj_workspace_bytes(B, T, HKV, a.rope_dtype), dev)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
 
     outs = ()

@@ -137,3 +137,94 @@ class SequenceShardedDecode:
         local_decode(partial_out=self.local)
         self.gather()
         return self.merge()
+
+
+class _DeviceArray:
+    """A device buffer owned by the library, seen by torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+class PeerShardedDecode:
+    """Sequence-split decode step whose exchange runs over peer memory, fused with the merge.
+
+    Same contract as ``SequenceShardedDecode`` (every rank holds a page range of every sequence and the
+    same thresholds; ``step`` returns the merged ``[B, HQ, 128]`` output on every rank), but instead of an
+    NCCL all-gather followed by the merge kernel, each rank stores its ``[B, HQ, 129]`` partial straight
+    into its slot of every peer's buffer (plain peer stores over NVLink, buffers mapped through CUDA
+    IPC) and raises a flag there; the merge kernel waits, for at most a second, for all flags of the step
+    and merges from local memory (``ffa_peer_exchange_merge``).  One box only: every rank must be able
+    to map every other rank's memory.  ``close()`` unmaps and frees; call it on every rank."""
+
+    def __init__(self, group, B: int, HQ: int, device, out_dtype: torch.dtype):
+        import ctypes as C
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 16:
+            raise ValueError("at most 16 ranks")
+        self.rows = B * HQ
+        self.device = torch.device(device)
+        L = _lib.lib()
+        n_part = self.rows * 129
+        self._gather_bytes = 2 * self.world * n_part * 4
+        total = self._gather_bytes + 256                       # + the flags, one int per rank
+        with torch.cuda.device(self.device):
+            ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+            _lib.check(L.ffa_peer_alloc(total, C.byref(ptr), handle), "ffa_peer_alloc")
+            self._own = ptr.value
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            self._bases = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self._bases.append(self._own)
+                    continue
+                p = C.c_void_p()
+                _lib.check(L.ffa_peer_open(h, C.byref(p)), "ffa_peer_open")
+                self._bases.append(p.value)
+        self._gathered_ptrs = (C.c_void_p * self.world)(*self._bases)
+        self._flag_ptrs = (C.c_void_p * self.world)(*[b + self._gather_bytes for b in self._bases])
+        # this rank's two slots, as tensors the decode kernel writes its partial into
+        holder = _DeviceArray(self._own, (2, self.world, B, HQ, 129), "<f4")
+        self.gathered = torch.as_tensor(holder, device=self.device)
+        self._holder = holder
+        self.out = torch.empty((B, HQ, 128), dtype=out_dtype, device=self.device)
+        self.status = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.step_no = 0
+        dist.barrier(group=group)
+
+    def local_slot(self) -> torch.Tensor:
+        """Where the NEXT step's local partial goes: ``[B, HQ, 129]``."""
+        return self.gathered[(self.step_no + 1) & 1, self.rank]
+
+    def step(self, local_decode) -> torch.Tensor:
+        local_decode(partial_out=self.local_slot())
+        return self.exchange_and_merge()
+
+    def exchange_and_merge(self) -> torch.Tensor:
+        """The part of a step after the local decode: push the partial in ``local_slot()`` to every peer,
+        wait for theirs, merge.  Every rank must call it the same number of times."""
+        slot = self.local_slot()
+        self.step_no += 1
+        _lib.check(_lib.lib().ffa_peer_exchange_merge(
+            slot.data_ptr(), self.rows, self.rank, self.world, self._gathered_ptrs, self._flag_ptrs, self.step_no,
+            self.out.data_ptr(), _lib.float_code(self.out.dtype), self.status.data_ptr(),
+            _lib.current_stream(self.device)), "ffa_peer_exchange_merge")
+        return self.out
+
+    def close(self) -> None:
+        if getattr(self, "_own", None) is None:
+            return
+        torch.cuda.synchronize(self.device)
+        self.dist.barrier(group=self.group)                  # nobody is still storing into a peer
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            for r, b in enumerate(self._bases):
+                if r != self.rank:
+                    L.ffa_peer_close(b)
+            self.dist.barrier(group=self.group)              # every mapping is gone before the owners free
+            del self.gathered
+            L.ffa_peer_free(self._own)
+        self._own = None

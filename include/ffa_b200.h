@@ -177,6 +177,35 @@ int ffa_quantize_nvfp4(const void* k, int32_t k_dtype, int32_t B, int32_t T, int
                        int32_t page_size, uint8_t* codes, void* scale, uint8_t* residual, ffa_stream_t stream);
 
 /*
+ * Sequence-split decode across the GPUs of one box, the exchange fused with the merge (no reference
+ * counterpart; the reference is single-GPU).  Every rank has produced its partial [rows, 129] of this
+ * step (ffa_decode with partial_out pointing at slot [step & 1][rank] of its own gathered buffer).  This
+ * call stores the partial into the same slot of every peer's gathered buffer over peer memory, raises
+ * this rank's flag on every peer to `step`, then waits (at most one second) until all `world` flags of
+ * this rank carry `step` and merges the world partials into out [rows, 128].
+ *   peer_gathered[p]: device pointer, valid on this GPU, to rank p's buffer [2, world, rows, 129] fp32
+ *                     (p == rank: the local buffer; others mapped through CUDA IPC by the caller)
+ *   peer_flags[p]:    likewise rank p's int32 flags [world], zero before the first step
+ *   step:             1, 2, 3, ... the same on every rank; buffers alternate by its parity
+ * Both pointer arrays are host arrays of `world` (<= 16) entries, read during the call.  A wait that
+ * gives up sets status[0] = 3 (if status is given) and writes NaN rows.  Plain peer stores and loads
+ * only.  Replaces an all-gather of the partials followed by ffa_merge_partials.
+ */
+int ffa_peer_exchange_merge(const float* local_partial, int32_t rows, int32_t rank, int32_t world,
+                            float* const* peer_gathered, int32_t* const* peer_flags, int32_t step, void* out,
+                            int32_t out_dtype, int32_t* status, ffa_stream_t stream);
+
+/* Set-up for ffa_peer_exchange_merge (these four allocate, map or free; none belongs in a step):
+ * ffa_peer_alloc makes a zeroed device buffer on the current device and its 64-byte inter-process
+ * handle; another process of the same box maps it on ITS current device with ffa_peer_open (peer access
+ * is enabled by the driver on first use) and unmaps it with ffa_peer_close before the owner frees it
+ * with ffa_peer_free. */
+int ffa_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int ffa_peer_open(const unsigned char* handle64, void** ptr);
+int ffa_peer_close(void* ptr);
+int ffa_peer_free(void* ptr);
+
+/*
  * Streaming append for the formats whose scales span the sequence (the incremental update the reference
  * lists as future work, ffa-q2fp8/OPTIMIZATION_NOTES.md:23-27).  K [B, T_new, HKV, 128] of the new tokens
  * is encoded against the scales the cache already has - q2: scale and zero, nf4: scale (absmax), each

@@ -47,6 +47,17 @@ def _worker(rank, world, port, ret):
         torch.cuda.synchronize()
         err_seq = float((out.float().cpu() - want).abs().max())
 
+        # --- the same step with the exchange over peer memory, fused with the merge: three steps, so
+        # that both halves of the double buffer and the step-numbered flags are exercised
+        peer = sharded.PeerShardedDecode(dist.group.WORLD, B, HQ, dev, torch.bfloat16)
+        same = True
+        for _ in range(3):
+            o_peer = peer.step(lambda partial_out: attn_forward_decode_fp8fp8(
+                qd, ck, vk, k_residual=rk, BS=64, precomputed_threshold=th, partial_out=partial_out))
+            torch.cuda.synchronize()
+            same = same and bool(torch.equal(o_peer, out)) and int(peer.status[0]) == 0
+        peer.close()
+
         # --- batch x kv-head sharding: disjoint outputs, no collective ------------------------------
         bs, hs = sharded.shard_batch_heads(rank, world, B, HKV)
         G = HQ // HKV
@@ -54,7 +65,7 @@ def _worker(rank, world, port, ret):
             q[bs][:, :, hs.start * G:hs.stop * G].contiguous().to(dev), coarse.codes[bs][:, :, hs].contiguous().to(dev),
             v[bs][:, :, hs].contiguous().to(dev), k_residual=res[bs][:, :, hs].contiguous().to(dev), BS=64, delta=6.0)
         err_unit = float((o.float().cpu() - want[bs][:, hs.start * G:hs.stop * G]).abs().max())
-        ret[rank] = (err_seq, err_unit)
+        ret[rank] = (err_seq, err_unit, same)
     finally:
         dist.destroy_process_group()
 
@@ -66,5 +77,6 @@ def test_two_rank_sequence_split_and_unit_sharding():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     assert len(ret) == 2
-    for rank, (err_seq, err_unit) in ret.items():
+    for rank, (err_seq, err_unit, peer_same) in ret.items():
         assert err_seq <= 2e-2 and err_unit <= 2e-2, dict(ret)
+        assert peer_same, "peer-memory exchange + merge differs from all-gather + merge"
