@@ -381,8 +381,13 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
         step = lambda: local()
     o = step()
     torch.cuda.synchronize()
-    if peer is not None and not torch.equal(o, o_nccl):
-        raise SystemExit("peer-memory exchange + merge differs from all-gather + merge")
+    peer_diff = 0.0
+    if peer is not None:
+        peer_diff = float((o.float() - o_nccl.float()).abs().max())
+        if not peer_diff <= 1e-2:          # the two merges may round the last bit of an output differently
+            bad = (o.float() - o_nccl.float()).abs().amax(dim=-1) > 1e-2
+            raise SystemExit(f"rank {rank}: peer-memory exchange + merge differs from all-gather + merge by {peer_diff} "
+                             f"in {int(bad.sum())} of {bad.numel()} rows; status {peer.status.tolist()}")
     err_vs_unsplit = float((o.float() - o_full).abs().max())
     th_err = float((th - th_full).abs().max())
     kept_local = float(ws.mask.float().mean())
@@ -439,7 +444,7 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     if ws.status() != 0:
         raise SystemExit("a bounded wait inside the decode kernel gave up (status word set): results are invalid")
     t = torch.tensor([ms, s_e2e, step_bytes, kept_local, ms_local, ms_gather, ms_merge, err_vs_unsplit, us_unsplit,
-                      ms_nccl, ms_exchange], dtype=torch.float64, device=dev)
+                      ms_nccl, ms_exchange, peer_diff], dtype=torch.float64, device=dev)
     tmax, tsum = t.clone(), t.clone()
     if world > 1:
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
@@ -469,6 +474,7 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
                          "max_abs_err_vs_unsplit": float(tmax[7]), "threshold_max_abs_diff": th_err,
                          "local_decode_us": float(tmax[4]) * 1e3 / steps,
                          "peer_exchange_merge_us": float(tmax[10]) * 1e3 / steps,
+                         "peer_vs_nccl_max_abs_diff": float(tmax[11]),
                          "nccl_step_us": float(tmax[9]) * 1e3 / steps, "nccl_allgather_us": float(tmax[5]) * 1e3 / steps,
                          "merge_kernel_us": float(tmax[6]) * 1e3 / steps, "kept_fraction_unsplit": kept_full},
             "e2e": {"value": job_bytes / float(tmax[1]) / 1e12, "unit": UNIT, "h2d_bytes_per_step": q_host.numel() * 2,

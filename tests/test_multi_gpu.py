@@ -55,7 +55,8 @@ def _worker(rank, world, port, ret):
             o_peer = peer.step(lambda partial_out: attn_forward_decode_fp8fp8(
                 qd, ck, vk, k_residual=rk, BS=64, precomputed_threshold=th, partial_out=partial_out))
             torch.cuda.synchronize()
-            same = same and bool(torch.equal(o_peer, out)) and int(peer.status[0]) == 0
+            close = float((o_peer.float() - out.float()).abs().max()) <= 2.0 ** -8      # one bf16 ulp at |o| <= 1
+            same = same and close and int(peer.status[0]) == 0
         peer.close()
 
         # --- batch x kv-head sharding: disjoint outputs, no collective ------------------------------
