@@ -365,9 +365,10 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     ws = allocate_decode_workspace(q, vk, BS=PAGE, SBS=PAGE)
     q_dev = q.clone()
 
-    def local(partial_out=None, out=None):
+    def local(partial_out=None, out=None, peer=None):
         return decode_call(kind, q_dev, ck, vk, k_scale=scale, k_zero=zero, k_residual=rk, BS=PAGE, SBS=PAGE,
-                           delta=delta, precomputed_threshold=th, workspace=ws, partial_out=partial_out, out=out)
+                           delta=delta, precomputed_threshold=th, workspace=ws, partial_out=partial_out, out=out,
+                           peer=peer, kernel="ws" if peer is not None else "auto")
 
     runner = peer = None
     if world > 1:
@@ -375,7 +376,7 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
         # library-only way (NCCL all-gather + merge kernel) is timed next to it.
         runner = sharded.SequenceShardedDecode(dist.group.WORLD, B, HQ, dev, q.dtype)
         peer = sharded.PeerShardedDecode(dist.group.WORLD, B, HQ, dev, q.dtype)
-        step = lambda: peer.step(local)
+        step = lambda: peer.step(local, fused=True)     # the decode kernel itself stores the rows on the peers
         o_nccl = runner.step(local).clone()
     else:
         step = lambda: local()
@@ -421,6 +422,7 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     ms_merge = timed(runner.merge, steps) if runner else 0.0
     ms_nccl = timed(lambda: runner.step(local), steps) if runner else 0.0
     ms_exchange = timed(peer.exchange_and_merge, steps) if peer else 0.0
+    ms_unfused = timed(lambda: peer.step(local), steps) if peer else 0.0
     if peer is not None and int(peer.status[0]) != 0:
         raise SystemExit("a bounded wait of the peer-memory exchange gave up (status word set): results are invalid")
 
@@ -444,7 +446,7 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     if ws.status() != 0:
         raise SystemExit("a bounded wait inside the decode kernel gave up (status word set): results are invalid")
     t = torch.tensor([ms, s_e2e, step_bytes, kept_local, ms_local, ms_gather, ms_merge, err_vs_unsplit, us_unsplit,
-                      ms_nccl, ms_exchange, peer_diff], dtype=torch.float64, device=dev)
+                      ms_nccl, ms_exchange, peer_diff, ms_unfused], dtype=torch.float64, device=dev)
     tmax, tsum = t.clone(), t.clone()
     if world > 1:
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
@@ -473,13 +475,16 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
                          "speedup_vs_unsplit": float(tmax[8]) / (per_step_s * 1e6),
                          "max_abs_err_vs_unsplit": float(tmax[7]), "threshold_max_abs_diff": th_err,
                          "local_decode_us": float(tmax[4]) * 1e3 / steps,
+                         "how": "decode kernel stores its partial rows on the peers as they are produced, then one "
+                                "wait-and-merge kernel",
+                         "peer_step_separate_push_us": float(tmax[12]) * 1e3 / steps,
                          "peer_exchange_merge_us": float(tmax[10]) * 1e3 / steps,
                          "peer_vs_nccl_max_abs_diff": float(tmax[11]),
                          "nccl_step_us": float(tmax[9]) * 1e3 / steps, "nccl_allgather_us": float(tmax[5]) * 1e3 / steps,
                          "merge_kernel_us": float(tmax[6]) * 1e3 / steps, "kept_fraction_unsplit": kept_full},
             "e2e": {"value": job_bytes / float(tmax[1]) / 1e12, "unit": UNIT, "h2d_bytes_per_step": q_host.numel() * 2,
                     "d2h_bytes_per_step": o_host.numel() * 2, "us_per_step": float(tmax[1]) * 1e6, "steps": n_e2e},
-            "gpu_launches": steps * (1 if world == 1 else 3),     # decode (+ peer push + wait-and-merge)
+            "gpu_launches": steps * (1 if world == 1 else 2),     # decode (+ wait-and-merge)
             "clocks": clocks,
         }
     if peer is not None:

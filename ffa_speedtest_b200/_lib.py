@@ -52,6 +52,11 @@ class FfaDecodeArgs(C.Structure):
     ]
 
 
+class FfaPeerArgs(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("step", C.c_int32),
+                ("peer_gathered", C.POINTER(C.c_void_p)), ("peer_flags", C.POINTER(C.c_void_p))]
+
+
 class FfaKprojArgs(C.Structure):
     _fields_ = [
         ("variant", C.c_int32),
@@ -102,6 +107,10 @@ def lib() -> C.CDLL:
     L.ffa_cache_append.restype = C.c_int
     L.ffa_peer_exchange_merge.argtypes = [vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), i32, vp, i32, vp, vp]
     L.ffa_peer_exchange_merge.restype = C.c_int
+    L.ffa_decode_peer.argtypes = [C.POINTER(FfaDecodeArgs), C.POINTER(FfaPeerArgs), C.c_void_p]
+    L.ffa_decode_peer.restype = C.c_int
+    L.ffa_peer_wait_merge.argtypes = [vp, vp, i32, i32, i32, vp, i32, vp, vp]
+    L.ffa_peer_wait_merge.restype = C.c_int
     L.ffa_peer_alloc.argtypes = [C.c_size_t, C.POINTER(vp), C.c_char_p]
     L.ffa_peer_open.argtypes = [C.c_char_p, C.POINTER(vp)]
     L.ffa_peer_close.argtypes = [vp]

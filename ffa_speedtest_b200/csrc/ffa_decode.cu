@@ -576,7 +576,19 @@ extern "C" size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, i
 // sequence) up: 2^20 cached tokens at 8 kv-heads
 constexpr long long kFp8WsPages = 131072;
 
-extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
+namespace {
+int decode_impl(const FfaDecodeArgs* a, const FfaPeerArgs* peer, ffa_stream_t stream_);
+}
+
+extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) { return decode_impl(a, nullptr, stream_); }
+
+extern "C" int ffa_decode_peer(const FfaDecodeArgs* a, const FfaPeerArgs* peer, ffa_stream_t stream_) {
+  if (!peer) return FFA_E_NULL;
+  return decode_impl(a, peer, stream_);
+}
+
+namespace {
+int decode_impl(const FfaDecodeArgs* a, const FfaPeerArgs* peer, ffa_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!a || !a->q || !a->k_codes || !a->v || !a->out || !a->workspace) return FFA_E_NULL;
   if (a->B <= 0 || a->T <= 0 || a->HKV <= 0 || a->HQ <= 0 || a->HQ % a->HKV != 0) return FFA_E_SHAPE;
@@ -675,6 +687,21 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   if ((m > 1 || sub_page) && !use_ws) return FFA_E_SHAPE;     // the other kernels prune page by page only
   if (sub_page && a->v_mean) return FFA_E_SHAPE;              // mean-V keeps whole pages' mass
 
+  if (peer) {
+    // the fused exchange lives in the warp-specialised kernel's merge
+    if (!use_ws || !a->partial_out || a->v_mean) return FFA_E_SHAPE;
+    if (peer->world < 1 || peer->world > kMaxPeerRanks || peer->rank < 0 || peer->rank >= peer->world || peer->step <= 0 ||
+        !peer->peer_gathered || !peer->peer_flags)
+      return FFA_E_SHAPE;
+    p.peer_world = peer->world; p.peer_rank = peer->rank; p.peer_step = peer->step;
+    const int64_t n_part = static_cast<int64_t>(rows) * (kHeadDim + 1);
+    for (int r = 0; r < peer->world; ++r) {
+      if (!peer->peer_gathered[r] || !peer->peer_flags[r]) return FFA_E_NULL;
+      p.peer_slot[r] = peer->peer_gathered[r] + (static_cast<int64_t>(peer->step & 1) * peer->world + peer->rank) * n_part;
+      p.peer_flag[r] = peer->peer_flags[r] + peer->rank;
+    }
+    if (a->partial_out != p.peer_slot[peer->rank]) return FFA_E_SHAPE;      // the local partial is this rank's own slot
+  }
   int rc;
   const int64_t kv_rows = a->kv_rows > 0 ? a->kv_rows : static_cast<int64_t>(a->B) * a->T;
   p.kv_rows = kv_rows;
@@ -696,6 +723,7 @@ extern "C" int ffa_decode(const FfaDecodeArgs* a, ffa_stream_t stream_) {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? FFA_OK : note_cuda_error(e, "decode_merge launch");
 }
+}  // namespace
 
 extern "C" int ffa_merge_partials(const float* parts, int32_t R, int32_t rows, void* out, int32_t out_dtype,
                                   ffa_stream_t stream_) {

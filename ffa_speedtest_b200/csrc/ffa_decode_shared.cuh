@@ -14,6 +14,7 @@ constexpr int kWsRefineWarps = 4; // refine warps of the warp-specialised kernel
 constexpr int kWsMaxParts = 32;   // partials (one per chunk) per q head that its merge handles
 // ints of the arrival-counter block that the warp-specialised kernel uses as its work counter (next
 // chunk to hand out) and as the count of CTAs that have left; both are zero between launches
+constexpr int kMaxPeerRanks = 16;
 constexpr int kWorkCounterIndex = 16000;
 constexpr int kResRow = 128;      // fp8 residual bytes per token per head
 constexpr int kVRow = 256;        // V bytes per token per head (fp16 / bf16)
@@ -87,6 +88,12 @@ struct DecodeParams {
   int64_t kv_rows;   // token rows of the K/V tensors
   float* part_pm;            // [B*HQ, nch]
   float* part_pl;            // [B*HQ, nch]
+  // sequence split over the GPUs of one box (warp-specialised kernel): every partial_out row is also
+  // stored into this rank's slot on each peer, and the last CTA to leave raises this rank's flag on
+  // every peer to `peer_step` (see ffa_peer.cu).  peer_world = 0: off.
+  int peer_world, peer_rank, peer_step;
+  float* peer_slot[kMaxPeerRanks];     // peer p's copy of this rank's [B*HQ, 129] slot for this step (mapped memory)
+  int* peer_flag[kMaxPeerRanks];       // this rank's flag on peer p
 };
 
 

@@ -323,9 +323,22 @@ __device__ __forceinline__ void ws_merge_unit(const DecodeParams& p, int b, int 
       store_from_float(p.out, e + 3, p.q_dtype, r3);
     }
     if (p.partial_out) {
+      const float lse = acc == 0.f ? -INFINITY : top + log2f(acc);
       float* po = p.partial_out + row * (kHeadDim + 1);
       po[4 * lane] = r0; po[4 * lane + 1] = r1; po[4 * lane + 2] = r2; po[4 * lane + 3] = r3;
-      if (lane == 0) po[kHeadDim] = acc == 0.f ? -INFINITY : top + log2f(acc);
+      if (lane == 0) po[kHeadDim] = lse;
+      if (p.peer_world > 0) {
+        // sequence split: the finished row goes to this rank's slot on every peer as soon as it exists, so
+        // the exchange overlaps the rest of the kernel; the fence orders the stores before the flag that
+        // the last CTA raises when the whole kernel is done
+        for (int pr = 0; pr < p.peer_world; ++pr) {
+          if (pr == p.peer_rank) continue;
+          float* pp = p.peer_slot[pr] + row * (kHeadDim + 1);
+          pp[4 * lane] = r0; pp[4 * lane + 1] = r1; pp[4 * lane + 2] = r2; pp[4 * lane + 3] = r3;
+          if (lane == 0) pp[kHeadDim] = lse;
+        }
+        __threadfence_system();
+      }
     }
   }
 }
@@ -1159,10 +1172,16 @@ __global__ void __launch_bounds__(kWsThreads, 1) decode_ws_kernel(const __grid_c
       p.status[5] = static_cast<int>(blockIdx.x);
     }
     // the last CTA to leave puts the work counter back to zero for the next launch
-    __threadfence();
+    if (p.peer_world > 0) __threadfence_system();
+    else __threadfence();
     if (atomicAdd(p.work + 1, 1) == static_cast<int>(gridDim.x) - 1) {
       p.work[0] = 0;
       p.work[1] = 0;
+      if (p.peer_world > 0) {
+        // every CTA's rows are out (each fenced its stores before it was counted): tell the peers
+        __threadfence_system();
+        for (int pr = 0; pr < p.peer_world; ++pr) *reinterpret_cast<volatile int*>(p.peer_flag[pr]) = p.peer_step;
+      }
     }
   }
 }

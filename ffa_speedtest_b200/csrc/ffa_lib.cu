@@ -15,4 +15,4 @@ int note_cuda_error(cudaError_t e, const char* where) {
 }  // namespace ffa
 
 extern "C" const char* ffa_last_cuda_error(void) { return ffa::g_last_error; }
-extern "C" int ffa_abi_version(void) { return 4; }   // 4: ffa_cache_append, ffa_quantize_append
+extern "C" int ffa_abi_version(void) { return 5; }   // 5: sub-page prune blocks, peer-memory exchange, ffa_decode_peer

@@ -132,6 +132,17 @@ extern "C" int ffa_peer_exchange_merge(const float* local_partial, int32_t rows,
   return e == cudaSuccess ? FFA_OK : note_cuda_error(e, "peer_wait_merge launch");
 }
 
+extern "C" int ffa_peer_wait_merge(const float* gathered_local, const int32_t* flags_local, int32_t world, int32_t rows,
+                                   int32_t step, void* out, int32_t out_dtype, int32_t* status, ffa_stream_t stream_) {
+  if (!gathered_local || !flags_local || !out) return FFA_E_NULL;
+  if (rows <= 0 || world <= 0 || world > kMaxPeers || step <= 0) return FFA_E_SHAPE;
+  if (out_dtype < FFA_F16 || out_dtype > FFA_F32) return FFA_E_DTYPE;
+  peer_wait_merge_kernel<<<static_cast<unsigned>(rows), kHeadDim, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+      gathered_local, flags_local, world, rows, step, out, out_dtype, status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FFA_OK : note_cuda_error(e, "peer_wait_merge launch");
+}
+
 // ---- set-up: a buffer other processes of the box can map ---------------------------------------------
 extern "C" int ffa_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
   if (!ptr || !handle64 || bytes == 0) return FFA_E_NULL;

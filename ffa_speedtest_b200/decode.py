@@ -175,6 +175,7 @@ def decode_call(
     pages_per_chunk: int = 0,
     kernel: str = "auto",
     mean_v: Optional[torch.Tensor] = None,
+    peer=None,
 ):
     """Shape bookkeeping shared by the five entry points; tensors are already type-checked.
 
@@ -294,7 +295,12 @@ def decode_call(
     a.pages_per_chunk = pages_per_chunk
     a.reserved = {"auto": 0, "fp16": 1, "pipe": 2, "ws": 4}[kernel]
     a.kv_rows = k_codes.shape[0] * k_codes.shape[1]
-    _lib.check(_lib.lib().ffa_decode(a, _lib.current_stream(q.device)), "ffa_decode")
+    if peer is not None:
+        # sequence split over peer memory (sharded.PeerShardedDecode): the kernel's merge also stores every
+        # partial row into this rank's slot on the peers and raises the step's flags when it is done
+        _lib.check(_lib.lib().ffa_decode_peer(a, peer, _lib.current_stream(q.device)), "ffa_decode_peer")
+    else:
+        _lib.check(_lib.lib().ffa_decode(a, _lib.current_stream(q.device)), "ffa_decode")
 
     if return_skip_ratio:
         mask = workspace.mask_view(B, HKV, NTBS)

@@ -199,9 +199,24 @@ class PeerShardedDecode:
         """Where the NEXT step's local partial goes: ``[B, HQ, 129]``."""
         return self.gathered[(self.step_no + 1) & 1, self.rank]
 
-    def step(self, local_decode) -> torch.Tensor:
-        local_decode(partial_out=self.local_slot())
-        return self.exchange_and_merge()
+    def step(self, local_decode, fused: bool = False) -> torch.Tensor:
+        """``fused=False``: ``local_decode(partial_out=...)`` as for ``SequenceShardedDecode``, then one call
+        pushes the partial to the peers, waits and merges.  ``fused=True``: ``local_decode(partial_out=...,
+        peer=...)`` must hand ``peer`` to the decode entry point (warp-specialised kernel); the kernel then
+        stores every partial row on the peers as it is produced and only the wait-and-merge remains."""
+        if not fused:
+            local_decode(partial_out=self.local_slot())
+            return self.exchange_and_merge()
+        slot = self.local_slot()
+        self.step_no += 1
+        args = _lib.FfaPeerArgs(world=self.world, rank=self.rank, step=self.step_no,
+                                peer_gathered=self._gathered_ptrs, peer_flags=self._flag_ptrs)
+        local_decode(partial_out=slot, peer=args)
+        _lib.check(_lib.lib().ffa_peer_wait_merge(
+            self._own, self._own + self._gather_bytes, self.world, self.rows, self.step_no, self.out.data_ptr(),
+            _lib.float_code(self.out.dtype), self.status.data_ptr(), _lib.current_stream(self.device)),
+            "ffa_peer_wait_merge")
+        return self.out
 
     def exchange_and_merge(self) -> torch.Tensor:
         """The part of a step after the local decode: push the partial in ``local_slot()`` to every peer,

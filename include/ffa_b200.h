@@ -195,6 +195,22 @@ int ffa_peer_exchange_merge(const float* local_partial, int32_t rows, int32_t ra
                             float* const* peer_gathered, int32_t* const* peer_flags, int32_t step, void* out,
                             int32_t out_dtype, int32_t* status, ffa_stream_t stream);
 
+/*
+ * The same exchange fused into the decode kernel.  ffa_decode_peer is ffa_decode (warp-specialised
+ * kernel, partial_out = slot [step & 1][rank] of this rank's own gathered buffer) whose merge also stores
+ * every finished partial row into this rank's slot on each peer the moment the row exists, and whose
+ * last CTA raises this rank's flags; the transfer overlaps the rest of the kernel.  ffa_peer_wait_merge
+ * is then the second half of ffa_peer_exchange_merge alone: wait for the `world` flags of `step`, merge.
+ */
+typedef struct FfaPeerArgs {
+  int32_t world, rank, step;           /* as for ffa_peer_exchange_merge                            */
+  float* const* peer_gathered;         /* host array [world]                                        */
+  int32_t* const* peer_flags;          /* host array [world]                                        */
+} FfaPeerArgs;
+int ffa_decode_peer(const FfaDecodeArgs* args, const FfaPeerArgs* peer, ffa_stream_t stream);
+int ffa_peer_wait_merge(const float* gathered_local, const int32_t* flags_local, int32_t world, int32_t rows,
+                        int32_t step, void* out, int32_t out_dtype, int32_t* status, ffa_stream_t stream);
+
 /* Set-up for ffa_peer_exchange_merge (these four allocate, map or free; none belongs in a step):
  * ffa_peer_alloc makes a zeroed device buffer on the current device and its 64-byte inter-process
  * handle; another process of the same box maps it on ITS current device with ffa_peer_open (peer access
@@ -281,7 +297,8 @@ size_t ffa_kproj_workspace_bytes(int32_t B, int32_t T, int32_t HKV, int32_t rope
 /* Text of the last CUDA runtime error seen by this library on the calling thread ("" if none). */
 const char* ffa_last_cuda_error(void);
 /* Library version, bumped when the ABI changes (2: FfaDecodeArgs ends in v_mean; FfaKprojArgs.slot_pos0;
- * 3: ffa_static_scratch_status, every SBS in one launch; 4: ffa_cache_append, ffa_quantize_append). */
+ * 3: ffa_static_scratch_status, every SBS in one launch; 4: ffa_cache_append, ffa_quantize_append;
+ * 5: SBS 16 / 32, the ffa_peer_* entry points, ffa_decode_peer). */
 int ffa_abi_version(void);
 
 #ifdef __cplusplus

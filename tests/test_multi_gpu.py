@@ -57,6 +57,16 @@ def _worker(rank, world, port, ret):
             torch.cuda.synchronize()
             close = float((o_peer.float() - out.float()).abs().max()) <= 2.0 ** -8      # one bf16 ulp at |o| <= 1
             same = same and close and int(peer.status[0]) == 0
+        # ... and with the push fused into the decode kernel (warp-specialised kernel), three more steps
+        from ffa_speedtest_b200.decode import decode_call
+        ws_local = allocate_decode_workspace(qd, vk, BS=64)
+        for _ in range(3):
+            o_peer = peer.step(lambda partial_out, peer: decode_call(
+                "fp8", qd, ck, vk, k_residual=rk, BS=64, SBS=64, precomputed_threshold=th, partial_out=partial_out,
+                peer=peer, kernel="ws", workspace=ws_local), fused=True)
+            torch.cuda.synchronize()
+            close = float((o_peer.float() - out.float()).abs().max()) <= 2.0 ** -8
+            same = same and close and int(peer.status[0]) == 0 and ws_local.status() == 0
         peer.close()
 
         # --- batch x kv-head sharding: disjoint outputs, no collective ------------------------------
