@@ -375,8 +375,21 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
         # the step: local decode, then the exchange over peer memory fused with the merge.  The
         # library-only way (NCCL all-gather + merge kernel) is timed next to it.
         runner = sharded.SequenceShardedDecode(dist.group.WORLD, B, HQ, dev, q.dtype)
-        peer = sharded.PeerShardedDecode(dist.group.WORLD, B, HQ, dev, q.dtype)
-        step = lambda: peer.step(local, fused=True)     # the decode kernel itself stores the rows on the peers
+        peer_note = None
+        try:
+            peer = sharded.PeerShardedDecode(dist.group.WORLD, B, HQ, dev, q.dtype)
+            ok_here = 1
+        except Exception as exc:       # e.g. a box whose processes cannot map each other's memory
+            peer, ok_here, peer_note = None, 0, f"{type(exc).__name__}: {exc}"
+        ok_all = torch.tensor([ok_here], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
+        if int(ok_all) == 0 and peer is not None:
+            peer.close()
+            peer, peer_note = None, "another rank could not map its peers"
+        if peer is not None:
+            step = lambda: peer.step(local, fused=True)     # the decode kernel itself stores the rows on the peers
+        else:
+            step = lambda: runner.step(local)               # library-only transport
         o_nccl = runner.step(local).clone()
     else:
         step = lambda: local()
@@ -475,8 +488,9 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
                          "speedup_vs_unsplit": float(tmax[8]) / (per_step_s * 1e6),
                          "max_abs_err_vs_unsplit": float(tmax[7]), "threshold_max_abs_diff": th_err,
                          "local_decode_us": float(tmax[4]) * 1e3 / steps,
-                         "how": "decode kernel stores its partial rows on the peers as they are produced, then one "
-                                "wait-and-merge kernel",
+                         "how": ("decode kernel stores its partial rows on the peers as they are produced, then one "
+                                 "wait-and-merge kernel") if peer is not None else
+                                f"NCCL all-gather + merge kernel (peer-memory transport unavailable: {peer_note})",
                          "peer_step_separate_push_us": float(tmax[12]) * 1e3 / steps,
                          "peer_exchange_merge_us": float(tmax[10]) * 1e3 / steps,
                          "peer_vs_nccl_max_abs_diff": float(tmax[11]),

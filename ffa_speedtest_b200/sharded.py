@@ -170,20 +170,39 @@ class PeerShardedDecode:
         n_part = self.rows * 129
         self._gather_bytes = 2 * self.world * n_part * 4
         total = self._gather_bytes + 256                       # + the flags, one int per rank
-        with torch.cuda.device(self.device):
+        # Set-up is collective and every rank takes every collective step whatever happens on it, so that
+        # a rank that cannot allocate or map ends in the same exception on all ranks, not in a hang.
+        import contextlib
+        on_device = torch.cuda.device(self.device) if self.device.type == "cuda" else contextlib.nullcontext()
+        with on_device:
             ptr, handle = C.c_void_p(), C.create_string_buffer(64)
-            _lib.check(L.ffa_peer_alloc(total, C.byref(ptr), handle), "ffa_peer_alloc")
-            self._own = ptr.value
+            rc = L.ffa_peer_alloc(total, C.byref(ptr), handle)
+            self._own = ptr.value if rc == 0 else None
             handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(handle.raw), group=group)
-            self._bases = []
-            for r, h in enumerate(handles):
-                if r == self.rank:
-                    self._bases.append(self._own)
-                    continue
-                p = C.c_void_p()
-                _lib.check(L.ffa_peer_open(h, C.byref(p)), "ffa_peer_open")
-                self._bases.append(p.value)
+            dist.all_gather_object(handles, bytes(handle.raw) if rc == 0 else None, group=group)
+            self._bases, failed = [], rc != 0                     # `failed`: this rank's own steps
+            if not failed and all(h is not None for h in handles):
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        self._bases.append(self._own)
+                        continue
+                    p = C.c_void_p()
+                    if L.ffa_peer_open(h, C.byref(p)) != 0:
+                        failed = True
+                        break
+                    self._bases.append(p.value)
+            oks = [None] * self.world
+            dist.all_gather_object(oks, not failed, group=group)
+            if not all(oks):
+                for r, b in enumerate(self._bases):
+                    if r != self.rank:
+                        L.ffa_peer_close(b)
+                dist.barrier(group=group)
+                if self._own is not None:
+                    L.ffa_peer_free(self._own)
+                self._own = None
+                raise RuntimeError("peer-memory set-up failed on rank(s) "
+                                   f"{[r for r, ok in enumerate(oks) if not ok]}: {L.ffa_last_cuda_error().decode()!r}")
         self._gathered_ptrs = (C.c_void_p * self.world)(*self._bases)
         self._flag_ptrs = (C.c_void_p * self.world)(*[b + self._gather_bytes for b in self._bases])
         # this rank's two slots, as tensors the decode kernel writes its partial into

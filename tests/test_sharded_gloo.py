@@ -158,3 +158,71 @@ def test_sample_token_rows_match_the_oracle_sampling():
         assert list(r1) == [(ntb - 1) * fo.THRESHOLD_SAMPLE + i for i in range(fo.THRESHOLD_SAMPLE)]
     with pytest.raises(ValueError):
         sample_token_rows(10, 64)
+
+
+class _FakePeerLib:
+    """Stands in for the CUDA library in the peer-memory set-up: host-side buffers, and an allocation
+    that fails on one chosen rank."""
+
+    def __init__(self, fail_alloc: bool, fail_open: bool):
+        self.fail_alloc, self.fail_open = fail_alloc, fail_open
+        self.opened, self.closed, self.freed = 0, 0, 0
+
+    def ffa_peer_alloc(self, nbytes, ptr_ref, handle):
+        if self.fail_alloc:
+            return -5
+        ptr_ref._obj.value = 0x1000
+        return 0
+
+    def ffa_peer_open(self, handle, ptr_ref):
+        if self.fail_open:
+            return -5
+        self.opened += 1
+        ptr_ref._obj.value = 0x2000 + self.opened
+        return 0
+
+    def ffa_peer_close(self, ptr):
+        self.closed += 1
+        return 0
+
+    def ffa_peer_free(self, ptr):
+        self.freed += 1
+        return 0
+
+    def ffa_last_cuda_error(self):
+        return b"out of memory (injected)"
+
+
+def _peer_setup_worker(rank, world, port, mode, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ffa_speedtest_b200 import _lib
+        fake = _FakePeerLib(fail_alloc=(mode == "alloc" and rank == 1), fail_open=(mode == "open" and rank == 0))
+        _lib.lib = lambda: fake
+        try:
+            sharded.PeerShardedDecode(dist.group.WORLD, 1, 8, "cpu", torch.float32)
+            ret[rank] = ("built", fake.opened, fake.closed, fake.freed)
+        except RuntimeError as exc:
+            ret[rank] = ("raised", str(exc), fake.closed, fake.freed)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["alloc", "open"])
+def test_peer_setup_failure_on_one_rank_raises_on_every_rank(mode):
+    """The set-up of the peer-memory transport is collective: when one rank cannot allocate its buffer,
+    or cannot map a peer's, every rank must leave with the same exception (and give back what it had
+    taken) instead of waiting for the failed rank in a later collective.  The failure is injected on
+    the host, through a stand-in for the library."""
+    world, port = 3, free_port()
+    ret = mp.Manager().dict()
+    mp.spawn(_peer_setup_worker, args=(world, port, mode, ret), nprocs=world, join=True)
+    assert len(ret) == world
+    failed = 1 if mode == "alloc" else 0
+    for rank in range(world):
+        kind, msg = ret[rank][0], ret[rank][1]
+        assert kind == "raised" and f"[{failed}]" in msg, dict(ret)
+    if mode == "open":
+        # ranks that had mapped their peers unmapped them again, and everyone freed its own buffer
+        assert ret[1][2] == world - 1 and all(ret[r][3] == 1 for r in range(world))
