@@ -67,13 +67,6 @@ struct DecodeParams {
   int q_dtype, scale_dtype;
   int use_res, v_bf16;
   int refine_lag;    // TMA kernel: pages between scoring and refining a page (1 or 2)
-  // TMA kernel, prune granularity above one page (SBS = 64 m): the step runs as two launches.
-  // mode 1 scores every page and writes the per-head maximum coarse score of each page (no refine,
-  // no output); a small kernel turns those into one keep flag per group of m pages; mode 2 takes the
-  // flags instead of testing pages itself.  mode 0 is the one-launch step.
-  int mode;
-  float* page_max;           // mode 1: [B*HQ, NP]
-  const int8_t* page_keep;   // mode 2: [B*HKV, NP]
   // mean-V variant (q2 only): pruned pages contribute their coarse softmax mass times the mean of V.
   // Every segment adds the running maximum and mass of its pruned pages to its partial.
   const void* v_mean;        // [B*HKV, 128] in V's dtype, or null

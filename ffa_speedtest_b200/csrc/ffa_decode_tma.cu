@@ -419,21 +419,8 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
 
       bool keep = false;
       if (do_score) {
-        if (p.mode == 1) {
-          // scoring pass: publish the page's per-head maximum, keep nothing
-          if (warp == 0 && g == 0) {
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              const int h = 4 * nt + t;
-              if (h < G)
-                p.page_max[(static_cast<int64_t>(b) * p.HQ + static_cast<int64_t>(hkv) * G + h) * p.NP + page_begin + j] = cm[nt];
-            }
-          }
-        } else if (p.mode == 2) {
-          keep = p.page_keep[(static_cast<int64_t>(b) * p.HKV + hkv) * p.NP + page_begin + j] != 0;
-        } else
         keep = !__all_sync(0xffffffffu, below);     // pruned only if every head is strictly below
-        if (MV && !keep && p.mode != 1) {
+        if (MV && !keep) {
           // pruned page: its coarse scores relative to the page maximum join the running mass
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
@@ -515,8 +502,6 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 3 : 2) decode_tma_kernel(c
       }
       keepq = (keepq << 1) | (keep ? 1u : 0u);
     }
-
-    if (p.mode == 1) continue;          // scoring pass: nothing to merge
 
     // ---- segment epilogue: add the four warps' token slices and write one partial -------------------
     __syncthreads();
