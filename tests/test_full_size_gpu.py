@@ -37,14 +37,16 @@ def quantise(kind, k, f8):
     return c, s, None, r
 
 
-@pytest.mark.parametrize("kind,B,T,check", [
-    ("fp8", 8, 32768, (0, 5)),           # config 1
-    ("fp4", 16, 65536, (3,)),            # config 2
-    ("nf4", 16, 65536, (9,)),
-    ("nvfp4", 16, 65536, (15,)),
-    ("q2", 4, 131072, (2,)),             # config 4 at 128K, four of the 32 sequences
+@pytest.mark.parametrize("kind,B,T,check,SBS", [
+    ("fp8", 8, 32768, (0, 5), 64),       # config 1
+    ("fp4", 16, 65536, (3,), 64),        # config 2
+    ("nf4", 16, 65536, (9,), 64),
+    ("nvfp4", 16, 65536, (15,), 64),
+    ("q2", 4, 131072, (2,), 64),         # config 4 at 128K, four of the 32 sequences
+    ("q2", 4, 65536, (1,), 128),         # the reference's default block sizes (BS = SBS = 128): pages pruned in pairs
+    ("fp8", 4, 65536, (3,), 32),         # prune blocks of half a page
 ])
-def test_bench_workload_against_oracle(kind, B, T, check):
+def test_bench_workload_against_oracle(kind, B, T, check, SBS):
     dev = torch.device("cuda")
     f8 = torch.float8_e4m3fn
     delta = 8.0
@@ -52,6 +54,8 @@ def test_bench_workload_against_oracle(kind, B, T, check):
     codes, scale, zero, res = quantise(kind, k, f8)
     del k
     NP = T // PAGE
+    BS = max(PAGE, SBS)
+    NTBS = T // SBS
     bt = make_block_table(B, NP, seed=7).to(dev)
 
     def to_pool(x):
@@ -62,12 +66,12 @@ def test_bench_workload_against_oracle(kind, B, T, check):
         return pool
 
     codes_p, res_p, v_p = to_pool(codes), to_pool(res), to_pool(v)
-    ws = allocate_decode_workspace(q, v_p, BS=PAGE, SBS=PAGE, seq_len=T)
-    o = decode_call(kind, q, codes_p, v_p, k_scale=scale, k_zero=zero, k_residual=res_p, BS=PAGE, SBS=PAGE, delta=delta,
+    ws = allocate_decode_workspace(q, v_p, BS=BS, SBS=SBS, seq_len=T)
+    o = decode_call(kind, q, codes_p, v_p, k_scale=scale, k_zero=zero, k_residual=res_p, BS=BS, SBS=SBS, delta=delta,
                     block_table=bt, seq_len=T, workspace=ws).clone()
     torch.cuda.synchronize()
     assert ws.status() == 0
-    mask = ws.mask_view(B, HKV, NP).cpu()
+    mask = ws.mask_view(B, HKV, NTBS).cpu()
     th = ws.threshold.cpu()
     del codes_p, res_p, v_p
 
@@ -76,14 +80,14 @@ def test_bench_workload_against_oracle(kind, B, T, check):
         coarse = fo.CoarseK(kind, codes[sl].cpu(), None if scale is None else scale[sl].cpu(),
                             None if zero is None else zero[sl].cpu(), D)
         qb, vb, rb = q[sl].cpu(), v[sl].cpu(), res[sl].cpu()
-        _, keep_ref, parts = fo.decode_attention_fast(qb, coarse, vb, rb, BS=PAGE, SBS=PAGE, delta=delta,
+        _, keep_ref, parts = fo.decode_attention_fast(qb, coarse, vb, rb, BS=BS, SBS=SBS, delta=delta,
                                                       out_dtype=torch.float32, return_parts=True)
         torch.testing.assert_close(th[sl], parts["threshold"], rtol=1e-5, atol=1e-4)
         assert band_ok(mask[sl], keep_ref, parts["block_max"], parts["threshold"], HQ // HKV)
         flips = int((mask[sl] != keep_ref).sum())
         assert flips <= 0.001 * keep_ref.numel(), f"{flips} pages decided differently"
         # the output, on the kept set the GPU used
-        o_ref, _ = fo.decode_attention_fast(qb, coarse, vb, rb, BS=PAGE, SBS=PAGE, delta=delta, out_dtype=torch.float32,
+        o_ref, _ = fo.decode_attention_fast(qb, coarse, vb, rb, BS=BS, SBS=SBS, delta=delta, out_dtype=torch.float32,
                                             keep_override=mask[sl])
         a = o[sl].float().cpu()
         assert torch.isfinite(a).all()
