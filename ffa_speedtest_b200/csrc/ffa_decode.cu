@@ -575,6 +575,9 @@ extern "C" size_t ffa_decode_workspace_bytes(int32_t B, int32_t T, int32_t HQ, i
 // fp8 coarse K goes to the warp-specialised kernel from this many pages (batch x kv-heads x pages per
 // sequence) up: 2^20 cached tokens at 8 kv-heads
 constexpr long long kFp8WsPages = 131072;
+// NF4 (the format with the most scoring work per page) does better on the page-pipeline kernel between
+// about 96K and a million cached tokens
+constexpr long long kNf4PipePages = 12288;
 
 namespace {
 int decode_impl(const FfaDecodeArgs* a, const FfaPeerArgs* peer, ffa_stream_t stream_);
@@ -634,8 +637,9 @@ int decode_impl(const FfaDecodeArgs* a, const FfaPeerArgs* peer, ffa_stream_t st
   // formats, for prune groups of more than one page, for the dtype pairs only it takes, and for fp8
   // coarse K from about a million cached tokens up; below that fp8 coarse K runs on the page-pipeline
   // kernel (three CTAs per SM, every warp scores and refines), which keeps more loads in flight per
-  // SM when the coarse pass is cheap and is 3-10 % faster there.  Bit 0 forces the fp16 tensor-core
-  // kernel, bit 1 the page-pipeline kernel, bit 2 the warp-specialised kernel.
+  // SM when the coarse pass is cheap and is 3-10 % faster there; NF4 takes the page-pipeline kernel
+  // between about 96K and a million cached tokens (2-11 % faster there at high kept fractions).  Bit 0
+  // forces the fp16 tensor-core kernel, bit 1 the page-pipeline kernel, bit 2 the warp-specialised kernel.
   const int m = sub_page ? 1 : a->SBS / kPage;  // pages per prune group
   p.sub = sub_page ? kPage / a->SBS : 1;
   const bool want_fp16 = (a->reserved & 1) != 0;
@@ -646,11 +650,12 @@ int decode_impl(const FfaDecodeArgs* a, const FfaPeerArgs* peer, ffa_stream_t st
   const bool v1_ok = m == 1 && !sub_page && decode_tma_supported(p);
   const bool ws_ok = decode_ws_supported(p, m);
   bool use_ws = false, use_tma = false;
+  const long long total_pages = static_cast<long long>(a->B) * a->HKV * p.NP;
   if (!want_fp16) {
     if (want_v1) use_tma = v1_ok;
     else if (want_ws) use_ws = ws_ok;
-    else if (a->variant == FFA_K_FP8 && v1_ok &&
-             static_cast<long long>(a->B) * a->HKV * p.NP < kFp8WsPages) use_tma = true;
+    else if (a->variant == FFA_K_FP8 && v1_ok && total_pages < kFp8WsPages) use_tma = true;
+    else if (a->variant == FFA_K_NF4 && v1_ok && total_pages >= kNf4PipePages && total_pages < kFp8WsPages) use_tma = true;
     else use_ws = ws_ok;
     if (!use_ws && !use_tma && !want_v1 && !want_ws) use_tma = v1_ok;
     if ((want_v1 || want_ws) && !use_ws && !use_tma) return m > 1 ? FFA_E_SHAPE : FFA_E_DTYPE;   // asked for by name

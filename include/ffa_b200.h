@@ -98,7 +98,8 @@ typedef struct FfaDecodeArgs {
   int32_t reserved;         /* kernel choice.  0: by measurement - the warp-specialised TMA kernel,
                                except for fp8 coarse K with SBS = 64, bf16 q (or fp16 q and V) and
                                fewer than 131072 pages in all (B x HKV x pages per sequence), where
-                               the page-pipeline TMA kernel is the faster one.  Bit 0: the fp16
+                               the page-pipeline TMA kernel is the faster one (NF4: likewise between
+                               12288 and 131072 pages).  Bit 0: the fp16
                                tensor-core kernel (the reference's rounding sequence to the letter;
                                SBS = 64 only).  Bit 1: the page-pipeline kernel (SBS = 64, bf16 q
                                or fp16 q with fp16 V).  Bit 2: the warp-specialised kernel.  A
