@@ -7,7 +7,7 @@
 // Here each rank instead STORES its partial straight into its slot of every peer's gathered buffer
 // (plain peer stores over NVLink; the peers' buffers are mapped through CUDA IPC) and then raises its
 // flag on that peer; the merge kernel of a rank waits until all flags carry the current step number and
-// merges from its own local copy.  No multicast of any kind is used, only ordinary stores and loads.
+// merges from its own local copy.  Only ordinary stores and loads are used.
 //
 // Protocol.  The gathered buffer is double-buffered by step parity and the flags carry the step number,
 // so nothing is ever reset: rank r can be at most one step ahead of a peer (its merge of step k + 1
