@@ -644,7 +644,7 @@ int decode_impl(const FfaDecodeArgs* a, const FfaPeerArgs* peer, ffa_stream_t st
   p.sub = sub_page ? kPage / a->SBS : 1;
   const bool want_fp16 = (a->reserved & 1) != 0;
   const bool want_v1 = (a->reserved & 2) != 0;
-  const bool want_ws = (a->reserved & 4) != 0;
+  const bool want_ws = (a->reserved & 4) != 0 || (peer != nullptr && (a->reserved & 3) == 0);   // the fused exchange lives in this kernel
   p.refine_lag = 1;
   p.group = m;
   const bool v1_ok = m == 1 && !sub_page && decode_tma_supported(p);

@@ -197,8 +197,8 @@ int ffa_peer_exchange_merge(const float* local_partial, int32_t rows, int32_t ra
                             int32_t out_dtype, int32_t* status, ffa_stream_t stream);
 
 /*
- * The same exchange fused into the decode kernel.  ffa_decode_peer is ffa_decode (warp-specialised
- * kernel, partial_out = slot [step & 1][rank] of this rank's own gathered buffer) whose merge also stores
+ * The same exchange fused into the decode kernel.  ffa_decode_peer is ffa_decode (always on the
+ * warp-specialised kernel unless `reserved` names another, which is refused; partial_out = slot [step & 1][rank] of this rank's own gathered buffer) whose merge also stores
  * every finished partial row into this rank's slot on each peer the moment the row exists, and whose
  * last CTA raises this rank's flags; the transfer overlaps the rest of the kernel.  ffa_peer_wait_merge
  * is then the second half of ffa_peer_exchange_merge alone: wait for the `world` flags of `step`, merge.
