@@ -10,7 +10,9 @@ reference's own code (its torch quantisers, and its Triton stage-1/stage-2
 kernels executed by the Triton interpreter on CPU tensors) on seeded inputs;
 those outputs are committed under ``tests/golden/`` together with the script
 that produced them (``tests/golden/make_golden.py``).  The reference holds no
-golden vectors or known-answer tests of its own for this path.
+golden vectors or known-answer tests of its own for this path.  On a GPU the
+reference's unmodified Triton kernels, compiled by Triton's JIT, are a second
+check of the CUDA kernels (``tests/test_reference_jit_gpu.py``).
 
 All arithmetic follows the reference's sequence of roundings (reference paths
 are relative to the root of qluoluo/ffa-speedtest):
