@@ -11,8 +11,11 @@ prefix lengths, quantise K for each length, time the decode call against a dense
 store ``{"meta", "lengths", "fused_ms", "flash_ms", "skip_ratios"}`` as JSON.  This driver keeps the
 arguments, the measurement protocol (CUDA events around ``iters`` calls after ``warmup`` calls) and
 the result schema, on seeded synthetic activations (the recordings are not available): ``--layer``
-selects the seed and ``--bsz`` the batch.  The dense column is torch's scaled-dot-product attention
-on the unquantised K (``--no-flash`` leaves it out, like the reference's flag of that name).
+selects the seed and ``--bsz`` the batch.  The dense column ``flash_ms`` is FlashAttention's
+``flash_attn_func`` on the unquantised K, as in the reference, where that package is installed and runs
+(torch's scaled-dot-product attention otherwise; ``meta["dense_baseline"]`` says which), and
+``meta["sdpa_ms"]`` holds torch's own dense decode next to it; ``--no-flash`` leaves both out, like the
+reference's flag.
 
 ``--kernel`` is the reference's plug-in point (run_attn_bench_q2.py:34-39, 108-113): a Python module
 path that exports the variant's entry point (``attn_forward_decode_quantized`` for q2fp8, ...); it
@@ -92,6 +95,25 @@ def benchmark(fn, iters: int, warmup: int) -> float:
     return start.elapsed_time(end) / iters
 
 
+def dense_attention(q, k, v, sm_scale: float, prefer):
+    """The dense baseline on the unquantised K, V ``[B, L, HKV, D]`` and q ``[B, 1, HQ, D]``: FlashAttention's
+    ``flash_attn_func`` as in the reference (utils/flash.py) where it is installed and runs on this GPU,
+    torch's scaled_dot_product_attention otherwise.  Returns ``(callable, name)``; ``prefer`` is the name a
+    previous length settled on."""
+    if prefer in (None, "flash_attn"):
+        try:
+            from flash_attn import flash_attn_func
+            fn = lambda: flash_attn_func(q, k, v, softmax_scale=sm_scale, causal=False)
+            fn()
+            torch.cuda.synchronize()
+            return fn, "flash_attn"
+        except Exception:
+            pass
+    qd, kd, vd = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)          # [B, H, L, D]
+    return (lambda: torch.nn.functional.scaled_dot_product_attention(qd, kd, vd, scale=sm_scale, enable_gqa=True),
+            "torch_sdpa")
+
+
 def to_k(n: int) -> str:
     val = n / 1024.0
     return f"{int(val)}k" if abs(val - int(val)) < 1e-9 else f"{val:.1f}k"
@@ -144,6 +166,7 @@ def main() -> None:
     bits = {} if kind == "fp8" else {"k_bits": 2 if kind == "q2" else 4}
 
     fused_ms, cg_ms, dense_ms, skip_ratios = [], [], [], []
+    dense_name, sdpa_ms = None, []
     for L in lengths:
         k, v = k_all[:, :L].contiguous(), v_all[:, :L].contiguous()
         codes, scale, zero, res = quantize_variant(kind, k, f8, BS)
@@ -166,21 +189,23 @@ def main() -> None:
         if args.no_flash:
             dense_ms.append(None)
         else:
-            qd = q_all.to(kv_dtype).transpose(1, 2)                      # [B, HQ, 1, D]
-            kd, vd = k.transpose(1, 2), v.transpose(1, 2)                # [B, HKV, L, D]
-            dense_ms.append(benchmark(
-                lambda: torch.nn.functional.scaled_dot_product_attention(qd, kd, vd, scale=sm_scale, enable_gqa=True),
-                args.iters, args.warmup))
+            dense_fn, dense_name = dense_attention(q_all.to(kv_dtype), k, v, sm_scale, dense_name)
+            dense_ms.append(benchmark(dense_fn, args.iters, args.warmup))
+            if dense_name != "torch_sdpa":          # torch's own dense decode, as a second dense column
+                sdpa_fn, _ = dense_attention(q_all.to(kv_dtype), k, v, sm_scale, "torch_sdpa")
+                sdpa_ms.append(benchmark(sdpa_fn, args.iters, args.warmup))
         line = f"L={to_k(L):>6}  fused {fused_ms[-1] * 1e3:8.1f} us"
         if cg_ms:
             line += f"  cudagraph {cg_ms[-1] * 1e3:8.1f} us"
         if dense_ms[-1] is not None:
-            line += f"  dense {dense_ms[-1] * 1e3:8.1f} us"
+            line += f"  dense ({dense_name}) {dense_ms[-1] * 1e3:8.1f} us"
+            if sdpa_ms:
+                line += f"  dense (torch_sdpa) {sdpa_ms[-1] * 1e3:8.1f} us"
         print(line + f"  skip {skip:.3f}", flush=True)
 
     meta = dict(layer_indices=[args.layer], T_full=T_full, Hq=HQ, Hkv=HKV, D=D, Dv=D, BS=BS, SBS=SBS,
                 delta=args.delta, dtype=args.dtype, step=args.step, iters=args.iters, warmup=args.warmup,
-                attn_kernel=kernel_path, bsz=args.bsz, data="synthetic", fp8=args.fp8)
+                attn_kernel=kernel_path, bsz=args.bsz, data="synthetic", fp8=args.fp8, dense_baseline=dense_name)
     stem = (f"layer_{args.layer}_Tmax{to_k(T_full)}_Hq{HQ}_Hkv{HKV}_D{D}_Dv{D}_BS{BS}_SBS{SBS}_delta{args.delta:g}_"
             f"{args.dtype}_step{args.step}_it{args.iters}_wu{args.warmup}_bsz{args.bsz}")
     if args.cudagraph:
@@ -192,6 +217,8 @@ def main() -> None:
     else:
         payload = {"meta": meta, "lengths": lengths, "fused_ms": fused_ms,
                    "flash_ms": [float("nan") if x is None else x for x in dense_ms], "skip_ratios": skip_ratios}
+    if sdpa_ms:
+        payload["meta"]["sdpa_ms"] = sdpa_ms            # inside meta: the top-level keys stay the reference's
     path = Path(args.out_dir) / args.variant / (stem + ".json")
     path.parent.mkdir(parents=True, exist_ok=True)
     path.write_text(json.dumps(payload, indent=2))
