@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -508,6 +509,42 @@ def run_seqsplit(args, wl_name: str, wl: dict, rank: int, world: int, local_rank
     return out
 
 
+def dense_baseline(q, k, v, steps: int) -> dict:
+    """Dense decode attention over the UNquantised K and V of the same step, the comparison the reference's
+    benches draw (utils/flash.py: FlashAttention's flash_attn_func), with torch's scaled-dot-product
+    attention beside it.  A column for context: it reads 4 x B x T x HKV x 128 bytes, more than the pruned step."""
+    out = {"bytes_per_step": float(2 * k.numel() * 2 + 2 * q.numel() * 2),
+           "how": "dense attention on bf16 K, V of the same shape (library kernels), CUDA events, eager launches"}
+    sm_scale = 1.0 / math.sqrt(q.shape[-1])
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / steps
+
+    try:
+        from flash_attn import flash_attn_func
+        out["flash_attn_us"] = timed(lambda: flash_attn_func(q, k, v, softmax_scale=sm_scale, causal=False))
+    except Exception as exc:
+        out["flash_attn_us"] = None
+        out["flash_attn_note"] = f"{type(exc).__name__}: {exc}"[:200]
+    try:
+        qd, kd, vd = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+        out["torch_sdpa_us"] = timed(lambda: torch.nn.functional.scaled_dot_product_attention(
+            qd, kd, vd, scale=sm_scale, enable_gqa=True))
+    except Exception as exc:
+        out["torch_sdpa_us"] = None
+        out["torch_sdpa_note"] = f"{type(exc).__name__}: {exc}"[:200]
+    return out
+
+
 def triton_baseline(kind: str, q, codes, scale, zero, res, v, delta: float, steps: int) -> dict:
     """The reference's own Triton kernels, JIT-compiled on this GPU, on the same (contiguous) tensors:
     its CUDA-graph runner's replay_only(), which is what its cudagraph bench times
@@ -609,7 +646,8 @@ def main():
     ap.add_argument("--workload", default="fp8fp8_b8_t32k", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-triton-baseline", action="store_true", help="skip the reference's Triton kernels column")
+    ap.add_argument("--no-triton-baseline", action="store_true",
+                    help="skip the reference-side GPU columns (its Triton kernels, dense attention)")
     ap.add_argument("--no-targets", action="store_true", help="skip the 128K target shape (one GPU)")
     ap.add_argument("--no-seqsplit", action="store_true", help="skip the sequence-split leg (several GPUs)")
     ap.add_argument("--identity-table", action="store_true", help="identity block table instead of a permutation")
@@ -659,6 +697,9 @@ def main():
 
     # ---- this rank's slice of the job: its own batch of B sequences, quantised on the GPU --------
     q, k, v = make_decode_inputs(B, T, HQ, HKV, D, seed=1 + rank, device=dev)
+    dense = None
+    if rank == 0 and world == 1 and not args.no_triton_baseline:
+        dense = dense_baseline(q, k, v, max(10, min(args.steps, 100)))
     scale = zero = None
     if kind == "fp8":
         codes, res = Q.quantize_k_fp8_fp8_residual(k, f8)
@@ -800,6 +841,8 @@ def main():
             "gpu_launches": args.steps,        # one decode kernel per step (the merge runs inside it)
             "clocks": clocks,
         }
+        if dense is not None:
+            out["dense_baseline"] = dense
         if want_triton:
             # the reference's own kernels on the same box, same tensors (contiguous layout: it has no block table)
             tb = triton_baseline(kind, q, codes, scale, zero, res, v, delta, max(10, min(args.steps, 200)))
