@@ -18,6 +18,14 @@
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
 // warps 2..5 = epilogue (TMEM lane quarter = warp % 4).  Every mbarrier wait is bounded.
+//
+// Up to eight token rows (one decode step of a batch) take kproj_few_kernel instead: the call is then a
+// stream over W_k, so 32-channel column groups times a thread-block cluster that splits the hidden
+// dimension read the weight once with plain 16-byte loads, feed it to warp-level MMAs whose eight
+// columns are the tokens, add the cluster's partial sums through distributed shared memory in a
+// fixed order and run the same epilogue: one launch, no partial tiles in global memory, no waits
+// other than the hardware cluster barrier.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "ffa_common.cuh"
@@ -57,6 +65,8 @@ struct KprojParams {
   const void* sin;
   void* k_out;           // [M, N] post-RoPE K in out dtype
   int* status;
+  const void* h;         // [M, H] and [N, H] operands as plain pointers (kproj_few_kernel; the GEMM uses TMA maps)
+  const void* w;
   int M, T, N, H;
   float* partial;        // [n_split, M, N] fp32 when n_split > 1
   int m_tiles, n_split;
@@ -524,6 +534,122 @@ __global__ void __launch_bounds__(128) kproj_finish_kernel(const __grid_constant
   }
 }
 
+// ---- at most eight token rows: one launch -----------------------------------------------------------
+//
+// grid = (N / 32 column groups) x (cluster of CS CTAs along the hidden dimension), 256 threads.
+// CTA (group, rank) owns channels [32 group, +32) x hidden slice [rank * H/CS, +H/CS), slice <= 1024.
+// Warp w: channel half cw = w & 1 (16 channels = the 16 rows of an m16n8k16 A fragment), slice
+// quarter kw = w >> 1.  A lane (g = lane / 4, t = lane % 4) loads 16 bytes (8 hidden elements) of
+// weight rows g and g + 8 per 32-element step and 16 bytes of token g's hidden row from shared
+// memory; the eight elements feed two MMAs whose k positions are a permutation of the real ones,
+// the same for both operands, so the dot products are the real ones.  D[channel][token] (fp32)
+// goes to shared memory; the four slice quarters are added, then rank 0 adds the CS ranks'
+// [8][32] sums in rank order through distributed shared memory (so the result does not depend on
+// timing) and one thread per token applies bias, rounding, RoPE and the fused quantiser.
+constexpr int kFewRows = 8;                       // token rows per call (the MMA's n extent)
+constexpr int kFewSlice = 1024;                   // hidden elements per CTA at most
+constexpr int kFewPad = 32;                       // 64 bytes between token rows: conflict-free 16-byte reads
+constexpr int kFewThreads = 256;
+
+template <int IO>
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  if constexpr (IO == FFA_BF16) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+
+template <int IO, int ROPE, int QUANT>
+__global__ void __launch_bounds__(kFewThreads) kproj_few_kernel(const __grid_constant__ KprojParams p) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ __align__(16) uint16_t s_h[kFewRows * (kFewSlice + kFewPad)];
+  __shared__ float s_quarter[4][32][kFewRows];     // [slice quarter][channel][token]
+  __shared__ float s_part[kFewRows * 32];          // this CTA's sums, [token][channel]: what the peers read
+  __shared__ float s_sum[kFewRows][33];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cs = static_cast<int>(cluster.num_blocks());
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int group = blockIdx.x / cs;
+  const int slice = p.H / cs, stride = slice + kFewPad;
+  const int k0 = rank * slice;
+  const int n0 = group * 32;
+  const int cw = warp & 1, kw = warp >> 1;
+  const int g = lane >> 2, t = lane & 3;
+  const int quarter = slice / 4;                   // a multiple of 32
+  const int n_steps = quarter / 32;                // <= 8
+
+  // the weight first: every load of this lane is in flight before anything waits
+  const uint16_t* wp = static_cast<const uint16_t*>(p.w);
+  const uint16_t* w_lo = wp + static_cast<int64_t>(n0 + 16 * cw + g) * p.H + k0 + kw * quarter + 8 * t;
+  const uint16_t* w_hi = w_lo + 8LL * p.H;
+  uint4 wx[8], wy[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (j < n_steps) {
+      wx[j] = __ldg(reinterpret_cast<const uint4*>(w_lo + 32 * j));
+      wy[j] = __ldg(reinterpret_cast<const uint4*>(w_hi + 32 * j));
+    }
+  }
+  // the threads that will run the epilogue fetch their RoPE rows and cache slot now, off the tail
+  const bool finisher = rank == 0 && tid < p.M;
+  RopeTables<ROPE> tab;
+  int64_t out_row = tid;
+  if (finisher) {
+    tab.load(p, tid % p.T, n0 % kHeadDim);
+    if (QUANT != kQuantNone) out_row = out_row_of(p, tid);
+  }
+  // the token rows' hidden slice (rows beyond M are zero)
+  const uint16_t* hp = static_cast<const uint16_t*>(p.h);
+  const int vec_per_row = slice / 8;
+  for (int i = tid; i < kFewRows * vec_per_row; i += kFewThreads) {
+    const int row = i / vec_per_row, c8 = i % vec_per_row;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < p.M) v = __ldg(reinterpret_cast<const uint4*>(hp + static_cast<int64_t>(row) * p.H + k0 + 8 * c8));
+    *reinterpret_cast<uint4*>(&s_h[row * stride + 8 * c8]) = v;
+  }
+  __syncthreads();
+
+  float d[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint16_t* h_lane = &s_h[g * stride + kw * quarter + 8 * t];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (j < n_steps) {
+      const uint4 hv = *reinterpret_cast<const uint4*>(h_lane + 32 * j);
+      mma_16816<IO>(d, wx[j].x, wy[j].x, wx[j].y, wy[j].y, hv.x, hv.y);
+      mma_16816<IO>(d, wx[j].z, wy[j].z, wx[j].w, wy[j].w, hv.z, hv.w);
+    }
+  }
+  // D[channel g (+8)][token 2t (+1)]
+  s_quarter[kw][16 * cw + g][2 * t] = d[0];
+  s_quarter[kw][16 * cw + g][2 * t + 1] = d[1];
+  s_quarter[kw][16 * cw + g + 8][2 * t] = d[2];
+  s_quarter[kw][16 * cw + g + 8][2 * t + 1] = d[3];
+  __syncthreads();
+  {
+    const int tok = tid >> 5, ch = tid & 31;
+    s_part[tid] = (s_quarter[0][ch][tok] + s_quarter[1][ch][tok]) + (s_quarter[2][ch][tok] + s_quarter[3][ch][tok]);
+  }
+  cluster.sync();                                  // every rank's s_part is complete and visible
+  if (rank == 0) {
+    float acc = 0.f;
+    for (int r = 0; r < cs; ++r) acc += cluster.map_shared_rank(s_part, r)[tid];
+    s_sum[tid >> 5][tid & 31] = acc;
+  }
+  cluster.sync();                                  // the peers' shared memory has been read: they may exit
+  if (!finisher) return;
+  float sum[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) sum[i] = s_sum[tid][i];
+  rope_apply_store<IO, ROPE, QUANT>(sum, tab, p, tid, out_row, (n0 / kHeadDim) * kHeadDim, n0 % kHeadDim);
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -588,6 +714,19 @@ size_t partial_reserve(int64_t M, int N) {
   return align256(full < kPartialCap ? full : kPartialCap);
 }
 
+// Cluster size along the hidden dimension for the few-row kernel, or 0 when the shape does not fit it:
+// the slice of one CTA is at most kFewSlice elements and a multiple of 128 (four warps x 32-element
+// steps); more ranks are added while the grid stays within one CTA per SM.
+int plan_few(int64_t M, int N, int H) {
+  if (M > kFewRows || N % 32 != 0) return 0;
+  int cs = 0;
+  for (int c = 1; c <= 8; c *= 2)
+    if (H % (c * 128) == 0 && H / c <= kFewSlice) { cs = c; break; }
+  if (!cs) return 0;
+  while (cs < 8 && H % (2 * cs * 128) == 0 && static_cast<int64_t>(N / 32) * 2 * cs <= sm_count()) cs *= 2;
+  return cs;
+}
+
 }  // namespace
 }  // namespace ffa
 
@@ -628,11 +767,16 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   // two heads per tile when that still leaves at least one tile per SM
   const int64_t m_tiles = (M + kBM - 1) / kBM;
   const int bn = (N % 256 == 0 && m_tiles * (N / 256) >= sm_count()) ? 256 : 128;
+  // a handful of token rows (one decode step) go through the one-launch kernel
+  const bool aligned16 = ((reinterpret_cast<uintptr_t>(a->h) | reinterpret_cast<uintptr_t>(a->w)) & 15u) == 0;
+  const int few_cs = aligned16 ? plan_few(M, N, a->H) : 0;
   alignas(64) CUtensorMap ma, mb;
-  if (!make_operand_map(&ma, a->h, M, a->H, kBM) || !make_operand_map(&mb, a->w, N, a->H, bn)) return FFA_E_LAUNCH;
+  if (!few_cs && (!make_operand_map(&ma, a->h, M, a->H, kBM) || !make_operand_map(&mb, a->w, N, a->H, bn)))
+    return FFA_E_LAUNCH;
 
   KprojParams p{};
   p.bias = a->bias; p.cos = a->cos; p.sin = a->sin; p.k_out = k_rope;
+  p.h = a->h; p.w = a->w;
   p.status = reinterpret_cast<int*>(ws + k_bytes + q_bytes + p_bytes);
   p.partial = reinterpret_cast<float*>(ws + k_bytes + q_bytes);
   p.M = static_cast<int>(M); p.T = a->T; p.N = N; p.H = a->H;
@@ -666,6 +810,22 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   // shared-memory limit the first time it runs on a device
 #define FFA_KPROJ_LAUNCH(BN_, IO_, ROPE_, Q_)                                                                      \
   do {                                                                                                             \
+    if (few_cs) {                                                                                                  \
+      cudaLaunchConfig_t cfg = {};                                                                                 \
+      cfg.gridDim = dim3(static_cast<unsigned>(N / 32) * few_cs);                                                  \
+      cfg.blockDim = dim3(kFewThreads);                                                                            \
+      cfg.stream = st;                                                                                             \
+      cudaLaunchAttribute attr[1];                                                                                 \
+      attr[0].id = cudaLaunchAttributeClusterDimension;                                                            \
+      attr[0].val.clusterDim.x = static_cast<unsigned>(few_cs);                                                    \
+      attr[0].val.clusterDim.y = 1;                                                                                \
+      attr[0].val.clusterDim.z = 1;                                                                                \
+      cfg.attrs = attr;                                                                                            \
+      cfg.numAttrs = 1;                                                                                            \
+      cudaError_t ce = cudaLaunchKernelEx(&cfg, kproj_few_kernel<IO_, ROPE_, Q_>, p);                              \
+      if (ce != cudaSuccess) return note_cuda_error(ce, "kproj_few launch");                                       \
+      break;                                                                                                       \
+    }                                                                                                              \
     static bool configured[64] = {};                                                                               \
     if (dev >= 0 && dev < 64 && !configured[dev]) {                                                                \
       cudaError_t ce = cudaFuncSetAttribute(kproj_rope_kernel<BN_, IO_, ROPE_, Q_>,                                 \

@@ -112,6 +112,59 @@ def test_scatter_into_paged_cache():
             assert torch.equal(pool_r[slot, : t1 - t0], res.view(torch.uint8)[b, t0:t1])
 
 
+@pytest.mark.parametrize("rows,H,HKV", [(1, 4096, 8), (3, 4096, 8), (8, 4096, 8), (5, 512, 2), (8, 1024, 1),
+                                        (2, 8192, 8), (4, 384, 1), (7, 128, 2)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_few_token_rows_one_launch_kernel(rows, H, HKV, dtype):
+    """One decode step of a batch (at most eight token rows, T = 1) takes the cluster kernel: every
+    cluster size it picks (hidden 128 ... 8192), every row count, against the oracle's recipe and
+    against the same rows inside a call large enough to take the tensor-memory GEMM."""
+    h, w = make_kproj_inputs(1, H, HKV, 128, B=rows, seed=90 + rows, dtype=dtype)
+    w = w * 4.0
+    bias = (0.1 * torch.randn(HKV * 128, generator=torch.Generator().manual_seed(2))).to(dtype)
+    cos, sin = rope_tables(1, 33, dtype)
+    want = fo.kproj_rope(h, w, cos, sin, HKV, 128, bias=bias)
+    (got,) = KP.kproj_fused(None, h.cuda(), w.cuda(), cos.cuda(), sin.cuda(), HKV, 128, bias=bias.cuda())
+    assert status() == 0
+    ulp = 2.0 ** (-7 if dtype == torch.bfloat16 else -10)
+    scale = want.float().abs().max().item()
+    err = (got.float().cpu() - want.float()).abs()
+    assert err.max().item() <= 2.5 * ulp * scale, err.max().item()
+    assert err.mean().item() <= 0.05 * ulp * scale, err.mean().item()
+    # the same rows as the first token of 12 sequences (12 rows: the other kernel), same RoPE position
+    hb = torch.cat([h, h[:1].expand(12 - rows, -1, -1)], 0).contiguous()
+    (big,) = KP.kproj_fused(None, hb.cuda(), w.cuda(), cos.cuda(), sin.cuda(), HKV, 128, bias=bias.cuda())
+    diff = (got.float() - big[:rows].float()).abs()
+    assert diff.max().item() <= 2.5 * ulp * scale and (diff > 0).float().mean().item() <= 0.02
+
+
+@pytest.mark.parametrize("kind", ["fp8", "fp4"])
+def test_few_token_rows_append_into_paged_cache(kind):
+    """The fused quantiser of the few-row kernel appends at slot_pos0 through the block table and
+    writes what the standalone quantiser makes of the K it returns."""
+    from ffa_speedtest_b200 import quantize as Q
+    B, H, HKV, pos = 4, 4096, 8, 64 * 2 + 37
+    h, w = make_kproj_inputs(1, H, HKV, 128, B=B, seed=12, dtype=torch.bfloat16)
+    cos, sin = rope_tables(1, pos, torch.bfloat16)
+    args = (h.cuda(), (w * 4).cuda(), cos.cuda(), sin.cuda(), HKV, 128)
+    codes, res, k = KP.kproj_fused(kind, *args, fp8_dtype=E4, return_k=True)
+    again = KP._QUANT[kind](k, E4, 64)
+    assert torch.equal(codes.view(torch.uint8), again[0].view(torch.uint8))
+    assert torch.equal(res.view(torch.uint8), again[1].view(torch.uint8))
+    NP = 4
+    bt = make_block_table(B, NP, seed=4).cuda()
+    cw = codes.view(torch.uint8).shape[-1]
+    pool_c = torch.zeros(B * NP, 64, HKV, cw, dtype=torch.uint8, device="cuda")
+    pool_r = torch.zeros(B * NP, 64, HKV, 128, dtype=torch.uint8, device="cuda")
+    KP.kproj_fused(kind, *args, fp8_dtype=E4, block_table=bt, out=(pool_c, pool_r), position=pos)
+    assert status() == 0
+    for b in range(B):
+        slot = int(bt[b, pos // 64])
+        assert torch.equal(pool_c[slot, pos % 64], codes.view(torch.uint8)[b, 0])
+        assert torch.equal(pool_r[slot, pos % 64], res.view(torch.uint8)[b, 0])
+    assert int((pool_c != 0).any(dim=-1).any(dim=-1).sum()) == B      # nothing else was written
+
+
 def test_large_tile_count_against_cublas():
     """T = 8192 (benchmark config 3): 512 output tiles; cuBLAS + eager RoPE on the same GPU as a
     second opinion (not the oracle: its accumulation order is its own)."""
