@@ -292,8 +292,8 @@ def run_kproj(args, wl_name: str, wl: dict) -> dict:
     # fp8fp8 is quantised inside the GEMM epilogue; q2 reduces min/max there and then runs three small
     # kernels (reset of the min/max scratch, scale finalisation, encode)
     n_quant = {"q2": 4, "fp8": 0}[variant]
-    # up to eight token rows: one cluster kernel; a few hundred: split-k GEMM + finish kernel; else one GEMM
-    n_gemm = 1 if (T >= 4096 or T <= 8) else 2
+    # up to 24 token rows: one cluster kernel; a few hundred: split-k GEMM + finish kernel; else one GEMM
+    n_gemm = 1 if (T >= 4096 or T <= 24) else 2
     return {
         "metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": steps, "warmup": W,
         "ms_per_step": per_step_s * 1e3, "us_per_step": per_step_s * 1e6, "higher_is_better": True, "scaling": "weak",

@@ -19,10 +19,10 @@
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
 // warps 2..5 = epilogue (TMEM lane quarter = warp % 4).  Every mbarrier wait is bounded.
 //
-// Up to eight token rows (one decode step of a batch) take kproj_few_kernel instead: the call is then a
-// stream over W_k, so 32-channel column groups times a thread-block cluster that splits the hidden
-// dimension read the weight once with plain 16-byte loads, feed it to warp-level MMAs whose eight
-// columns are the tokens, add the cluster's partial sums through distributed shared memory in a
+// Up to 24 token rows (one decode step of a batch, a short chunk) take kproj_few_kernel instead: the
+// call is then a stream over W_k, so 32-channel column groups times a thread-block cluster that splits
+// the hidden dimension read the weight once with plain 16-byte loads, feed it to warp-level MMAs whose
+// eight columns are tokens, add the cluster's partial sums through distributed shared memory in a
 // fixed order and run the same epilogue: one launch, no partial tiles in global memory, no waits
 // other than the hardware cluster barrier.
 #include <cooperative_groups.h>
@@ -534,22 +534,30 @@ __global__ void __launch_bounds__(128) kproj_finish_kernel(const __grid_constant
   }
 }
 
-// ---- at most eight token rows: one launch -----------------------------------------------------------
+// ---- a few token rows (one decode step of a batch, a short chunk): one launch ------------------------
 //
 // grid = (N / 32 column groups) x (cluster of CS CTAs along the hidden dimension), 256 threads.
 // CTA (group, rank) owns channels [32 group, +32) x hidden slice [rank * H/CS, +H/CS), slice <= 1024.
 // Warp w: channel half cw = w & 1 (16 channels = the 16 rows of an m16n8k16 A fragment), slice
 // quarter kw = w >> 1.  A lane (g = lane / 4, t = lane % 4) loads 16 bytes (8 hidden elements) of
-// weight rows g and g + 8 per 32-element step and 16 bytes of token g's hidden row from shared
-// memory; the eight elements feed two MMAs whose k positions are a permutation of the real ones,
-// the same for both operands, so the dot products are the real ones.  D[channel][token] (fp32)
-// goes to shared memory; the four slice quarters are added, then rank 0 adds the CS ranks'
-// [8][32] sums in rank order through distributed shared memory (so the result does not depend on
-// timing) and one thread per token applies bias, rounding, RoPE and the fused quantiser.
-constexpr int kFewRows = 8;                       // token rows per call (the MMA's n extent)
+// weight rows g and g + 8 per 32-element step, once, and per block of eight token rows 16 bytes of
+// token g's hidden row from shared memory; the eight elements feed two MMAs whose k positions are
+// a permutation of the real ones, the same for both operands, so the dot products are the real
+// ones.  D[channel][token] (fp32) goes to shared memory; the four slice quarters are added, then
+// the ranks share out the blocks of eight rows: the owner of a block adds the CS ranks' [8][32]
+// sums in rank order through distributed shared memory (so the result does not depend on timing)
+// and one of its threads per token applies bias, rounding, RoPE and the fused quantiser.  NB = 1
+// (up to eight rows) compiles the block loops away; NB = kFewBlocks serves up to 24 rows.
+constexpr int kFewBlocks = 3;                     // blocks of eight token rows (the MMA's n extent) per call at most
+constexpr int kFewRows = 8 * kFewBlocks;          // beyond that the tensor-memory GEMM with split k is faster
 constexpr int kFewSlice = 1024;                   // hidden elements per CTA at most
 constexpr int kFewPad = 32;                       // 64 bytes between token rows: conflict-free 16-byte reads
 constexpr int kFewThreads = 256;
+
+// dynamic shared memory of the few-row kernel: hidden rows, per-quarter sums, CTA sums, cluster sums
+constexpr size_t few_smem_bytes(int rows, int slice) {
+  return static_cast<size_t>(rows) * ((slice + kFewPad) * 2 + (4 * 32 + 32 + 33) * 4);
+}
 
 template <int IO>
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -565,14 +573,11 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
   }
 }
 
-template <int IO, int ROPE, int QUANT>
+template <int IO, int ROPE, int QUANT, int NB>
 __global__ void __launch_bounds__(kFewThreads) kproj_few_kernel(const __grid_constant__ KprojParams p) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
-  __shared__ __align__(16) uint16_t s_h[kFewRows * (kFewSlice + kFewPad)];
-  __shared__ float s_quarter[4][32][kFewRows];     // [slice quarter][channel][token]
-  __shared__ float s_part[kFewRows * 32];          // this CTA's sums, [token][channel]: what the peers read
-  __shared__ float s_sum[kFewRows][33];
+  extern __shared__ __align__(16) uint8_t few_smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cs = static_cast<int>(cluster.num_blocks());
   const int rank = static_cast<int>(cluster.block_rank());
@@ -584,6 +589,12 @@ __global__ void __launch_bounds__(kFewThreads) kproj_few_kernel(const __grid_con
   const int g = lane >> 2, t = lane & 3;
   const int quarter = slice / 4;                   // a multiple of 32
   const int n_steps = quarter / 32;                // <= 8
+  const int nb = NB == 1 ? 1 : (p.M + 7) / 8;      // blocks of eight token rows (NB = 1: known when compiling)
+  const int rows = 8 * nb;
+  uint16_t* s_h = reinterpret_cast<uint16_t*>(few_smem);                      // [rows][stride]
+  float* s_quarter = reinterpret_cast<float*>(few_smem + static_cast<size_t>(rows) * stride * 2);   // [4][32][rows]
+  float* s_part = s_quarter + 4 * 32 * rows;       // [rows][32]: this CTA's sums, what the peers read
+  float* s_sum = s_part + 32 * rows;               // [rows][33]
 
   // the weight first: every load of this lane is in flight before anything waits
   const uint16_t* wp = static_cast<const uint16_t*>(p.w);
@@ -597,57 +608,76 @@ __global__ void __launch_bounds__(kFewThreads) kproj_few_kernel(const __grid_con
       wy[j] = __ldg(reinterpret_cast<const uint4*>(w_hi + 32 * j));
     }
   }
-  // the threads that will run the epilogue fetch their RoPE rows and cache slot now, off the tail
-  const bool finisher = rank == 0 && tid < p.M;
+  // Row block b (eight tokens) is finished by rank b % cs: that rank adds the cluster's sums of the block
+  // and runs its epilogue, thread i of the rank taking token 8 (rank + (i / 8) cs) + i % 8.  These threads
+  // fetch their RoPE rows and cache slot now, off the tail.
+  const int m_fin = 8 * (rank + (tid >> 3) * cs) + (tid & 7);
+  const bool finisher = tid < 8 * NB && m_fin < p.M;
   RopeTables<ROPE> tab;
-  int64_t out_row = tid;
+  int64_t out_row = m_fin;
   if (finisher) {
-    tab.load(p, tid % p.T, n0 % kHeadDim);
-    if (QUANT != kQuantNone) out_row = out_row_of(p, tid);
+    tab.load(p, m_fin % p.T, n0 % kHeadDim);
+    if (QUANT != kQuantNone) out_row = out_row_of(p, m_fin);
   }
   // the token rows' hidden slice (rows beyond M are zero)
   const uint16_t* hp = static_cast<const uint16_t*>(p.h);
   const int vec_per_row = slice / 8;
-  for (int i = tid; i < kFewRows * vec_per_row; i += kFewThreads) {
+  const uint32_t s_h_addr = smem_u32(s_h);
+  for (int i = tid; i < rows * vec_per_row; i += kFewThreads) {
     const int row = i / vec_per_row, c8 = i % vec_per_row;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (row < p.M) v = __ldg(reinterpret_cast<const uint4*>(hp + static_cast<int64_t>(row) * p.H + k0 + 8 * c8));
-    *reinterpret_cast<uint4*>(&s_h[row * stride + 8 * c8]) = v;
+    const bool live = row < p.M;                   // asynchronous 16-byte copies, all in flight; zero fill beyond M
+    const uint16_t* src = hp + static_cast<int64_t>(live ? row : 0) * p.H + k0 + 8 * c8;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s_h_addr + 2u * (row * stride + 8 * c8)),
+                 "l"(src), "r"(live ? 16 : 0)
+                 : "memory");
   }
+  asm volatile("cp.async.wait_all;\n" ::: "memory");
   __syncthreads();
 
-  float d[4] = {0.f, 0.f, 0.f, 0.f};
+  // One block of eight token rows at a time (a rolled loop: every instruction of this kernel runs once
+  // or twice per warp, so its time follows its code size); two accumulators halve the MMA chain.
   const uint16_t* h_lane = &s_h[g * stride + kw * quarter + 8 * t];
+  float* q_lo = s_quarter + (kw * 32 + 16 * cw + g) * rows + 2 * t;     // D[channel g (+8)][token 8 b + 2 t (+1)]
+  float* q_hi = q_lo + 8 * rows;
+#pragma unroll 1
+  for (int b = 0; b < nb; ++b) {
+    float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    if (j < n_steps) {
-      const uint4 hv = *reinterpret_cast<const uint4*>(h_lane + 32 * j);
-      mma_16816<IO>(d, wx[j].x, wy[j].x, wx[j].y, wy[j].y, hv.x, hv.y);
-      mma_16816<IO>(d, wx[j].z, wy[j].z, wx[j].w, wy[j].w, hv.z, hv.w);
+    for (int j = 0; j < 8; ++j) {
+      if (j < n_steps) {
+        const uint4 hv = *reinterpret_cast<const uint4*>(h_lane + 8 * b * stride + 32 * j);
+        mma_16816<IO>(d0, wx[j].x, wy[j].x, wx[j].y, wy[j].y, hv.x, hv.y);
+        mma_16816<IO>(d1, wx[j].z, wy[j].z, wx[j].w, wy[j].w, hv.z, hv.w);
+      }
     }
+    *reinterpret_cast<float2*>(q_lo + 8 * b) = make_float2(d0[0] + d1[0], d0[1] + d1[1]);
+    *reinterpret_cast<float2*>(q_hi + 8 * b) = make_float2(d0[2] + d1[2], d0[3] + d1[3]);
   }
-  // D[channel g (+8)][token 2t (+1)]
-  s_quarter[kw][16 * cw + g][2 * t] = d[0];
-  s_quarter[kw][16 * cw + g][2 * t + 1] = d[1];
-  s_quarter[kw][16 * cw + g + 8][2 * t] = d[2];
-  s_quarter[kw][16 * cw + g + 8][2 * t + 1] = d[3];
   __syncthreads();
-  {
-    const int tok = tid >> 5, ch = tid & 31;
-    s_part[tid] = (s_quarter[0][ch][tok] + s_quarter[1][ch][tok]) + (s_quarter[2][ch][tok] + s_quarter[3][ch][tok]);
+  const int tok8 = tid >> 5, ch = tid & 31;
+#pragma unroll 1
+  for (int b = 0; b < nb; ++b) {
+    const float* q = s_quarter + ch * rows + 8 * b + tok8;
+    s_part[256 * b + tid] = (q[0] + q[32 * rows]) + (q[64 * rows] + q[96 * rows]);
   }
   cluster.sync();                                  // every rank's s_part is complete and visible
-  if (rank == 0) {
+  // this rank's blocks: the remote values of a block are loaded together, the sum runs in rank order
+#pragma unroll 1
+  for (int i = 0, b = rank; b < nb; ++i, b += cs) {
+    float v[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) v[r] = r < cs ? cluster.map_shared_rank(s_part, r)[256 * b + tid] : 0.f;
     float acc = 0.f;
-    for (int r = 0; r < cs; ++r) acc += cluster.map_shared_rank(s_part, r)[tid];
-    s_sum[tid >> 5][tid & 31] = acc;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) acc += v[r];
+    s_sum[(8 * i + tok8) * 33 + ch] = acc;
   }
   cluster.sync();                                  // the peers' shared memory has been read: they may exit
   if (!finisher) return;
   float sum[32];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) sum[i] = s_sum[tid][i];
-  rope_apply_store<IO, ROPE, QUANT>(sum, tab, p, tid, out_row, (n0 / kHeadDim) * kHeadDim, n0 % kHeadDim);
+  for (int i = 0; i < 32; ++i) sum[i] = s_sum[tid * 33 + i];
+  rope_apply_store<IO, ROPE, QUANT>(sum, tab, p, m_fin, out_row, (n0 / kHeadDim) * kHeadDim, n0 % kHeadDim);
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -714,7 +744,8 @@ size_t partial_reserve(int64_t M, int N) {
   return align256(full < kPartialCap ? full : kPartialCap);
 }
 
-// Cluster size along the hidden dimension for the few-row kernel, or 0 when the shape does not fit it:
+// Cluster size along the hidden dimension for the few-row kernel, or 0 when the shape does not fit it
+// (more than kFewRows token rows, or a hidden size it cannot slice):
 // the slice of one CTA is at most kFewSlice elements and a multiple of 128 (four warps x 32-element
 // steps); more ranks are added while the grid stays within one CTA per SM.
 int plan_few(int64_t M, int N, int H) {
@@ -822,7 +853,21 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
       attr[0].val.clusterDim.z = 1;                                                                                \
       cfg.attrs = attr;                                                                                            \
       cfg.numAttrs = 1;                                                                                            \
-      cudaError_t ce = cudaLaunchKernelEx(&cfg, kproj_few_kernel<IO_, ROPE_, Q_>, p);                              \
+      cfg.dynamicSmemBytes = few_smem_bytes(static_cast<int>((M + 7) / 8 * 8), a->H / few_cs);                     \
+      cudaError_t ce;                                                                                              \
+      if (M <= 8) {                                                                                                \
+        ce = cudaLaunchKernelEx(&cfg, kproj_few_kernel<IO_, ROPE_, Q_, 1>, p);                                     \
+      } else {                                                                                                     \
+        static bool few_configured[64] = {};                                                                       \
+        if (dev >= 0 && dev < 64 && !few_configured[dev]) {                                                        \
+          ce = cudaFuncSetAttribute(kproj_few_kernel<IO_, ROPE_, Q_, kFewBlocks>,                                  \
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,                                   \
+                                    static_cast<int>(few_smem_bytes(kFewRows, kFewSlice)));                        \
+          if (ce != cudaSuccess) return note_cuda_error(ce, "cudaFuncSetAttribute(kproj_few)");                    \
+          few_configured[dev] = true;                                                                              \
+        }                                                                                                          \
+        ce = cudaLaunchKernelEx(&cfg, kproj_few_kernel<IO_, ROPE_, Q_, kFewBlocks>, p);                            \
+      }                                                                                                            \
       if (ce != cudaSuccess) return note_cuda_error(ce, "kproj_few launch");                                       \
       break;                                                                                                       \
     }                                                                                                              \

@@ -113,12 +113,13 @@ def test_scatter_into_paged_cache():
 
 
 @pytest.mark.parametrize("rows,H,HKV", [(1, 4096, 8), (3, 4096, 8), (8, 4096, 8), (5, 512, 2), (8, 1024, 1),
-                                        (2, 8192, 8), (4, 384, 1), (7, 128, 2)])
+                                        (2, 8192, 8), (4, 384, 1), (7, 128, 2), (9, 4096, 8), (16, 4096, 8),
+                                        (24, 4096, 8), (20, 512, 2), (24, 8192, 8), (17, 384, 1)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_few_token_rows_one_launch_kernel(rows, H, HKV, dtype):
-    """One decode step of a batch (at most eight token rows, T = 1) takes the cluster kernel: every
-    cluster size it picks (hidden 128 ... 8192), every row count, against the oracle's recipe and
-    against the same rows inside a call large enough to take the tensor-memory GEMM."""
+    """One decode step of a batch (at most 24 token rows) takes the cluster kernel: every cluster size
+    it picks (hidden 128 ... 8192), row counts in one and in several blocks of eight, against the
+    oracle's recipe and against the same rows inside a call large enough to take the tensor-memory GEMM."""
     h, w = make_kproj_inputs(1, H, HKV, 128, B=rows, seed=90 + rows, dtype=dtype)
     w = w * 4.0
     bias = (0.1 * torch.randn(HKV * 128, generator=torch.Generator().manual_seed(2))).to(dtype)
@@ -131,8 +132,8 @@ def test_few_token_rows_one_launch_kernel(rows, H, HKV, dtype):
     err = (got.float().cpu() - want.float()).abs()
     assert err.max().item() <= 2.5 * ulp * scale, err.max().item()
     assert err.mean().item() <= 0.05 * ulp * scale, err.mean().item()
-    # the same rows as the first token of 12 sequences (12 rows: the other kernel), same RoPE position
-    hb = torch.cat([h, h[:1].expand(12 - rows, -1, -1)], 0).contiguous()
+    # the same rows as the first token of 70 sequences (70 rows: the other kernel), same RoPE position
+    hb = torch.cat([h, h[:1].expand(70 - rows, -1, -1)], 0).contiguous()
     (big,) = KP.kproj_fused(None, hb.cuda(), w.cuda(), cos.cuda(), sin.cuda(), HKV, 128, bias=bias.cuda())
     diff = (got.float() - big[:rows].float()).abs()
     assert diff.max().item() <= 2.5 * ulp * scale and (diff > 0).float().mean().item() <= 0.02
@@ -163,6 +164,30 @@ def test_few_token_rows_append_into_paged_cache(kind):
         assert torch.equal(pool_c[slot, pos % 64], codes.view(torch.uint8)[b, 0])
         assert torch.equal(pool_r[slot, pos % 64], res.view(torch.uint8)[b, 0])
     assert int((pool_c != 0).any(dim=-1).any(dim=-1).sum()) == B      # nothing else was written
+
+
+def test_short_chunk_takes_the_few_row_kernel_with_positions():
+    """B x T <= 24 with T > 1: RoPE rows and cache slots follow (row % T), per sequence."""
+    B, T, H, HKV, pos = 2, 12, 4096, 8, 64 + 55          # the chunk crosses a page boundary
+    h, w = make_kproj_inputs(T, H, HKV, 128, B=B, seed=31, dtype=torch.bfloat16)
+    cos, sin = rope_tables(T, pos, torch.bfloat16)
+    args = (h.cuda(), (w * 4).cuda(), cos.cuda(), sin.cuda(), HKV, 128)
+    codes, res, k = KP.kproj_fused("fp8", *args, fp8_dtype=E4, return_k=True)
+    want = fo.kproj_rope(h, w * 4, cos, sin, HKV, 128)
+    err = (k.float().cpu() - want.float()).abs()
+    scale = want.float().abs().max().item()
+    assert err.max().item() <= 2.5 * 2.0 ** -7 * scale and err.mean().item() <= 0.05 * 2.0 ** -7 * scale
+    NP = 3
+    bt = make_block_table(B, NP, seed=6).cuda()
+    pool_c = torch.zeros(B * NP, 64, HKV, 128, dtype=torch.uint8, device="cuda")
+    pool_r = torch.zeros_like(pool_c)
+    KP.kproj_fused("fp8", *args, fp8_dtype=E4, block_table=bt, out=(pool_c, pool_r), position=pos)
+    assert status() == 0
+    for b in range(B):
+        for t in range(T):
+            slot, off = int(bt[b, (pos + t) // 64]), (pos + t) % 64
+            assert torch.equal(pool_c[slot, off], codes.view(torch.uint8)[b, t])
+            assert torch.equal(pool_r[slot, off], res.view(torch.uint8)[b, t])
 
 
 def test_large_tile_count_against_cublas():
