@@ -38,6 +38,12 @@ int quantize_dispatch(int variant, const void* k, int k_dtype, int B, int T, int
                       uint8_t* codes, void* scale, void* zero, uint8_t* residual, void* scratch,
                       const int32_t* slot_table, int slot_stride, int slot_pos0, cudaStream_t st);
 
+// same, with the per-channel min/max already reduced per group of 32 token rows by the GEMM's epilogue:
+// parts[B * parts_per_b][HKV*128][2] ordered uints (defined in ffa_quantize.cu)
+int quantize_from_partials(int variant, const void* k, int k_dtype, int B, int T, int HKV, int fp8, uint8_t* codes,
+                           void* scale, void* zero, uint8_t* residual, void* scratch, const uint32_t* parts,
+                           int parts_per_b, const int32_t* slot_table, int slot_stride, cudaStream_t st);
+
 namespace {
 
 constexpr int kBM = 128, kBK = 64;                  // tile rows; kBK 16-bit elements = one 128-byte swizzle row
@@ -69,6 +75,7 @@ struct KprojParams {
   const void* w;
   int M, T, N, H;
   float* partial;        // [n_split, M, N] fp32 when n_split > 1
+  uint32_t* mm_part;     // [M / 32, N, 2] ordered-uint (min, max) of K per 32 token rows, when the epilogue reduces them
   int m_tiles, n_split;
   int io_dtype;          // FFA_F16 | FFA_BF16: h, W, bias
   int rope_dtype;        // dtype of cos/sin; the RoPE arithmetic and k_out use promote(io, rope)
@@ -217,11 +224,19 @@ struct RopeTables16 {
 template <> struct RopeTables<FFA_BF16> : RopeTables16 {};
 template <> struct RopeTables<FFA_F16> : RopeTables16 {};
 
-template <int IO, int ROPE, int QUANT>
+// MM: 0 = nothing more; 1 = also reduce min and max of each channel over the warp's 32 token rows
+// (2-bit format), 2 = max of |K| (NF4), as order-preserving uints, into mm_row[32][2].  With MM every
+// lane of the warp must be here (the reductions are warp-wide): the caller uses it only when all
+// rows of every tile exist.
+enum { kMmNone = 0, kMmMinMax = 1, kMmAbsMax = 2 };
+
+template <int IO, int ROPE, int QUANT, int MM = kMmNone>
 __device__ __forceinline__ void rope_apply_store(const float (&acc)[32], const RopeTables<ROPE>& tab,
                                                  const KprojParams& p, int64_t m, int64_t out_row, int n_base,
-                                                 int ch0) {
+                                                 int ch0, uint32_t* mm_row = nullptr, int lane = 0) {
   static_assert(QUANT == kQuantNone || ROPE != FFA_F32, "the fused quantisers take 16-bit K");
+  static_assert(MM == kMmNone || (ROPE != FFA_F32 && QUANT == kQuantNone), "min/max in the epilogue: 16-bit K, no fused quantiser");
+  uint32_t wk[MM != kMmNone ? 16 : 1];             // the row's 32 K values as packed pairs (|K| for NF4)
   using P = Pack16<IO>;
   using T2 = typename P::T2;
   const int64_t o = m * p.N + n_base + ch0;
@@ -261,6 +276,10 @@ __device__ __forceinline__ void rope_apply_store(const float (&acc)[32], const R
         w[j] = *reinterpret_cast<const uint32_t*>(&r);
       }
       if (p.k_out) dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      if constexpr (MM != kMmNone) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wk[4 * i + j] = MM == kMmAbsMax ? (w[j] & 0x7fff7fffu) : w[j];
+      }
       if constexpr (QUANT != kQuantNone) {
         // the reference quantisers on these eight K values (ffa_numeric.h has the per-element rules)
         constexpr int kF8 = (QUANT == kQuantFp8E4 || QUANT == kQuantFp4E4) ? num::kE4M3 : num::kE5M2;
@@ -288,6 +307,53 @@ __device__ __forceinline__ void rope_apply_store(const float (&acc)[32], const R
         }
         *reinterpret_cast<uint2*>(p.residual + oe) = num::narrow8<kF8>(rf);
       }
+    }
+    if constexpr (MM != kMmNone) {
+      // Transposing butterfly over the warp's 32 rows on packed pairs: at lane bit b a lane keeps one half
+      // of its registers and trades the other half with lane ^ (1 << b), so after bits 4..1 lane L holds
+      // pair L >> 1 reduced over 16 rows, and bit 0 finishes it: lane L ends with channel L.
+      auto mn = [](uint32_t a, uint32_t b) {
+        const T2 r = __hmin2(*reinterpret_cast<const T2*>(&a), *reinterpret_cast<const T2*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
+      };
+      auto mx = [](uint32_t a, uint32_t b) {
+        const T2 r = __hmax2(*reinterpret_cast<const T2*>(&a), *reinterpret_cast<const T2*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
+      };
+      uint32_t lo[8], hi[8];
+      {
+        const bool up = (lane & 16) != 0;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const uint32_t keep = up ? wk[r + 8] : wk[r];
+          const uint32_t got = __shfl_xor_sync(0xffffffffu, up ? wk[r] : wk[r + 8], 16);
+          lo[r] = mn(keep, got);
+          hi[r] = mx(keep, got);
+        }
+      }
+#pragma unroll
+      for (int half = 4; half >= 1; half >>= 1) {   // lane bits 3, 2, 1
+        const bool up = (lane & (2 * half)) != 0;
+#pragma unroll
+        for (int r = 0; r < half; ++r) {
+          const uint32_t keep_hi = up ? hi[r + half] : hi[r];
+          const uint32_t got_hi = __shfl_xor_sync(0xffffffffu, up ? hi[r] : hi[r + half], 2 * half);
+          hi[r] = mx(keep_hi, got_hi);
+          if (MM == kMmMinMax) {
+            const uint32_t keep_lo = up ? lo[r + half] : lo[r];
+            const uint32_t got_lo = __shfl_xor_sync(0xffffffffu, up ? lo[r] : lo[r + half], 2 * half);
+            lo[r] = mn(keep_lo, got_lo);
+          }
+        }
+      }
+      hi[0] = mx(hi[0], __shfl_xor_sync(0xffffffffu, hi[0], 1));
+      if (MM == kMmMinMax) lo[0] = mn(lo[0], __shfl_xor_sync(0xffffffffu, lo[0], 1));
+      const float2 flo = P::to_floats(*reinterpret_cast<const T2*>(&lo[0]));
+      const float2 fhi = P::to_floats(*reinterpret_cast<const T2*>(&hi[0]));
+      const uint32_t ulo = __float_as_uint((lane & 1) ? flo.y : flo.x), uhi = __float_as_uint((lane & 1) ? fhi.y : fhi.x);
+      reinterpret_cast<uint2*>(mm_row)[lane] =
+          make_uint2(MM == kMmMinMax ? ((ulo & 0x80000000u) ? ~ulo : (ulo | 0x80000000u)) : 0u,
+                     (uhi & 0x80000000u) ? ~uhi : (uhi | 0x80000000u));
     }
   } else {
     float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.k_out) + o);
@@ -317,7 +383,7 @@ __device__ __forceinline__ void rope_store_32_t(const float (&acc)[32], const Kp
 // the row's cos/sin, so each 32-channel slice of the tables is loaded once (the next slice while the
 // current one is used) and applied to every head.  All 32 lanes run the TMEM loads; rows beyond M
 // only skip the global loads and stores.  The accumulator is released once the last TMEM load has landed.
-template <int IO, int ROPE, int QUANT, int BN>
+template <int IO, int ROPE, int QUANT, int BN, int MM>
 __device__ __forceinline__ void epilogue_row(const KprojParams& p, uint32_t taddr, int64_t m, int n0,
                                              uint32_t bar_release, int lane) {
   constexpr int kHeads = BN / kHeadDim;
@@ -336,7 +402,13 @@ __device__ __forceinline__ void epilogue_row(const KprojParams& p, uint32_t tadd
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_release) : "memory");
       }
-      if (valid) rope_apply_store<IO, ROPE, QUANT>(v, tab, p, m, out_row, n0 + hd * kHeadDim, 32 * c);
+      if constexpr (MM != kMmNone) {
+        // every row of the tile exists (the host checked): the whole warp takes part in the reductions
+        uint32_t* mm_row = p.mm_part + ((m >> 5) * p.N + n0 + hd * kHeadDim + 32 * c) * 2;
+        rope_apply_store<IO, ROPE, QUANT, MM>(v, tab, p, m, out_row, n0 + hd * kHeadDim, 32 * c, mm_row, lane);
+      } else {
+        if (valid) rope_apply_store<IO, ROPE, QUANT>(v, tab, p, m, out_row, n0 + hd * kHeadDim, 32 * c);
+      }
     }
   };
   if constexpr (ROPE == FFA_F32) {
@@ -363,7 +435,7 @@ __device__ __forceinline__ void epilogue_row(const KprojParams& p, uint32_t tadd
 // With n_split == 1 the epilogue is fused (bias, rounding, RoPE, store K); with n_split > 1 (few
 // tokens: the GEMM is then a stream over W_k and needs more CTAs than output tiles) each item
 // stores its fp32 partial tile and kproj_finish_kernel adds the splits and applies the epilogue.
-template <int BN, int IO, int ROPE, int QUANT>
+template <int BN, int IO, int ROPE, int QUANT, int MM>
 __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_constant__ KprojParams p,
                                                                const __grid_constant__ CUtensorMap tm_a,
                                                                const __grid_constant__ CUtensorMap tm_b) {
@@ -464,7 +536,7 @@ __global__ void __launch_bounds__(kThreadsK) kproj_rope_kernel(const __grid_cons
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * kBN;
       const uint32_t bar_release = bar_tempty + 8 * buf;
       if (p.n_split == 1) {
-        epilogue_row<IO, ROPE, QUANT, kBN>(p, taddr, m, n0, bar_release, lane);
+        epilogue_row<IO, ROPE, QUANT, kBN, MM>(p, taddr, m, n0, bar_release, lane);
       } else {
         const int split = w % p.n_split;
 #pragma unroll 1
@@ -744,6 +816,16 @@ size_t partial_reserve(int64_t M, int N) {
   return align256(full < kPartialCap ? full : kPartialCap);
 }
 
+// The epilogue can reduce the per-channel min/max the 2-bit and NF4 scales need (one pair per 32 token
+// rows and channel, folded by a small kernel afterwards) when every tile is full and belongs to
+// one sequence (T a multiple of the tile height) and the GEMM is not split along k.
+bool minmax_in_epilogue(int T, int64_t M, int N) {
+  return T % kBM == 0 && ((M + kBM - 1) / kBM) * (N / 128) >= kFewTiles;
+}
+size_t minmax_part_reserve(int T, int64_t M, int N) {
+  return minmax_in_epilogue(T, M, N) ? align256(static_cast<size_t>(M / 32) * N * 2 * sizeof(uint32_t)) : 0;
+}
+
 // Cluster size along the hidden dimension for the few-row kernel, or 0 when the shape does not fit it
 // (more than kFewRows token rows, or a hidden size it cannot slice):
 // the slice of one CTA is at most kFewSlice elements and a multiple of 128 (four warps x 32-element
@@ -768,7 +850,8 @@ extern "C" size_t ffa_kproj_workspace_bytes(int32_t B, int32_t T, int32_t HKV, i
   const int64_t M = static_cast<int64_t>(B) * T;
   const int N = HKV * kHeadDim;
   const size_t k_bytes = static_cast<size_t>(M) * N * elem_size(rope_dtype == FFA_F32 ? FFA_F32 : FFA_BF16);
-  return align256(k_bytes) + align256(ffa_quantize_scratch_bytes(B, HKV)) + partial_reserve(M, N) + 256;
+  return align256(k_bytes) + align256(ffa_quantize_scratch_bytes(B, HKV)) + partial_reserve(M, N) +
+         minmax_part_reserve(T, M, N) + 256;
 }
 
 extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
@@ -786,10 +869,10 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   if (M > 0x7fffffffLL) return FFA_E_LIMIT;
   const int out_dt = a->rope_dtype == FFA_F32 ? FFA_F32 : a->io_dtype;
 
-  // workspace: [post-RoPE K][quantiser min/max][k-split partial tiles][status]
+  // workspace: [post-RoPE K][quantiser min/max][k-split partial tiles or per-32-row min/max][status]
   const size_t k_bytes = align256(static_cast<size_t>(M) * N * elem_size(out_dt));
   const size_t q_bytes = align256(ffa_quantize_scratch_bytes(a->B, a->HKV));
-  const size_t p_bytes = partial_reserve(M, N);
+  const size_t p_bytes = partial_reserve(M, N) + minmax_part_reserve(a->T, M, N);   // never both
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   if (!ws || a->workspace_bytes < k_bytes + q_bytes + p_bytes + 256) return FFA_E_WORKSPACE;
   void* k_rope = a->k_rope_out ? a->k_rope_out : static_cast<void*>(ws);
@@ -814,6 +897,11 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   p.m_tiles = static_cast<int>(m_tiles);
   p.n_split = bn == 256 ? 1 : plan_split(M, N, a->H / kBK);
   p.io_dtype = a->io_dtype; p.rope_dtype = a->rope_dtype;
+  p.mm_part = reinterpret_cast<uint32_t*>(ws + k_bytes + q_bytes);
+  int mm_mode = kMmNone;
+  if (need_quant && out_dt != FFA_F32 && !few_cs && p.n_split == 1 && minmax_in_epilogue(a->T, M, N) &&
+      (a->variant == FFA_K_Q2 || a->variant == FFA_K_NF4))
+    mm_mode = a->variant == FFA_K_Q2 ? kMmMinMax : kMmAbsMax;
 
   // the elementwise formats are quantised inside the epilogue when K is 16-bit; K itself is then
   // written only if the caller asked for it
@@ -839,7 +927,7 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   cudaGetDevice(&dev);
   // one kernel per (tile width, activation dtype, table dtype, fused quantiser); each raises its
   // shared-memory limit the first time it runs on a device
-#define FFA_KPROJ_LAUNCH(BN_, IO_, ROPE_, Q_)                                                                      \
+#define FFA_KPROJ_LAUNCH(BN_, IO_, ROPE_, Q_, MM_)                                                                  \
   do {                                                                                                             \
     if (few_cs) {                                                                                                  \
       cudaLaunchConfig_t cfg = {};                                                                                 \
@@ -873,32 +961,36 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
     }                                                                                                              \
     static bool configured[64] = {};                                                                               \
     if (dev >= 0 && dev < 64 && !configured[dev]) {                                                                \
-      cudaError_t ce = cudaFuncSetAttribute(kproj_rope_kernel<BN_, IO_, ROPE_, Q_>,                                 \
+      cudaError_t ce = cudaFuncSetAttribute(kproj_rope_kernel<BN_, IO_, ROPE_, Q_, MM_>,                            \
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<BN_>::kBytes);       \
       if (ce != cudaSuccess) return note_cuda_error(ce, "cudaFuncSetAttribute(kproj_rope)");                       \
       configured[dev] = true;                                                                                      \
     }                                                                                                              \
-    kproj_rope_kernel<BN_, IO_, ROPE_, Q_><<<grid, kThreadsK, Tile<BN_>::kBytes, st>>>(p, ma, mb);                  \
+    kproj_rope_kernel<BN_, IO_, ROPE_, Q_, MM_><<<grid, kThreadsK, Tile<BN_>::kBytes, st>>>(p, ma, mb);             \
     if (p.n_split > 1 && cudaPeekAtLastError() == cudaSuccess)                                                     \
       kproj_finish_kernel<IO_, ROPE_, Q_><<<finish_grid, 128, 0, st>>>(p);                                         \
   } while (0)
 #define FFA_KPROJ_Q(BN_, IO_)                                                                                      \
   do {                                                                                                             \
     switch (quant) {                                                                                               \
-      case kQuantFp8E4: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp8E4); break;                                       \
-      case kQuantFp8E5: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp8E5); break;                                       \
-      case kQuantFp4E4: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp4E4); break;                                       \
-      case kQuantFp4E5: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp4E5); break;                                       \
-      default: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantNone); break;                                                 \
+      case kQuantFp8E4: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp8E4, kMmNone); break;                              \
+      case kQuantFp8E5: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp8E5, kMmNone); break;                              \
+      case kQuantFp4E4: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp4E4, kMmNone); break;                              \
+      case kQuantFp4E5: FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantFp4E5, kMmNone); break;                              \
+      default:                                                                                                     \
+        if (mm_mode == kMmMinMax) FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantNone, kMmMinMax);                          \
+        else if (mm_mode == kMmAbsMax) FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantNone, kMmAbsMax);                     \
+        else FFA_KPROJ_LAUNCH(BN_, IO_, IO_, kQuantNone, kMmNone);                                                 \
+        break;                                                                                                     \
     }                                                                                                              \
   } while (0)
 #define FFA_KPROJ_BN(BN_)                                                                                          \
   do {                                                                                                             \
     if (a->io_dtype == FFA_BF16) {                                                                                 \
-      if (a->rope_dtype == FFA_F32) FFA_KPROJ_LAUNCH(BN_, FFA_BF16, FFA_F32, kQuantNone);                          \
+      if (a->rope_dtype == FFA_F32) FFA_KPROJ_LAUNCH(BN_, FFA_BF16, FFA_F32, kQuantNone, kMmNone);                 \
       else FFA_KPROJ_Q(BN_, FFA_BF16);                                                                             \
     } else {                                                                                                       \
-      if (a->rope_dtype == FFA_F32) FFA_KPROJ_LAUNCH(BN_, FFA_F16, FFA_F32, kQuantNone);                           \
+      if (a->rope_dtype == FFA_F32) FFA_KPROJ_LAUNCH(BN_, FFA_F16, FFA_F32, kQuantNone, kMmNone);                  \
       else FFA_KPROJ_Q(BN_, FFA_F16);                                                                              \
     }                                                                                                              \
   } while (0)
@@ -910,6 +1002,11 @@ extern "C" int ffa_kproj_rope(const FfaKprojArgs* a, ffa_stream_t stream_) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return note_cuda_error(e, "kproj_rope launch");
   if (!need_quant || quant != kQuantNone) return FFA_OK;
+  if (mm_mode != kMmNone)
+    return quantize_from_partials(a->variant, k_rope, out_dt, a->B, a->T, a->HKV, a->fp8_format,
+                                  static_cast<uint8_t*>(a->codes), a->scale, a->zero,
+                                  static_cast<uint8_t*>(a->residual), ws + k_bytes, p.mm_part, a->T / 32,
+                                  a->slot_table, a->slot_stride, st);
   return quantize_dispatch(a->variant, k_rope, out_dt, a->B, a->T, a->HKV, a->fp8_format, a->page_size,
                            static_cast<uint8_t*>(a->codes), a->scale, a->zero, static_cast<uint8_t*>(a->residual),
                            ws + k_bytes, a->slot_table, a->slot_stride, a->slot_table ? a->slot_pos0 : 0, st);

@@ -158,6 +158,44 @@ __global__ void nf4_finalize_kernel(const uint32_t* mm, int n, int dt, void* sca
   if (i < n) store_elem(scale, i, dt, fmaxf(ord_decode(mm[2 * i + 1]), 1e-6f));
 }
 
+// Folds per-slab (min, max) pairs, parts[B * parts_per_b][n_cols][2] ordered uints (what the K-projection's
+// epilogue leaves per 32 token rows), into mm[B][n_cols][2] and finalises the scales in the same
+// pass.  Block = 32 channels x 32 slab lanes (every load of a thread in flight at once for up to
+// 256 slabs), grid = (n_cols / 32, B).
+template <bool ABS>
+__global__ void __launch_bounds__(1024) minmax_fold_kernel(const uint32_t* __restrict__ parts, int parts_per_b,
+                                                           int n_cols, uint32_t* __restrict__ mm, int dt,
+                                                           void* scale, void* zero) {
+  __shared__ uint32_t s_lo[32][33], s_hi[32][33];
+  const int lane = threadIdx.x & 31, pl = threadIdx.x >> 5, b = blockIdx.y;
+  const int c = blockIdx.x * 32 + lane;
+  uint32_t lo = 0xffffffffu, hi = 0u;
+  const uint2* src = reinterpret_cast<const uint2*>(parts) + static_cast<int64_t>(b) * parts_per_b * n_cols + c;
+#pragma unroll 8
+  for (int q = pl; q < parts_per_b; q += 32) {
+    const uint2 v = src[static_cast<int64_t>(q) * n_cols];
+    lo = min(lo, v.x);
+    hi = max(hi, v.y);
+  }
+  s_lo[pl][lane] = lo;
+  s_hi[pl][lane] = hi;
+  __syncthreads();
+  if (pl != 0) return;
+#pragma unroll
+  for (int q = 1; q < 32; ++q) { lo = min(lo, s_lo[q][lane]); hi = max(hi, s_hi[q][lane]); }
+  const int64_t i = static_cast<int64_t>(b) * n_cols + c;
+  mm[2 * i] = ABS ? ord_encode(0.f) : lo;
+  mm[2 * i + 1] = hi;
+  if (ABS) {
+    store_elem(scale, i, dt, fmaxf(ord_decode(hi), 1e-6f));
+  } else {
+    float sc, z;
+    q2_scale_zero(ord_decode(lo), ord_decode(hi), dt, &sc, &z);
+    store_elem(scale, i, dt, sc);
+    store_elem(zero, i, dt, z);
+  }
+}
+
 // nf4 append: the encoder reads absmax as ordered uints; rebuild them from the (frozen) scale tensor
 __global__ void nf4_mm_from_scale_kernel(const void* scale, int n, int dt, uint32_t* mm) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -451,6 +489,34 @@ int quantize_dispatch(int variant, const void* k, int k_dtype, int B, int T, int
   if (slot_pos0 != 0 && (!slot_table || (variant != FFA_K_FP8 && variant != FFA_K_FP4))) return FFA_E_VARIANT;
   return quantize_impl(variant, k, k_dtype, B, T, HKV, fp8, page_size, codes, scale, zero, residual, scratch,
                        RowMap{slot_table, slot_stride, T, slot_pos0}, st);
+}
+
+// q2 / nf4 with the min/max already reduced per slab of token rows (by the K-projection's epilogue):
+// fold + finalise in one small kernel, then the usual encode pass.
+int quantize_from_partials(int variant, const void* k, int k_dtype, int B, int T, int HKV, int fp8, uint8_t* codes,
+                           void* scale, void* zero, uint8_t* residual, void* scratch, const uint32_t* parts,
+                           int parts_per_b, const int32_t* slot_table, int slot_stride, cudaStream_t st) {
+  int rc = check_common(k, k_dtype, B, T, HKV, fp8);
+  if (rc) return rc;
+  if (variant != FFA_K_Q2 && variant != FFA_K_NF4) return FFA_E_VARIANT;
+  if (!codes || !residual || !scale || !scratch || !parts || (variant == FFA_K_Q2 && !zero)) return FFA_E_NULL;
+  if (parts_per_b <= 0 || B > 65535) return FFA_E_SHAPE;
+  if (static_cast<int64_t>(B) * T >= (int64_t{1} << 31)) return FFA_E_LIMIT;
+  if (!aligned16(k) || !aligned16(codes) || !aligned16(residual) || !aligned16(scale) || !aligned16(zero) ||
+      !aligned16(scratch) || !aligned16(parts))
+    return FFA_E_ALIGN;
+  const int n_cols = HKV * D;
+  uint32_t* mm = static_cast<uint32_t*>(scratch);
+  const RowMap map{slot_table, slot_stride, T, 0};
+  const dim3 grid(n_cols / 32, B);
+  if (variant == FFA_K_Q2) {
+    minmax_fold_kernel<false><<<grid, 1024, 0, st>>>(parts, parts_per_b, n_cols, mm, k_dtype, scale, zero);
+    launch_encode<kEncQ2>(k, k_dtype, fp8, B, T, HKV, scale, zero, codes, residual, map, st);
+  } else {
+    minmax_fold_kernel<true><<<grid, 1024, 0, st>>>(parts, parts_per_b, n_cols, mm, k_dtype, scale, nullptr);
+    launch_encode<kEncNf4>(k, k_dtype, fp8, B, T, HKV, mm, nullptr, codes, residual, map, st);
+  }
+  return last_launch("ffa_quantize (min/max from the projection)");
 }
 
 }  // namespace ffa

@@ -190,6 +190,26 @@ def test_short_chunk_takes_the_few_row_kernel_with_positions():
             assert torch.equal(pool_r[slot, off], res.view(torch.uint8)[b, t])
 
 
+@pytest.mark.parametrize("kind", ["q2", "nf4"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,T,H,HKV", [(2, 1024, 512, 8), (1, 2048, 256, 8), (3, 512, 256, 8), (1, 4864, 128, 8)])
+def test_minmax_reduced_in_the_epilogue_equals_the_standalone_quantiser(kind, dtype, B, T, H, HKV):
+    """Whole tiles of one sequence (T a multiple of 128, enough tiles for an unsplit GEMM): the epilogue
+    leaves per-32-row min/max, a fold kernel finishes the scales.  Same bits as quantising the returned
+    K with the standalone quantiser and with the oracle, per sequence of the batch."""
+    h, w = make_kproj_inputs(T, H, HKV, 128, B=B, seed=61, dtype=dtype)
+    cos, sin = rope_tables(T, 5, dtype)
+    *outs, k = KP.kproj_fused(kind, h.cuda(), (w * 4).cuda(), cos.cuda(), sin.cuda(), HKV, 128, fp8_dtype=E4,
+                              return_k=True)
+    assert status() == 0
+    again = KP._QUANT[kind](k, E4, 64)
+    ref = fo.QUANTIZERS[kind](k.cpu(), E4)
+    for a, b, c in zip(outs, again, ref):
+        view = (lambda x: x.view(torch.uint8) if x.dtype.itemsize == 1 else x)
+        assert torch.equal(view(a), view(b))
+        assert torch.equal(view(a.cpu()), view(c))
+
+
 def test_large_tile_count_against_cublas():
     """T = 8192 (benchmark config 3): 512 output tiles; cuBLAS + eager RoPE on the same GPU as a
     second opinion (not the oracle: its accumulation order is its own)."""
