@@ -48,6 +48,21 @@ def test_all_quantisers_bit_exact(dt, f8):
             assert same(got, ref)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_q2_quotient_rounding_on_many_values(dt):
+    """(k - zero) / scale rounded to K's dtype, then to the nearest code with ties to even: four million
+    values, plus constructed ties at code + 0.5 and tiny / huge magnitudes, must give the oracle's bits."""
+    _, k, _ = make_decode_inputs(1, 4096, 32, 8, 128, seed=17, dtype=dt)
+    k = k.contiguous()
+    # channels with an exact grid: min 0, max 3 -> scale 1, so values at n + 0.5 are exact ties
+    k[0, :, 0, 0] = torch.tensor([0.0, 3.0, 0.5, 1.5, 2.5, 2.4921875, 2.5078125, 1.0], dtype=dt).repeat(512)
+    k[0, :, 1, 1] = torch.tensor([-1e-4, 1e-4, 0.0, 6e-5], dtype=dt).repeat(1024)
+    k[0, :, 2, 2] = torch.tensor([-30000.0, 30000.0, 1.0, -1.0], dtype=dt).repeat(1024)
+    for f8 in (torch.float8_e4m3fn, torch.float8_e5m2):
+        for got, ref in zip(Q.quantize_k_2bit_fp8_residual(k.cuda(), f8), fo.quantize_q2(k, f8)):
+            assert same(got, ref)
+
+
 def test_large_shape_properties():
     """Config-1-sized K (cut to B=2): idempotence of the fp8 base and residual bound."""
     _, k, _ = make_decode_inputs(2, 32768, 32, 8, 128, seed=1, device="cuda")
