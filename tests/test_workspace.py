@@ -49,3 +49,24 @@ def test_reference_constructor_and_matches(built_lib):
     ws3 = allocate_decode_workspace(q, v, BS=64, SBS=64, seq_len=4096)
     assert ws3.NTBS == 64 and ws3.fits(2, 8, 2, 128, 10, q.device, q.dtype) and not ws3.fits(2, 8, 2, 128, 65, q.device, q.dtype)
     assert isinstance(ws3, DecodeWorkspace)
+
+
+def test_kproj_workspace_covers_its_regions(built_lib):
+    """K-projection workspace = post-RoPE K + quantiser min/max + (k-split partial tiles for few tiles, or the
+    epilogue's per-32-row min/max pairs when T is a multiple of the tile height) + 256 bytes of status."""
+    L = _lib.lib()
+    B, HKV, N = 1, 8, 1024
+    bf16 = _lib.float_code(torch.bfloat16)
+
+    def need(T):
+        return L.ffa_kproj_workspace_bytes(B, T, HKV, bf16)
+
+    k_and_mm = lambda T: T * N * 2 + B * N * 8
+    # whole tiles, enough of them for an unsplit GEMM: one (min, max) pair per 32 rows and channel on top
+    assert need(8192) >= k_and_mm(8192) + (8192 // 32) * N * 8 + 256
+    # a ragged length keeps the separate min/max kernel: no such region
+    assert need(8191) < k_and_mm(8191) + (8191 // 32) * N * 8
+    # few tiles: fp32 partial tiles of the k split (up to 16 splits, capped at 16 MiB)
+    assert need(64) >= k_and_mm(64) + 16 * 64 * N * 4 + 256
+    assert need(1) >= k_and_mm(1) + 256
+    assert L.ffa_kproj_workspace_bytes(0, 64, HKV, bf16) == 0
