@@ -289,9 +289,10 @@ def run_kproj(args, wl_name: str, wl: dict) -> dict:
                 "note": "few-token projection: streaming the 8 MiB weight from HBM is the floor; launch latency dominates"}
         metric, unit, value = "kproj_rope_quantize_TBps", "TB/s", byt / per_step_s / 1e12
         e2e_value = byt / s_e2e / 1e12
-    # fp8fp8 is quantised inside the GEMM epilogue; q2 reduces min/max there and then runs three small
-    # kernels (reset of the min/max scratch, scale finalisation, encode)
-    n_quant = {"q2": 4, "fp8": 0}[variant]
+    # fp8fp8 is quantised inside the GEMM epilogue.  q2 with whole 128-row tiles (T=8192): the epilogue leaves
+    # per-32-row min/max, then a fold kernel and the encode kernel; other lengths: reset of the min/max
+    # scratch, min/max, scale finalisation, encode
+    n_quant = 0 if variant == "fp8" else (2 if T % 128 == 0 and T >= 4096 else 4)
     # up to 24 token rows: one cluster kernel; a few hundred: split-k GEMM + finish kernel; else one GEMM
     n_gemm = 1 if (T >= 4096 or T <= 24) else 2
     return {
